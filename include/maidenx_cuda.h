@@ -1,0 +1,230 @@
+/*
+ * maidenx_cuda.h — C ABI of the sm_100a op library (libmaidenx_cuda.so).
+ *
+ * Every `cuda_<op>_<dtype>` entry point below has the name, argument order and argument
+ * meaning of the symbol of the same name that the reference's `maidenx_cuda` crate
+ * declares for its own kernels and that `maidenx_core`'s backend dispatch calls; the
+ * library is a link-time replacement for that crate's `libops.a` / `libnn.a`.
+ *
+ * Conventions shared by all op entry points (reference: crates/maidenx_cuda/src/ops/*.rs,
+ * crates/maidenx_core/src/be/ops/binary.rs:96-169):
+ *   - data pointers are device buffer BASE pointers; element offsets travel in `metadata`;
+ *   - `metadata` is an array of size_t.  The reference uploads it to device memory before
+ *     each call; this library accepts device memory (resolved through its upload wrappers
+ *     without a device round trip, or read back when uploaded some other way) and, as an
+ *     extension, plain host memory;
+ *   - outputs are written contiguously from element 0 and never need to be pre-zeroed;
+ *   - launches go to the legacy default stream of the calling thread's current device
+ *     unless mx_set_stream() was called on that thread;
+ *   - functions return void; failures are recorded in a sticky per-thread status
+ *     (mx_last_error) instead of being silently dropped.
+ *   - bf16 / f16 values cross the boundary as 16-bit patterns (the reference's half::bf16 /
+ *     half::f16 are repr(transparent) u16), bool as one byte holding 0 or 1.
+ */
+#ifndef MAIDENX_CUDA_H
+#define MAIDENX_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+typedef bool mx_bool;
+#else
+typedef _Bool mx_bool;
+/* The dtype suffix `bool` is pasted into symbol names below; keep <stdbool.h>'s macro of
+ * the same name out of the way while the declarations are generated. */
+#pragma push_macro("bool")
+#undef bool
+#endif
+
+/* Element types as they appear in pointer arguments.  When the library itself is built
+ * the 16-bit float pointers are the CUDA vector types; callers see uint16_t. */
+#ifdef MAIDENX_CUDA_BUILD
+typedef __nv_bfloat16 mx_bf16;
+typedef __half mx_f16;
+#else
+typedef uint16_t mx_bf16;
+typedef uint16_t mx_f16;
+#endif
+typedef float mx_f32;
+typedef double mx_f64;
+typedef uint8_t mx_u8;
+typedef uint16_t mx_u16;
+typedef uint32_t mx_u32;
+typedef uint64_t mx_u64;
+typedef int8_t mx_i8;
+typedef int16_t mx_i16;
+typedef int32_t mx_i32;
+typedef int64_t mx_i64;
+/* By-value scalar arguments: 16-bit floats are passed as their bit pattern. */
+typedef uint16_t mx_bf16_arg;
+typedef uint16_t mx_f16_arg;
+typedef float mx_f32_arg;
+typedef double mx_f64_arg;
+typedef mx_bool mx_bool_arg;
+typedef uint8_t mx_u8_arg;
+typedef uint16_t mx_u16_arg;
+typedef uint32_t mx_u32_arg;
+typedef uint64_t mx_u64_arg;
+typedef int8_t mx_i8_arg;
+typedef int16_t mx_i16_arg;
+typedef int32_t mx_i32_arg;
+typedef int64_t mx_i64_arg;
+
+/* ---- dtype lists (X-macros: X(suffix, ...)) ------------------------------------------ */
+#define MX_DTYPES_FLOAT(X, ...) X(bf16, __VA_ARGS__) X(f16, __VA_ARGS__) X(f32, __VA_ARGS__) X(f64, __VA_ARGS__)
+#define MX_DTYPES_UINT(X, ...) X(u8, __VA_ARGS__) X(u16, __VA_ARGS__) X(u32, __VA_ARGS__) X(u64, __VA_ARGS__)
+#define MX_DTYPES_SINT(X, ...) X(i8, __VA_ARGS__) X(i16, __VA_ARGS__) X(i32, __VA_ARGS__) X(i64, __VA_ARGS__)
+#define MX_DTYPES_SIGNED(X, ...) MX_DTYPES_FLOAT(X, __VA_ARGS__) MX_DTYPES_SINT(X, __VA_ARGS__)
+#define MX_DTYPES_ARITH(X, ...) MX_DTYPES_FLOAT(X, __VA_ARGS__) MX_DTYPES_UINT(X, __VA_ARGS__) MX_DTYPES_SINT(X, __VA_ARGS__)
+#define MX_DTYPES_ALL(X, ...) MX_DTYPES_ARITH(X, __VA_ARGS__) X(bool, __VA_ARGS__)
+
+/* ======================================================================================
+ * Runtime wrappers — replace crates/maidenx_cuda/src/lib.rs:38-163 (`#[no_mangle] extern "C"`,
+ * each returns the cudaError_t as int).  cuda_memcpy_h2d additionally records small uploads
+ * so that metadata blocks can be resolved on the host; cuda_free forgets them.
+ * ====================================================================================== */
+typedef struct MxCudaPointerAttributes { /* lib.rs:23-29 */
+    int type_;
+    int device;
+    void* devicePointer;
+    void* hostPointer;
+} MxCudaPointerAttributes;
+
+int cuda_malloc(void** ptr, size_t size);                       /* lib.rs:38-41 */
+int cuda_free(void* ptr);                                       /* lib.rs:47-50 */
+int cuda_memcpy_h2d(void* dst, const void* src, size_t size);   /* lib.rs:58-61 */
+int cuda_memcpy_d2h(void* dst, const void* src, size_t size);   /* lib.rs:69-72 */
+int cuda_memcpy_d2d(void* dst, const void* src, size_t size);   /* lib.rs:80-83 */
+int cuda_set_device(int device_id);                             /* lib.rs:107-110 */
+int cuda_get_device(int* device_id);                            /* lib.rs:116-119 */
+int cuda_stream_create(void** stream);                          /* lib.rs:125-128 */
+int cuda_stream_destroy(void* stream);                          /* lib.rs:134-137 */
+int cuda_stream_synchronize(void* stream);                      /* lib.rs:143-146 */
+int cuda_pointer_get_attributes(MxCudaPointerAttributes* attributes, const void* ptr); /* lib.rs:153-163 */
+const char* cuda_error_string(int error_code);                  /* C twin of the Rust-ABI cuda_error, lib.rs:90-100 */
+
+/* ======================================================================================
+ * Binary elementwise — replace crates/maidenx_cuda/src/ops/binary.rs:6-182
+ * (kernels: crates/maidenx_cuda/kernels/ops/binary.cu:13-163; semantics follow the CPU
+ * backend, crates/maidenx_cpu/src/ops/binary.rs:13-934).
+ *   metadata = [dims(n) | lhs_strides(n) | rhs_strides(n) | lhs_offset, rhs_offset], or NULL
+ *   out[i] = op(lhs[lhs_offset + idx_l(i)], rhs[rhs_offset + idx_r(i)])
+ *   in-place: lhs[lhs_offset + idx_l(i)] = op(lhs[...], rhs[...])
+ * dtype sets are the ones maidenx_core dispatches (crates/maidenx_core/src/be/ops/binary.rs:245-310).
+ * ====================================================================================== */
+#define MX_BINARY_ARITH_OPS(X, ...) X(add, __VA_ARGS__) X(sub, __VA_ARGS__) X(mul, __VA_ARGS__) X(div, __VA_ARGS__) X(maximum, __VA_ARGS__) X(minimum, __VA_ARGS__)
+#define MX_BINARY_BOOL_OPS(X, ...) X(logical_and, __VA_ARGS__) X(logical_or, __VA_ARGS__) X(logical_xor, __VA_ARGS__) \
+    X(eq, __VA_ARGS__) X(ne, __VA_ARGS__) X(lt, __VA_ARGS__) X(le, __VA_ARGS__) X(gt, __VA_ARGS__) X(ge, __VA_ARGS__)
+#define MX_BINARY_INPLACE_OPS(X, ...) X(add_inplace, __VA_ARGS__) X(sub_inplace, __VA_ARGS__) X(mul_inplace, __VA_ARGS__) X(div_inplace, __VA_ARGS__)
+
+#define MX_DECL_BINARY(op, T) void cuda_##op##_##T(size_t num_els, size_t num_dims, const size_t* metadata, const mx_##T* lhs, const mx_##T* rhs, mx_##T* out);
+#define MX_DECL_BINARY_BOOL(op, T) void cuda_##op##_##T(size_t num_els, size_t num_dims, const size_t* metadata, const mx_##T* lhs, const mx_##T* rhs, mx_bool* out);
+#define MX_DECL_BINARY_INPLACE(op, T) void cuda_##op##_##T(size_t num_els, size_t num_dims, const size_t* metadata, mx_##T* lhs, const mx_##T* rhs);
+#define MX_DECL_BINARY_T(T, ...) MX_BINARY_ARITH_OPS(MX_DECL_BINARY, T) MX_BINARY_INPLACE_OPS(MX_DECL_BINARY_INPLACE, T)
+#define MX_DECL_BINARY_BOOL_T(T, ...) MX_BINARY_BOOL_OPS(MX_DECL_BINARY_BOOL, T)
+MX_DTYPES_ARITH(MX_DECL_BINARY_T, _)
+MX_DTYPES_ALL(MX_DECL_BINARY_BOOL_T, _)
+
+/* ======================================================================================
+ * Unary elementwise — replace crates/maidenx_cuda/src/ops/unary.rs:6-192
+ * (kernels: crates/maidenx_cuda/kernels/ops/unary.cu:9-88; CPU semantics:
+ * crates/maidenx_cpu/src/ops/unary.rs:14-741).
+ *   metadata = [dims(n) | strides(n) | offset], or NULL;  out[i] = op(in[offset + idx(i)][, constant])
+ *   input == NULL means "read from out".
+ * dtype sets: crates/maidenx_core/src/be/ops/unary.rs:486-526.
+ * ====================================================================================== */
+#define MX_UNARY_FLOAT_OPS(X, ...) X(relu, __VA_ARGS__) X(sigmoid, __VA_ARGS__) X(tanh, __VA_ARGS__) X(gelu, __VA_ARGS__) X(sin, __VA_ARGS__) \
+    X(cos, __VA_ARGS__) X(tan, __VA_ARGS__) X(ln, __VA_ARGS__) X(log10, __VA_ARGS__) X(log2, __VA_ARGS__) X(exp, __VA_ARGS__)                \
+    X(exp10, __VA_ARGS__) X(exp2, __VA_ARGS__) X(softplus, __VA_ARGS__) X(recip, __VA_ARGS__)
+#define MX_UNARY_SIGNED_OPS(X, ...) X(neg, __VA_ARGS__) X(abs, __VA_ARGS__)
+#define MX_UNARY_ARITH_OPS(X, ...) X(sign, __VA_ARGS__) X(square, __VA_ARGS__) X(sqrt, __VA_ARGS__)
+#define MX_UNARY_CONST_ARITH_OPS(X, ...) X(add_scalar, __VA_ARGS__) X(sub_scalar, __VA_ARGS__) X(mul_scalar, __VA_ARGS__) X(div_scalar, __VA_ARGS__) \
+    X(maximum_scalar, __VA_ARGS__) X(minimum_scalar, __VA_ARGS__) X(pow, __VA_ARGS__)
+#define MX_UNARY_CONST_FLOAT_OPS(X, ...) X(leaky_relu, __VA_ARGS__) X(elu, __VA_ARGS__)
+#define MX_UNARY_CONST_BOOL_OPS(X, ...) X(eq_scalar, __VA_ARGS__) X(ne_scalar, __VA_ARGS__) X(lt_scalar, __VA_ARGS__) X(le_scalar, __VA_ARGS__) \
+    X(gt_scalar, __VA_ARGS__) X(ge_scalar, __VA_ARGS__)
+
+#define MX_DECL_UNARY(op, T) void cuda_##op##_##T(size_t num_els, size_t num_dims, const size_t* metadata, const mx_##T* input, mx_##T* output);
+#define MX_DECL_UNARY_BOOL(op, T) void cuda_##op##_##T(size_t num_els, size_t num_dims, const size_t* metadata, const mx_##T* input, mx_bool* output);
+#define MX_DECL_UNARY_CONST(op, T) void cuda_##op##_##T(size_t num_els, size_t num_dims, const size_t* metadata, const mx_##T* input, mx_##T##_arg constant, mx_##T* output);
+#define MX_DECL_UNARY_CONST_BOOL(op, T) void cuda_##op##_##T(size_t num_els, size_t num_dims, const size_t* metadata, const mx_##T* input, mx_##T##_arg constant, mx_bool* output);
+#define MX_DECL_UNARY_FLOAT_T(T, ...) MX_UNARY_FLOAT_OPS(MX_DECL_UNARY, T) MX_UNARY_CONST_FLOAT_OPS(MX_DECL_UNARY_CONST, T)
+#define MX_DECL_UNARY_SIGNED_T(T, ...) MX_UNARY_SIGNED_OPS(MX_DECL_UNARY, T)
+#define MX_DECL_UNARY_ARITH_T(T, ...) MX_UNARY_ARITH_OPS(MX_DECL_UNARY, T) MX_UNARY_CONST_ARITH_OPS(MX_DECL_UNARY_CONST, T)
+#define MX_DECL_UNARY_ALL_T(T, ...) MX_DECL_UNARY_BOOL(logical_not, T) MX_UNARY_CONST_BOOL_OPS(MX_DECL_UNARY_CONST_BOOL, T)
+MX_DTYPES_FLOAT(MX_DECL_UNARY_FLOAT_T, _)
+MX_DTYPES_SIGNED(MX_DECL_UNARY_SIGNED_T, _)
+MX_DTYPES_ARITH(MX_DECL_UNARY_ARITH_T, _)
+MX_DTYPES_ALL(MX_DECL_UNARY_ALL_T, _)
+
+/* ======================================================================================
+ * Reductions — replace crates/maidenx_cuda/src/ops/reduction.rs:6-104
+ * (kernels: crates/maidenx_cuda/kernels/ops/reduction.cu:18-167,243-419; CPU semantics:
+ * crates/maidenx_cpu/src/ops/reduction.rs:6-272,383-625).
+ *   sum/mean/max/min: metadata = [dims(n) | strides(n) | red_len(r) | red_stride(r) | offset]
+ *   sum_to_shape:     metadata = [in_dims(n) | in_strides(n) | out_dims(n) | offset]
+ * The output is overwritten (no pre-zero contract); results are deterministic.
+ * dtype sets: crates/maidenx_core/src/be/ops/reduction.rs:251-256.
+ * ====================================================================================== */
+#define MX_DECL_REDUCE(op, T) void cuda_##op##_##T(size_t num_els, size_t num_dims, size_t num_red_dims, const size_t* metadata, const mx_##T* inp, mx_##T* out);
+#define MX_DECL_REDUCE_ARITH_T(T, ...) MX_DECL_REDUCE(sum, T) MX_DECL_REDUCE(max, T) MX_DECL_REDUCE(min, T) \
+    void cuda_sum_to_shape_##T(size_t num_els, size_t num_dims, const size_t* metadata, const mx_##T* inp, mx_##T* out);
+#define MX_DECL_REDUCE_FLOAT_T(T, ...) MX_DECL_REDUCE(mean, T)
+MX_DTYPES_ARITH(MX_DECL_REDUCE_ARITH_T, _)
+MX_DTYPES_FLOAT(MX_DECL_REDUCE_FLOAT_T, _)
+
+/* ======================================================================================
+ * Matmul — replace crates/maidenx_cuda/src/ops/matmul.rs:6-50
+ * (kernels: crates/maidenx_cuda/kernels/ops/matmul.cu:5-179; CPU semantics:
+ * crates/maidenx_cpu/src/ops/matmul.rs:5-268).
+ *   metadata = [out_ndim, a_ndim, b_ndim | out_shape | a_shape | b_shape | a_strides | b_strides | a_off, b_off]
+ *   matmul:          C[b,m,n] = sum_k A[b,m,k] * B[b,k,n], C contiguous, num_els = batch*M*N
+ *   matmul_backward: grad_a = g * B^T, grad_b = A^T * g with A, B, g read as contiguous
+ *                    (strides ignored, offsets applied); either output may be NULL.
+ * dtype set: crates/maidenx_core/src/be/ops/matmul.rs:265.
+ * ====================================================================================== */
+#define MX_DECL_MATMUL_T(T, ...)                                                                                                       \
+    void cuda_matmul_##T(size_t num_els, const size_t* metadata, const mx_##T* a, const mx_##T* b, mx_##T* c);                        \
+    void cuda_matmul_backward_##T(size_t num_els_a, size_t num_els_b, const size_t* metadata, const mx_##T* grad_output,               \
+                                  const mx_##T* a, const mx_##T* b, mx_##T* grad_a, mx_##T* grad_b);
+MX_DTYPES_ARITH(MX_DECL_MATMUL_T, _)
+
+/* ======================================================================================
+ * Conv2d helpers — replace crates/maidenx_cuda/src/nn/conv.rs:6-36
+ * (kernels: crates/maidenx_cuda/kernels/nn/conv.cu:8-136; CPU semantics:
+ * crates/maidenx_cpu/src/nn/conv.rs:13-149).
+ *   metadata = [B, C, H, W, kh, kw, out_h, out_w, pad_h, pad_w, stride_h, stride_w]
+ *   im2col: col[b][c,kh,kw][oh,ow] = x[b,c,oh*s-p+kh,ow*s-p+kw] or 0; num_els = col length
+ *   col2im: every (b,c,h,w) is overwritten with the sum of the col entries mapping to it;
+ *           num_els = readable length of col (entries beyond it are skipped).
+ * dtype set: crates/maidenx_core/src/be/nn/conv.rs:240.
+ * ====================================================================================== */
+#define MX_DECL_CONV_T(T, ...)                                                                                     \
+    void cuda_conv2d_im2col_##T(size_t num_els, const size_t* metadata, const mx_##T* input, mx_##T* col);        \
+    void cuda_conv2d_col2im_##T(size_t num_els, const size_t* metadata, const mx_##T* col, mx_##T* output);
+MX_DTYPES_FLOAT(MX_DECL_CONV_T, _)
+
+/* ======================================================================================
+ * Additive exports (no counterpart in the reference).
+ * ====================================================================================== */
+/* Stream used by this thread's subsequent op launches (NULL = legacy default stream). */
+void mx_set_stream(void* stream);
+void* mx_get_stream(void);
+/* Sticky per-thread status: 0 = ok, 1 = CUDA error (see mx_last_cuda_error), 2 = bad metadata,
+ * 3 = unsupported shape, 4 = no device, 5 = a bounded device-side wait ran out. */
+int mx_last_error(void);
+int mx_last_cuda_error(void);
+const char* mx_last_error_where(void);
+void mx_clear_error(void);
+int mx_device_synchronize(void);
+/* Number of metadata blocks currently remembered by cuda_memcpy_h2d (diagnostics). */
+int mx_metadata_table_size(void);
+
+#ifdef __cplusplus
+}
+#else
+#pragma pop_macro("bool")
+#endif
+#endif /* MAIDENX_CUDA_H */

@@ -1,0 +1,67 @@
+"""Loader of libmaidenx_cuda.so.  There is no fallback: without the built CUDA library
+every op call fails with an error that says how to build it."""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+from . import _signatures as sig
+
+LIB_PATH = Path(__file__).resolve().parent / "libmaidenx_cuda.so"
+
+_lib = None
+_ops = None
+
+RUNTIME_SIGNATURES = {
+    "cuda_malloc": ([ctypes.POINTER(ctypes.c_void_p), ctypes.c_size_t], ctypes.c_int),
+    "cuda_free": ([ctypes.c_void_p], ctypes.c_int),
+    "cuda_memcpy_h2d": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t], ctypes.c_int),
+    "cuda_memcpy_d2h": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t], ctypes.c_int),
+    "cuda_memcpy_d2d": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t], ctypes.c_int),
+    "cuda_set_device": ([ctypes.c_int], ctypes.c_int),
+    "cuda_get_device": ([ctypes.POINTER(ctypes.c_int)], ctypes.c_int),
+    "cuda_stream_create": ([ctypes.POINTER(ctypes.c_void_p)], ctypes.c_int),
+    "cuda_stream_destroy": ([ctypes.c_void_p], ctypes.c_int),
+    "cuda_stream_synchronize": ([ctypes.c_void_p], ctypes.c_int),
+    "cuda_pointer_get_attributes": ([ctypes.c_void_p, ctypes.c_void_p], ctypes.c_int),
+    "cuda_error_string": ([ctypes.c_int], ctypes.c_char_p),
+    "mx_set_stream": ([ctypes.c_void_p], None),
+    "mx_get_stream": ([], ctypes.c_void_p),
+    "mx_last_error": ([], ctypes.c_int),
+    "mx_last_cuda_error": ([], ctypes.c_int),
+    "mx_last_error_where": ([], ctypes.c_char_p),
+    "mx_clear_error": ([], None),
+    "mx_device_synchronize": ([], ctypes.c_int),
+    "mx_metadata_table_size": ([], ctypes.c_int),
+}
+
+
+class LibraryMissing(RuntimeError):
+    pass
+
+
+def load() -> ctypes.CDLL:
+    global _lib, _ops
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise LibraryMissing(
+            f"{LIB_PATH} is not built; run `python -m maidenx_b200.build` (needs nvcc). "
+            "The op layer has no CPU or PyTorch fallback.")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (args, res) in RUNTIME_SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = res
+    _ops = sig.bind(lib, "cuda_")
+    _lib = lib
+    return lib
+
+
+def op(name: str, dtype_name: str):
+    """The `cuda_<name>_<dtype>` entry point."""
+    load()
+    try:
+        return _ops[(name, dtype_name)]
+    except KeyError:
+        raise KeyError(f"cuda_{name}_{dtype_name} is not part of the op layer") from None

@@ -1,0 +1,358 @@
+// Strided elementwise engine shared by the binary, in-place binary, unary and
+// unary-with-constant families.
+//
+// The host reduces the (dims, strides, offsets) metadata of the C ABI to a canonical
+// form — size-1 dims dropped, adjacent dims merged wherever every operand allows it —
+// and picks one of four kernels:
+//   flat     every operand is one contiguous run (or a broadcast scalar): 16-byte
+//            vector loads/stores, four vectors in flight per thread;
+//   row      every operand has stride 1 or 0 along the innermost dim; outer dims are
+//            arbitrary (row-vector / column-vector broadcasts, padded rows): one
+//            fast-divmod per 16-byte vector instead of per element;
+//   tile     an input is unit-stride along another dim (a transposed view): 64x64
+//            tiles staged through shared memory so both the transposed read and the
+//            output write are full 128-byte lines;
+//   generic  anything else (also misaligned bases): per-element fast-divmod gather.
+// In-place ops reuse the same kernels with the output aliased to the lhs and the dims
+// re-ordered by the lhs strides; an lhs that overlaps itself (stride 0) runs serially
+// on one thread, which is the order the CPU backend applies.
+#pragma once
+#include "common.cuh"
+#include "ops.cuh"
+
+namespace mx {
+
+enum EwKind { EW_EMPTY = 0, EW_FLAT, EW_ROW, EW_TILE, EW_GENERIC, EW_SERIAL, EW_ERROR };
+
+struct EwPlan {
+    int kind;
+    int nin;
+    uint64_t n;
+    int nd;
+    uint32_t dim[kMaxDims];
+    int64_t st[3][kMaxDims];  // element strides: 0 = out, 1 = a, 2 = b
+    int64_t off[3];           // element offsets applied to the base pointers
+    int p;                    // tile: the dim along which the transposed inputs are unit-stride
+    bool transposed[3];       // tile: operand is read through shared memory
+    bool vec;                 // 16-byte vector access is legal for every operand
+};
+
+// in_size / out_size: element sizes in bytes; ptrs: base addresses (out, a, b) before offsets.
+void ew_make_plan(EwPlan& pl, size_t num_els, size_t num_dims, const size_t* hmeta, int nin, bool inplace, size_t in_size,
+                  size_t out_size, const void* out, const void* a, const void* b);
+
+// ---------------------------------------------------------------------------------
+// kernels
+// ---------------------------------------------------------------------------------
+constexpr int kEwThreads = 256;
+constexpr int kEwUnroll = 4;
+
+template <class T, int N>
+__device__ __forceinline__ Vec<T, N> ld_vec(const T* p) {
+    return *reinterpret_cast<const Vec<T, N>*>(p);
+}
+template <class T, int N>
+__device__ __forceinline__ void st_vec(T* p, const Vec<T, N>& v) {
+    *reinterpret_cast<Vec<T, N>*>(p) = v;
+}
+template <class T, int N>
+__device__ __forceinline__ Vec<T, N> splat(T x) {
+    Vec<T, N> v;
+#pragma unroll
+    for (int i = 0; i < N; i++) v.v[i] = x;
+    return v;
+}
+
+template <class F, class T, class O, int NIN, int VEC>
+__device__ __forceinline__ Vec<O, VEC> apply_vec(const F& f, const Vec<T, VEC>& a, const Vec<T, VEC>& b) {
+    Vec<O, VEC> r;
+#pragma unroll
+    for (int i = 0; i < VEC; i++) {
+        if constexpr (NIN == 2) r.v[i] = f(a.v[i], b.v[i]);
+        else r.v[i] = f(a.v[i]);
+    }
+    return r;
+}
+
+// sa / sb: 1 = contiguous, 0 = broadcast scalar
+template <class F, class T, class O, int NIN, int VEC>
+__global__ void __launch_bounds__(kEwThreads) ew_flat_kernel(F f, const T* a, const T* b, O* out, uint64_t n, int sa, int sb) {
+    constexpr uint64_t kChunk = (uint64_t)kEwThreads * VEC * kEwUnroll;
+    const uint64_t base = (uint64_t)blockIdx.x * kChunk;
+    if (base + kChunk <= n) {
+        Vec<T, VEC> va[kEwUnroll], vb[kEwUnroll];
+#pragma unroll
+        for (int u = 0; u < kEwUnroll; u++) {
+            uint64_t i = base + ((uint64_t)u * kEwThreads + threadIdx.x) * VEC;
+            va[u] = sa ? ld_vec<T, VEC>(a + i) : splat<T, VEC>(a[0]);
+            if constexpr (NIN == 2) vb[u] = sb ? ld_vec<T, VEC>(b + i) : splat<T, VEC>(b[0]);
+        }
+#pragma unroll
+        for (int u = 0; u < kEwUnroll; u++) {
+            uint64_t i = base + ((uint64_t)u * kEwThreads + threadIdx.x) * VEC;
+            st_vec<O, VEC>(out + i, apply_vec<F, T, O, NIN, VEC>(f, va[u], vb[u]));
+        }
+    } else {
+        for (uint64_t i = base + threadIdx.x; i < n; i += kEwThreads) {
+            T x = a[sa ? i : 0];
+            if constexpr (NIN == 2) out[i] = f(x, b[sb ? i : 0]);
+            else out[i] = f(x);
+        }
+    }
+}
+
+struct EwRowParams {
+    int nd_outer;
+    uint32_t total_vecs;
+    FastDiv qv_div;                 // vectors per row
+    FastDiv outer_div[kMaxDims];    // outer dims, innermost outer dim last
+    int64_t st[3][kMaxDims];        // outer strides per operand
+    int sq[3];                      // stride along q per operand (1 or 0)
+};
+
+template <class F, class T, class O, int NIN, int VEC>
+__global__ void __launch_bounds__(kEwThreads) ew_row_kernel(F f, const T* a, const T* b, O* out, EwRowParams P) {
+    const uint32_t base = blockIdx.x * (kEwThreads * kEwUnroll);
+    Vec<T, VEC> va[kEwUnroll], vb[kEwUnroll];
+    int64_t oo[kEwUnroll];
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; u++) {
+        uint32_t v = base + u * kEwThreads + threadIdx.x;
+        oo[u] = -1;
+        if (v < P.total_vecs) {
+            uint32_t r, qv;
+            P.qv_div.divmod(v, r, qv);
+            int64_t o_out = (int64_t)qv * VEC, o_a = (int64_t)qv * VEC * P.sq[1], o_b = (int64_t)qv * VEC * P.sq[2];
+            for (int d = P.nd_outer - 1; d >= 0; d--) {
+                uint32_t c;
+                P.outer_div[d].divmod(r, r, c);
+                o_out += (int64_t)c * P.st[0][d];
+                o_a += (int64_t)c * P.st[1][d];
+                if constexpr (NIN == 2) o_b += (int64_t)c * P.st[2][d];
+            }
+            oo[u] = o_out;
+            va[u] = P.sq[1] ? ld_vec<T, VEC>(a + o_a) : splat<T, VEC>(a[o_a]);
+            if constexpr (NIN == 2) vb[u] = P.sq[2] ? ld_vec<T, VEC>(b + o_b) : splat<T, VEC>(b[o_b]);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; u++)
+        if (oo[u] >= 0) st_vec<O, VEC>(out + oo[u], apply_vec<F, T, O, NIN, VEC>(f, va[u], vb[u]));
+}
+
+struct EwTileParams {
+    uint32_t P, Q;                  // extents of the tiled dims
+    uint32_t tiles_p, tiles_q;
+    FastDiv tiles_q_div, tiles_p_div;
+    int nd_batch;
+    FastDiv batch_div[kMaxDims];
+    int64_t st_batch[3][kMaxDims];
+    int64_t st_p[3], st_q[3];
+    int transposed[3];              // [1], [2]: input goes through shared memory
+};
+
+template <class T>
+struct EwTile {
+    static constexpr int kTile = sizeof(T) == 8 ? 32 : 64;
+    static constexpr int kPitch = kTile * (int)sizeof(T) + (sizeof(T) == 8 ? 8 : 4);  // bytes per staged row
+};
+
+template <class F, class T, class O, int NIN, int VEC>
+__global__ void __launch_bounds__(kEwThreads) ew_tile_kernel(F f, const T* a, const T* b, O* out, EwTileParams P) {
+    constexpr int TILE = EwTile<T>::kTile;
+    constexpr int PITCH = EwTile<T>::kPitch;
+    constexpr int VPR = TILE / VEC;  // vectors per tile row
+    __shared__ __align__(16) unsigned char smem[NIN][TILE * PITCH];
+
+    uint32_t t = blockIdx.x, tq, tp, bidx;
+    P.tiles_q_div.divmod(t, t, tq);
+    P.tiles_p_div.divmod(t, bidx, tp);
+    int64_t base[3] = {0, 0, 0};
+    for (int d = P.nd_batch - 1; d >= 0; d--) {
+        uint32_t c;
+        P.batch_div[d].divmod(bidx, bidx, c);
+#pragma unroll
+        for (int k = 0; k < 3; k++) base[k] += (int64_t)c * P.st_batch[k][d];
+    }
+    const uint32_t p0 = tp * TILE, q0 = tq * TILE;
+#pragma unroll
+    for (int k = 0; k < 3; k++) base[k] += (int64_t)p0 * P.st_p[k] + (int64_t)q0 * P.st_q[k];
+    const T* in[2] = {a, b};
+
+    // phase 1: transposed inputs, read along p (their unit-stride dim), staged as [q][p]
+#pragma unroll
+    for (int x = 0; x < NIN; x++) {
+        if (!P.transposed[x + 1]) continue;
+        const T* src = in[x] + base[x + 1];
+        for (int i = threadIdx.x; i < TILE * VPR; i += kEwThreads) {
+            int qq = i / VPR, pv = i % VPR;
+            if (q0 + qq < P.Q && p0 + pv * VEC < P.P) {
+                Vec<T, VEC> v = ld_vec<T, VEC>(src + (int64_t)qq * P.st_q[x + 1] + pv * VEC);
+                unsigned char* row = smem[x] + qq * PITCH + pv * VEC * (int)sizeof(T);
+                if constexpr (VEC * sizeof(T) >= 4 && sizeof(T) < 4) {
+                    const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+                    for (int j = 0; j < (int)(VEC * sizeof(T) / 4); j++) reinterpret_cast<uint32_t*>(row)[j] = w[j];
+                } else {
+#pragma unroll
+                    for (int j = 0; j < VEC; j++) reinterpret_cast<T*>(row)[j] = v.v[j];
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    // phase 2: walk the tile along q (the output's unit-stride dim)
+    for (int i = threadIdx.x; i < TILE * VPR; i += kEwThreads) {
+        int pp = i / VPR, qv = i % VPR;
+        if (p0 + pp >= P.P || q0 + qv * VEC >= P.Q) continue;
+        Vec<T, VEC> v[2];
+#pragma unroll
+        for (int x = 0; x < NIN; x++) {
+            if (P.transposed[x + 1]) {
+#pragma unroll
+                for (int j = 0; j < VEC; j++)
+                    v[x].v[j] = *reinterpret_cast<const T*>(smem[x] + (qv * VEC + j) * PITCH + pp * (int)sizeof(T));
+            } else {
+                const T* src = in[x] + base[x + 1] + (int64_t)pp * P.st_p[x + 1];
+                v[x] = P.st_q[x + 1] ? ld_vec<T, VEC>(src + qv * VEC) : splat<T, VEC>(src[0]);
+            }
+        }
+        st_vec<O, VEC>(out + base[0] + (int64_t)pp * P.st_p[0] + qv * VEC, apply_vec<F, T, O, NIN, VEC>(f, v[0], v[1]));
+    }
+}
+
+struct EwGenParams {
+    int nd;
+    uint64_t n;
+    uint32_t dim[kMaxDims];
+    FastDiv div[kMaxDims];
+    int64_t st[3][kMaxDims];
+};
+
+template <class F, class T, class O, int NIN>
+__global__ void __launch_bounds__(kEwThreads) ew_generic_kernel(F f, const T* a, const T* b, O* out, EwGenParams P) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < P.n; i += stride) {
+        int64_t o0 = 0, o1 = 0, o2 = 0;
+        if (P.n <= 0xFFFFFFFFull) {
+            uint32_t r = (uint32_t)i;
+            for (int d = P.nd - 1; d >= 0; d--) {
+                uint32_t c;
+                P.div[d].divmod(r, r, c);
+                o0 += (int64_t)c * P.st[0][d];
+                o1 += (int64_t)c * P.st[1][d];
+                if constexpr (NIN == 2) o2 += (int64_t)c * P.st[2][d];
+            }
+        } else {
+            uint64_t r = i;
+            for (int d = P.nd - 1; d >= 0; d--) {
+                uint64_t c = r % P.dim[d];
+                r /= P.dim[d];
+                o0 += (int64_t)c * P.st[0][d];
+                o1 += (int64_t)c * P.st[1][d];
+                if constexpr (NIN == 2) o2 += (int64_t)c * P.st[2][d];
+            }
+        }
+        if constexpr (NIN == 2) out[o0] = f(a[o1], b[o2]);
+        else out[o0] = f(a[o1]);
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// launcher
+// ---------------------------------------------------------------------------------
+void ew_fill_row_params(const EwPlan& pl, int vec, EwRowParams& P);
+void ew_fill_tile_params(const EwPlan& pl, int tile, EwTileParams& P, uint32_t& blocks);
+void ew_fill_gen_params(const EwPlan& pl, EwGenParams& P);
+
+template <class F, class T, class O, int NIN>
+void ew_launch(const EwPlan& pl, const F& f, const T* a, const T* b, O* out, const char* where) {
+    constexpr int VEC = 16 / sizeof(T);
+    cudaStream_t s = ctx().stream;
+    a += pl.off[1];
+    if (NIN == 2) b += pl.off[2];
+    out += pl.off[0];
+    switch (pl.kind) {
+        case EW_EMPTY:
+            return;
+        case EW_FLAT: {
+            uint64_t chunk = (uint64_t)kEwThreads * VEC * kEwUnroll;
+            uint64_t blocks = (pl.n + chunk - 1) / chunk;
+            if (blocks > 0x7FFFFFFFull) {
+                set_error(kErrUnsupported, 0, where);
+                return;
+            }
+            ew_flat_kernel<F, T, O, NIN, VEC><<<(uint32_t)blocks, kEwThreads, 0, s>>>(f, a, b, out, pl.n, (int)pl.st[1][0], NIN == 2 ? (int)pl.st[2][0] : 0);
+            break;
+        }
+        case EW_ROW: {
+            EwRowParams P;
+            ew_fill_row_params(pl, VEC, P);
+            uint32_t blocks = ceil_div_u32(P.total_vecs, kEwThreads * kEwUnroll);
+            ew_row_kernel<F, T, O, NIN, VEC><<<blocks, kEwThreads, 0, s>>>(f, a, b, out, P);
+            break;
+        }
+        case EW_TILE: {
+            EwTileParams P;
+            uint32_t blocks;
+            ew_fill_tile_params(pl, EwTile<T>::kTile, P, blocks);
+            if (pl.vec) ew_tile_kernel<F, T, O, NIN, VEC><<<blocks, kEwThreads, 0, s>>>(f, a, b, out, P);
+            else ew_tile_kernel<F, T, O, NIN, 1><<<blocks, kEwThreads, 0, s>>>(f, a, b, out, P);
+            break;
+        }
+        case EW_GENERIC:
+        case EW_SERIAL: {
+            EwGenParams P;
+            ew_fill_gen_params(pl, P);
+            if (pl.kind == EW_SERIAL) {
+                ew_generic_kernel<F, T, O, NIN><<<1, 1, 0, s>>>(f, a, b, out, P);
+            } else {
+                uint64_t blocks = (pl.n + kEwThreads - 1) / kEwThreads;
+                uint64_t cap = (uint64_t)sm_count() * 32;
+                if (blocks > cap) blocks = cap;
+                ew_generic_kernel<F, T, O, NIN><<<(uint32_t)blocks, kEwThreads, 0, s>>>(f, a, b, out, P);
+            }
+            break;
+        }
+        default:
+            set_error(kErrBadMetadata, 0, where);
+            return;
+    }
+    check_launch(where);
+}
+
+// Entry points used by the C-ABI wrappers.  `meta` is the pointer the caller passed
+// (device or host memory, or NULL for "contiguous, no offsets").
+template <class Op, class T, class O>
+void binary_entry(size_t n, size_t nd, const size_t* meta, const T* lhs, const T* rhs, O* out, bool inplace, const char* where) {
+    const size_t* hm = meta ? resolve_metadata(meta, 3 * nd + 2) : nullptr;
+    if (meta && !hm) return;
+    EwPlan pl;
+    ew_make_plan(pl, n, nd, hm, 2, inplace, sizeof(T), sizeof(O), out, lhs, rhs);
+    ew_launch<Binary<Op, T, O>, T, O, 2>(pl, Binary<Op, T, O>(), lhs, rhs, out, where);
+}
+template <class Op, class T, class O>
+void unary_entry(size_t n, size_t nd, const size_t* meta, const T* in, O* out, const char* where) {
+    const size_t* hm = meta ? resolve_metadata(meta, 2 * nd + 1) : nullptr;
+    if (meta && !hm) return;
+    // The reference accepts input == NULL as "read from the output buffer"; that is
+    // only meaningful when input and output have the same element type.
+    if (!in) in = reinterpret_cast<const T*>(out);
+    EwPlan pl;
+    ew_make_plan(pl, n, nd, hm, 1, false, sizeof(T), sizeof(O), out, in, nullptr);
+    ew_launch<Unary<Op, T, O>, T, O, 1>(pl, Unary<Op, T, O>(), in, (const T*)nullptr, out, where);
+}
+template <class Op, class T, class O>
+void unary_const_entry(size_t n, size_t nd, const size_t* meta, const T* in, T c, O* out, const char* where) {
+    const size_t* hm = meta ? resolve_metadata(meta, 2 * nd + 1) : nullptr;
+    if (meta && !hm) return;
+    if (!in) in = reinterpret_cast<const T*>(out);
+    EwPlan pl;
+    ew_make_plan(pl, n, nd, hm, 1, false, sizeof(T), sizeof(O), out, in, nullptr);
+    UnaryConst<Op, T, O> f;
+    f.c = c;
+    ew_launch<UnaryConst<Op, T, O>, T, O, 1>(pl, f, in, (const T*)nullptr, out, where);
+}
+
+}  // namespace mx

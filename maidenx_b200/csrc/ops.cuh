@@ -1,0 +1,455 @@
+// Device functors for the elementwise families.  Semantics follow the CPU backend of
+// the reference (the parity target), not its CUDA kernels, where the two differ:
+// saturating integer add/sub/mul, defined division by zero, truncating integer sqrt,
+// 16-bit float math carried out in f32 and rounded once.
+//   binary lambdas:  crates/maidenx_cpu/src/ops/binary.rs:372-934
+//   unary lambdas:   crates/maidenx_cpu/src/ops/unary.rs:124-741
+#pragma once
+#include <cfloat>
+#include <climits>
+#include <cmath>
+#include <limits>
+
+#include "common.cuh"
+
+namespace mx {
+
+template <class T>
+__device__ __forceinline__ T zero_of() {
+    if constexpr (is_half_v<T>) return from_f32<T>(0.0f);
+    else return (T)0;
+}
+
+template <class T>
+struct Lim {
+    __device__ static constexpr T min() { return std::numeric_limits<T>::min(); }
+    __device__ static constexpr T max() { return std::numeric_limits<T>::max(); }
+};
+
+// float -> integer with saturation and NaN -> 0 (the CPU backend's `as` casts)
+template <class T, class F>
+__device__ __forceinline__ T sat_cast(F v) {
+    if (v != v) return (T)0;
+    const F lo = (F)Lim<T>::min();
+    // 2^(bits-1) (signed) or 2^bits (unsigned): exactly representable, unlike max()
+    const F half_range = (F)(1ull << (sizeof(T) * 8 - 1));
+    const F hi_excl = std::is_signed<T>::value ? half_range : half_range * (F)2;
+    if (v <= lo) return Lim<T>::min();
+    if (v >= hi_excl) return Lim<T>::max();
+    return (T)v;
+}
+
+template <class T>
+__device__ __forceinline__ T wrap_neg(T a) {
+    typedef typename std::make_unsigned<T>::type U;
+    return (T)(U)((U)0 - (U)a);
+}
+template <class T>
+__device__ __forceinline__ T wrap_abs(T a) {
+    return a < 0 ? wrap_neg(a) : a;
+}
+template <class T>
+__device__ __forceinline__ T wrap_mul(T a, T b) {
+    typedef typename std::make_unsigned<T>::type U;
+    return (T)(U)((u64)(U)a * (u64)(U)b);
+}
+template <class T>
+__device__ __forceinline__ T wrap_add(T a, T b) {
+    typedef typename std::make_unsigned<T>::type U;
+    return (T)(U)((U)a + (U)b);
+}
+
+template <class T>
+__device__ __forceinline__ T sat_add(T a, T b) {
+    if constexpr (sizeof(T) < 8) {
+        i64 r = (i64)a + (i64)b;
+        return r < (i64)Lim<T>::min() ? Lim<T>::min() : (r > (i64)Lim<T>::max() ? Lim<T>::max() : (T)r);
+    } else if constexpr (std::is_signed<T>::value) {
+        u64 r = (u64)a + (u64)b;
+        // overflow iff operands share a sign that the result does not
+        if ((((u64)a ^ r) & ((u64)b ^ r)) >> 63) return a < 0 ? Lim<T>::min() : Lim<T>::max();
+        return (T)r;
+    } else {
+        u64 r = a + b;
+        return r < a ? Lim<T>::max() : (T)r;
+    }
+}
+template <class T>
+__device__ __forceinline__ T sat_sub(T a, T b) {
+    if constexpr (sizeof(T) < 8) {
+        i64 r = (i64)a - (i64)b;
+        return r < (i64)Lim<T>::min() ? Lim<T>::min() : (r > (i64)Lim<T>::max() ? Lim<T>::max() : (T)r);
+    } else if constexpr (std::is_signed<T>::value) {
+        u64 r = (u64)a - (u64)b;
+        if ((((u64)a ^ (u64)b) & ((u64)a ^ r)) >> 63) return a < 0 ? Lim<T>::min() : Lim<T>::max();
+        return (T)r;
+    } else {
+        return a < b ? (T)0 : (T)(a - b);
+    }
+}
+template <class T>
+__device__ __forceinline__ T sat_mul(T a, T b) {
+    if constexpr (sizeof(T) < 4) {
+        i64 r = (i64)a * (i64)b;
+        return r < (i64)Lim<T>::min() ? Lim<T>::min() : (r > (i64)Lim<T>::max() ? Lim<T>::max() : (T)r);
+    } else if constexpr (sizeof(T) == 4) {
+        if constexpr (std::is_signed<T>::value) {
+            i64 r = (i64)a * (i64)b;
+            return r < (i64)INT_MIN ? INT_MIN : (r > (i64)INT_MAX ? INT_MAX : (T)r);
+        } else {
+            u64 r = (u64)a * (u64)b;
+            return r > 0xFFFFFFFFull ? 0xFFFFFFFFu : (T)r;
+        }
+    } else if constexpr (std::is_signed<T>::value) {
+        i64 hi = __mul64hi(a, b);
+        i64 lo = (i64)((u64)a * (u64)b);
+        if (hi != (lo >> 63)) return ((a < 0) != (b < 0)) ? Lim<T>::min() : Lim<T>::max();
+        return lo;
+    } else {
+        u64 hi = __umul64hi(a, b);
+        return hi ? Lim<T>::max() : (T)(a * b);
+    }
+}
+template <class T>
+__device__ __forceinline__ T sat_div(T a, T b) {  // b != 0
+    if constexpr (std::is_signed<T>::value) {
+        if (a == Lim<T>::min() && b == (T)-1) return Lim<T>::max();
+    }
+    return (T)(a / b);
+}
+
+// x^c for integers with the result the CPU backend produces by going through a
+// floating-point pow and a saturating cast: exact while the power fits the float
+// format, rounded to nearest double in [2^53, 2^64), saturated beyond.
+template <class T>
+__device__ __forceinline__ T int_pow(T x, T c) {
+    typedef typename std::make_unsigned<T>::type U;
+    bool neg_base = false, neg_exp = false;
+    u64 base, e;
+    if constexpr (std::is_signed<T>::value) {
+        neg_base = x < 0;
+        neg_exp = c < 0;
+        base = neg_base ? (u64)0 - (u64)(i64)x : (u64)x;
+        e = neg_exp ? (u64)0 - (u64)(i64)c : (u64)c;
+    } else {
+        base = (u64)x;
+        e = (u64)c;
+    }
+    bool odd = e & 1;
+    if (e == 0) return (T)1;  // pow(x, 0) == 1 for every x, NaN-free here
+    if (neg_exp) {
+        if (base == 0) return Lim<T>::max();              // pow(0, -n) = +inf
+        if (base == 1) return (neg_base && odd) ? (T)-1 : (T)1;
+        return (T)0;                                      // |result| < 1 truncates to 0
+    }
+    if (base == 0) return (T)0;
+    if (base == 1) return (neg_base && odd) ? (T)-1 : (T)1;
+    // base >= 2: at most 64 multiplications before overflowing 2^64
+    u64 r = 1;
+    bool overflow = false;
+    if (e > 64) overflow = true;
+    else
+        for (u64 i = 0; i < e; i++) {
+            if (__umul64hi(r, base)) {
+                overflow = true;
+                break;
+            }
+            r *= base;
+        }
+    bool negative = neg_base && odd;
+    if (overflow) return negative ? Lim<T>::min() : Lim<T>::max();
+    if constexpr (sizeof(T) == 8) {
+        f64 d = __ull2double_rn(r);
+        if (negative) d = -d;
+        return sat_cast<T, f64>(d);
+    } else {
+        if (negative) return r > (u64)1 << (sizeof(T) * 8 - 1) ? Lim<T>::min() : (T)(U)((u64)0 - r);
+        return r > (u64)Lim<T>::max() ? Lim<T>::max() : (T)r;
+    }
+}
+
+// ------------------------------------------------------------------ float helpers
+template <class T, class F32Fn, class F64Fn>
+__device__ __forceinline__ T fp_apply(T x, F32Fn f32fn, F64Fn f64fn) {
+    if constexpr (is_half_v<T>) return from_f32<T>(f32fn(to_f32(x)));
+    else if constexpr (std::is_same<T, f32>::value) return f32fn(x);
+    else return f64fn(x);
+}
+template <class T>
+__device__ __forceinline__ bool fgt(T a, T b) {
+    if constexpr (is_half_v<T>) return to_f32(a) > to_f32(b);
+    else return a > b;
+}
+template <class T>
+__device__ __forceinline__ bool flt(T a, T b) {
+    if constexpr (is_half_v<T>) return to_f32(a) < to_f32(b);
+    else return a < b;
+}
+template <class T>
+__device__ __forceinline__ bool feq(T a, T b) {
+    if constexpr (is_half_v<T>) return to_f32(a) == to_f32(b);
+    else return a == b;
+}
+template <class T>
+__device__ __forceinline__ bool truthy(T a) {
+    return !feq(a, zero_of<T>());
+}
+
+// ------------------------------------------------------------------ binary
+struct OpAdd {
+    template <class T>
+    __device__ static T f(T a, T b) {
+        if constexpr (is_bool_v<T>) return a | b;
+        else if constexpr (is_int_v<T>) return sat_add(a, b);
+        else if constexpr (is_half_v<T>) return from_f32<T>(to_f32(a) + to_f32(b));
+        else return a + b;
+    }
+};
+struct OpSub {
+    template <class T>
+    __device__ static T f(T a, T b) {
+        if constexpr (is_bool_v<T>) return a & b;
+        else if constexpr (is_int_v<T>) return sat_sub(a, b);
+        else if constexpr (is_half_v<T>) return from_f32<T>(to_f32(a) - to_f32(b));
+        else return a - b;
+    }
+};
+struct OpMul {
+    template <class T>
+    __device__ static T f(T a, T b) {
+        if constexpr (is_bool_v<T>) return a ^ b;
+        else if constexpr (is_int_v<T>) return sat_mul(a, b);
+        else if constexpr (is_half_v<T>) return from_f32<T>(to_f32(a) * to_f32(b));
+        else return a * b;
+    }
+};
+struct OpDiv {
+    template <class T>
+    __device__ static T f(T a, T b) {
+        if constexpr (is_bool_v<T>) return a & b;
+        else if constexpr (is_int_v<T>) {
+            if (b == 0) {
+                if (a == 0) return (T)0;
+                if constexpr (std::is_signed<T>::value) {
+                    if (a < 0) return Lim<T>::min();
+                }
+                return Lim<T>::max();
+            }
+            return sat_div(a, b);
+        } else if constexpr (is_half_v<T>) {
+            f32 x = to_f32(a), y = to_f32(b);
+            if (y == 0.0f) return from_f32<T>(x == 0.0f ? 0.0f : INFINITY);
+            return from_f32<T>(x / y);
+        } else {
+            if (b == (T)0) return a == (T)0 ? (T)0 : (T)INFINITY;
+            return a / b;
+        }
+    }
+};
+struct OpMax {
+    template <class T>
+    __device__ static T f(T a, T b) {
+        if constexpr (is_bool_v<T>) return a | b;
+        else if constexpr (std::is_same<T, f32>::value) return fmaxf(a, b);
+        else if constexpr (std::is_same<T, f64>::value) return fmax(a, b);
+        else return fgt(a, b) ? a : b;
+    }
+};
+struct OpMin {
+    template <class T>
+    __device__ static T f(T a, T b) {
+        if constexpr (is_bool_v<T>) return a & b;
+        else if constexpr (std::is_same<T, f32>::value) return fminf(a, b);
+        else if constexpr (std::is_same<T, f64>::value) return fmin(a, b);
+        else return flt(a, b) ? a : b;
+    }
+};
+struct OpEq {
+    template <class T>
+    __device__ static bool f(T a, T b) { return feq(a, b); }
+};
+struct OpNe {
+    template <class T>
+    __device__ static bool f(T a, T b) { return !feq(a, b); }
+};
+struct OpLt {
+    template <class T>
+    __device__ static bool f(T a, T b) {
+        if constexpr (is_bool_v<T>) return !a & b;
+        else return flt(a, b);
+    }
+};
+struct OpLe {
+    template <class T>
+    __device__ static bool f(T a, T b) {
+        if constexpr (is_bool_v<T>) return a <= b;
+        else return flt(a, b) || feq(a, b);
+    }
+};
+struct OpGt {
+    template <class T>
+    __device__ static bool f(T a, T b) {
+        if constexpr (is_bool_v<T>) return a & !b;
+        else return fgt(a, b);
+    }
+};
+struct OpGe {
+    template <class T>
+    __device__ static bool f(T a, T b) {
+        if constexpr (is_bool_v<T>) return a >= b;
+        else return fgt(a, b) || feq(a, b);
+    }
+};
+struct OpLAnd {
+    template <class T>
+    __device__ static bool f(T a, T b) { return truthy(a) && truthy(b); }
+};
+struct OpLOr {
+    template <class T>
+    __device__ static bool f(T a, T b) { return truthy(a) || truthy(b); }
+};
+struct OpLXor {
+    template <class T>
+    __device__ static bool f(T a, T b) { return truthy(a) != truthy(b); }
+};
+
+// ------------------------------------------------------------------ unary
+#define MX_FP_UNARY(NAME, EXPR32, EXPR64)                                                                            \
+    struct NAME {                                                                                                    \
+        template <class T>                                                                                           \
+        __device__ static T f(T x) {                                                                                 \
+            return fp_apply(x, [](f32 v) -> f32 { return EXPR32; }, [](f64 v) -> f64 { return EXPR64; });             \
+        }                                                                                                            \
+    };
+MX_FP_UNARY(OpSigmoid, 1.0f / (1.0f + expf(-v)), 1.0 / (1.0 + exp(-v)))
+MX_FP_UNARY(OpTanh, tanhf(v), tanh(v))
+MX_FP_UNARY(OpSin, sinf(v), sin(v))
+MX_FP_UNARY(OpCos, cosf(v), cos(v))
+MX_FP_UNARY(OpTan, tanf(v), tan(v))
+MX_FP_UNARY(OpLn, logf(v), log(v))
+MX_FP_UNARY(OpLog10, log10f(v), log10(v))
+MX_FP_UNARY(OpLog2, log2f(v), log2(v))
+MX_FP_UNARY(OpExp, expf(v), exp(v))
+MX_FP_UNARY(OpExp10, powf(10.0f, v), pow(10.0, v))
+MX_FP_UNARY(OpExp2, exp2f(v), exp2(v))
+MX_FP_UNARY(OpSoftplus, logf(1.0f + expf(v)), log(1.0 + exp(v)))
+MX_FP_UNARY(OpRecip, 1.0f / v, 1.0 / v)
+MX_FP_UNARY(OpSqrtF, sqrtf(v), sqrt(v))
+MX_FP_UNARY(OpAbsF, fabsf(v), fabs(v))
+#undef MX_FP_UNARY
+
+__device__ __forceinline__ f32 gelu_f32(f32 x) {
+    const f32 s = 0.7978845608028654f, c = 0.044715f;
+    f32 t = s * (x + c * x * x * x);
+    return 0.5f * x * (1.0f + tanhf(t));
+}
+__device__ __forceinline__ f64 gelu_f64(f64 x) {
+    const f64 s = 0.7978845608028654, c = 0.044715;
+    f64 t = s * (x + c * x * x * x);
+    return 0.5 * x * (1.0 + tanh(t));
+}
+struct OpGelu {
+    template <class T>
+    __device__ static T f(T x) {
+        return fp_apply(x, [](f32 v) { return gelu_f32(v); }, [](f64 v) { return gelu_f64(v); });
+    }
+};
+struct OpNeg {
+    template <class T>
+    __device__ static T f(T x) {
+        if constexpr (is_int_v<T>) return wrap_neg(x);
+        else if constexpr (is_half_v<T>) return from_f32<T>(-to_f32(x));
+        else return -x;
+    }
+};
+struct OpAbs {
+    template <class T>
+    __device__ static T f(T x) {
+        if constexpr (is_int_v<T>) return wrap_abs(x);
+        else return OpAbsF::f(x);
+    }
+};
+struct OpSign {
+    template <class T>
+    __device__ static T f(T x) {
+        if constexpr (is_half_v<T>) {
+            f32 v = to_f32(x);
+            return from_f32<T>(v > 0.0f ? 1.0f : (v < 0.0f ? -1.0f : 0.0f));
+        } else if constexpr (std::is_unsigned<T>::value) return x > 0 ? (T)1 : (T)0;
+        else return x > 0 ? (T)1 : (x < 0 ? (T)-1 : (T)0);
+    }
+};
+struct OpSquare {
+    template <class T>
+    __device__ static T f(T x) {
+        if constexpr (is_int_v<T>) return wrap_mul(x, x);
+        else if constexpr (is_half_v<T>) return from_f32<T>(to_f32(x) * to_f32(x));
+        else return x * x;
+    }
+};
+struct OpSqrt {
+    template <class T>
+    __device__ static T f(T x) {
+        if constexpr (std::is_same<T, i64>::value) return sat_cast<T, f64>(sqrt(__ll2double_rn(wrap_abs(x))));
+        else if constexpr (std::is_same<T, u64>::value) return sat_cast<T, f32>(sqrtf(__ull2float_rn(x)));
+        else if constexpr (is_int_v<T> && std::is_signed<T>::value) return sat_cast<T, f32>(sqrtf((f32)wrap_abs(x)));
+        else if constexpr (is_int_v<T>) return sat_cast<T, f32>(sqrtf((f32)x));
+        else return OpSqrtF::f(x);
+    }
+};
+struct OpRelu {
+    template <class T>
+    __device__ static T f(T x) { return fgt(x, zero_of<T>()) ? x : zero_of<T>(); }
+};
+struct OpLogicalNot {
+    template <class T>
+    __device__ static bool f(T x) {
+        if constexpr (is_bool_v<T>) return !x;
+        else return feq(x, zero_of<T>());
+    }
+};
+
+// ------------------------------------------------------------------ unary with constant
+struct OpPow {
+    template <class T>
+    __device__ static T f(T x, T c) {
+        if constexpr (is_half_v<T>) return from_f32<T>(powf(to_f32(x), to_f32(c)));
+        else if constexpr (std::is_same<T, f32>::value) return powf(x, c);
+        else if constexpr (std::is_same<T, f64>::value) return pow(x, c);
+        else return int_pow(x, c);
+    }
+};
+struct OpLeakyRelu {
+    template <class T>
+    __device__ static T f(T x, T a) {
+        if constexpr (is_half_v<T>) return to_f32(x) > 0.0f ? x : from_f32<T>(to_f32(a) * to_f32(x));
+        else return x > (T)0 ? x : a * x;
+    }
+};
+struct OpElu {
+    template <class T>
+    __device__ static T f(T x, T a) {
+        if constexpr (is_half_v<T>) {
+            f32 xf = to_f32(x);
+            return xf > 0.0f ? x : from_f32<T>(to_f32(a) * (expf(xf) - 1.0f));
+        } else if constexpr (std::is_same<T, f32>::value) return x > 0.0f ? x : a * (expf(x) - 1.0f);
+        else return x > 0.0 ? x : a * (exp(x) - 1.0);
+    }
+};
+
+// Adapters giving every family the call shape the kernels use.
+template <class Op, class T, class O>
+struct Binary {  // out = Op(a, b)
+    __device__ __forceinline__ O operator()(T a, T b) const { return (O)Op::template f<T>(a, b); }
+};
+template <class Op, class T, class O>
+struct Unary {  // out = Op(a)
+    __device__ __forceinline__ O operator()(T a) const { return (O)Op::template f<T>(a); }
+};
+template <class Op, class T, class O>
+struct UnaryConst {  // out = Op(a, c)
+    T c;
+    __device__ __forceinline__ O operator()(T a) const { return (O)Op::template f<T>(a, c); }
+};
+
+}  // namespace mx

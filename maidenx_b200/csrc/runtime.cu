@@ -1,0 +1,197 @@
+// Runtime half of the C ABI: the cudart wrappers the reference's Rust crate exports
+// (crates/maidenx_cuda/src/lib.rs:38-163), the per-thread launch context, the metadata
+// side table and the scratch allocator.
+//
+// Metadata side table.  The reference's dispatch layer uploads each op's dims/strides
+// block with cuda_malloc + cuda_memcpy_h2d right before the call and frees it right
+// after (crates/maidenx_core/src/be/ops/binary.rs:112-133,161-163), so the launcher
+// would have to read device memory back just to size its grid.  Because those wrappers
+// live in this library, cuda_memcpy_h2d remembers small uploads keyed by destination
+// address; the op entry points find the block there without touching the GPU.  Blocks
+// uploaded some other way are read back with a synchronous cudaMemcpy, and a metadata
+// pointer that is ordinary host memory is used directly.
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "common.cuh"
+#include "maidenx_cuda.h"
+
+namespace mx {
+
+namespace {
+constexpr size_t kSideTableMaxBytes = 2048;
+
+std::mutex g_meta_mutex;
+std::unordered_map<const void*, std::vector<size_t>> g_meta_table;
+
+struct ScratchSlot {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+};
+thread_local ScratchSlot t_scratch[64];
+thread_local std::vector<size_t> t_meta_copy;
+thread_local ThreadCtx t_ctx;
+
+int g_sm_count[64] = {0};
+}  // namespace
+
+ThreadCtx& ctx() { return t_ctx; }
+
+void set_error(int status, int cuda_error, const char* where) {
+    ThreadCtx& c = t_ctx;
+    if (c.status != kOk) return;  // sticky: keep the first
+    c.status = status;
+    c.cuda_error = cuda_error;
+    std::snprintf(c.where, sizeof(c.where), "%s", where ? where : "");
+}
+
+void check_launch(const char* where) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) set_error(kErrCuda, (int)e, where);
+}
+
+int sm_count() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (g_sm_count[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        g_sm_count[dev] = n;
+    }
+    return g_sm_count[dev];
+}
+
+const size_t* resolve_metadata(const size_t* meta, size_t count) {
+    if (!meta) return nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_meta_mutex);
+        auto it = g_meta_table.find(meta);
+        if (it != g_meta_table.end() && it->second.size() >= count) {
+            t_meta_copy = it->second;
+            return t_meta_copy.data();
+        }
+    }
+    cudaPointerAttributes attr;
+    cudaError_t e = cudaPointerGetAttributes(&attr, meta);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        set_error(kErrBadMetadata, (int)e, "resolve_metadata");
+        return nullptr;
+    }
+    if (attr.type == cudaMemoryTypeUnregistered || attr.type == cudaMemoryTypeHost) return meta;
+    t_meta_copy.resize(count);
+    // Synchronous on purpose: ordered after prior work on the legacy stream, as the
+    // reference's own cudaMemcpy-based uploads are.
+    e = cudaMemcpy(t_meta_copy.data(), meta, count * sizeof(size_t), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        set_error(kErrBadMetadata, (int)e, "resolve_metadata");
+        return nullptr;
+    }
+    return t_meta_copy.data();
+}
+
+void* scratch(size_t bytes) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        set_error(kErrNoDevice, 0, "scratch");
+        return nullptr;
+    }
+    ScratchSlot& s = t_scratch[dev];
+    if (s.bytes >= bytes && s.ptr) return s.ptr;
+    size_t want = bytes < (size_t)(8u << 20) ? (size_t)(8u << 20) : bytes + bytes / 4;
+    if (s.ptr) {
+        // cudaFree synchronises the device, so earlier kernels that used the old block are done.
+        cudaFree(s.ptr);
+        s.ptr = nullptr;
+        s.bytes = 0;
+    }
+    cudaError_t e = cudaMalloc(&s.ptr, want);
+    if (e != cudaSuccess) {
+        s.ptr = nullptr;
+        set_error(kErrCuda, (int)e, "scratch");
+        return nullptr;
+    }
+    s.bytes = want;
+    return s.ptr;
+}
+
+static void side_table_forget(const void* p) {
+    std::lock_guard<std::mutex> lk(g_meta_mutex);
+    if (!g_meta_table.empty()) g_meta_table.erase(p);
+}
+
+}  // namespace mx
+
+using namespace mx;
+
+extern "C" {
+
+int cuda_malloc(void** ptr, size_t size) { return (int)cudaMalloc(ptr, size); }
+
+int cuda_free(void* ptr) {
+    side_table_forget(ptr);
+    return (int)cudaFree(ptr);
+}
+
+int cuda_memcpy_h2d(void* dst, const void* src, size_t size) {
+    cudaError_t e = cudaMemcpy(dst, src, size, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess && size > 0 && size <= kSideTableMaxBytes && size % sizeof(size_t) == 0) {
+        std::vector<size_t> v(size / sizeof(size_t));
+        std::memcpy(v.data(), src, size);
+        std::lock_guard<std::mutex> lk(g_meta_mutex);
+        g_meta_table[dst] = std::move(v);
+    } else {
+        side_table_forget(dst);
+    }
+    return (int)e;
+}
+
+int cuda_memcpy_d2h(void* dst, const void* src, size_t size) { return (int)cudaMemcpy(dst, src, size, cudaMemcpyDeviceToHost); }
+
+int cuda_memcpy_d2d(void* dst, const void* src, size_t size) {
+    side_table_forget(dst);
+    return (int)cudaMemcpy(dst, src, size, cudaMemcpyDeviceToDevice);
+}
+
+int cuda_set_device(int device_id) { return (int)cudaSetDevice(device_id); }
+int cuda_get_device(int* device_id) { return (int)cudaGetDevice(device_id); }
+int cuda_stream_create(void** stream) { return (int)cudaStreamCreate(reinterpret_cast<cudaStream_t*>(stream)); }
+int cuda_stream_destroy(void* stream) { return (int)cudaStreamDestroy(reinterpret_cast<cudaStream_t>(stream)); }
+int cuda_stream_synchronize(void* stream) { return (int)cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)); }
+
+int cuda_pointer_get_attributes(MxCudaPointerAttributes* attributes, const void* ptr) {
+    cudaPointerAttributes a;
+    cudaError_t e = cudaPointerGetAttributes(&a, ptr);
+    if (e == cudaSuccess && attributes) {
+        attributes->type_ = (int)a.type;
+        attributes->device = a.device;
+        attributes->devicePointer = a.devicePointer;
+        attributes->hostPointer = a.hostPointer;
+    }
+    return (int)e;
+}
+
+const char* cuda_error_string(int error_code) { return cudaGetErrorString((cudaError_t)error_code); }
+
+// ---- additive exports ------------------------------------------------------------
+void mx_set_stream(void* stream) { ctx().stream = reinterpret_cast<cudaStream_t>(stream); }
+void* mx_get_stream(void) { return reinterpret_cast<void*>(ctx().stream); }
+int mx_last_error(void) { return ctx().status; }
+int mx_last_cuda_error(void) { return ctx().cuda_error; }
+const char* mx_last_error_where(void) { return ctx().where; }
+void mx_clear_error(void) {
+    ThreadCtx& c = ctx();
+    c.status = kOk;
+    c.cuda_error = 0;
+    c.where[0] = 0;
+}
+int mx_device_synchronize(void) { return (int)cudaDeviceSynchronize(); }
+int mx_metadata_table_size(void) {
+    std::lock_guard<std::mutex> lk(g_meta_mutex);
+    return (int)g_meta_table.size();
+}
+
+}  // extern "C"

@@ -1,0 +1,236 @@
+"""Parity of the strided elementwise families (binary, in-place, unary, unary-with-constant)
+against the CPU oracle, through the C ABI, on a B200.
+
+Bar: bit-exact for bool / integer outputs and for float ops whose arithmetic is IEEE-exact
+(+ - * / sqrt min max compare ...); transcendental float ops within f32 rel 1e-5
+(f64 1e-12, bf16/f16 1e-2 = about one unit in the last place of the 16-bit result).
+Layouts cover every kernel of the engine: flat (with tail), row broadcasts, transposed
+tiles with and without vector alignment, permuted 3-D (generic), offset-1 views like the
+reference's fixtures, scalars (num_dims = 0) and NULL metadata.
+"""
+import numpy as np
+import pytest
+
+import harness as H
+from maidenx_b200 import _signatures as sig
+from maidenx_b200 import dtypes as D
+
+pytestmark = pytest.mark.gpu
+
+TRANSCENDENTAL = {"sigmoid", "tanh", "gelu", "sin", "cos", "tan", "ln", "log10", "log2", "exp", "exp10", "exp2",
+                  "softplus", "pow", "elu"}
+POSITIVE_DOMAIN = {"ln", "log10", "log2"}
+
+
+def float_tol(op, dt):
+    if op not in TRANSCENDENTAL or dt.kind != "float":
+        return 0.0
+    return {"f32": 1e-5, "f64": 1e-12, "bf16": 1e-2, "f16": 1e-2}[dt.name]
+
+
+def layouts(rng):
+    """(name, dims, lhs_strides, rhs_strides, lhs_off, rhs_off, lhs_len, rhs_len)"""
+    out = []
+    n = 10007
+    out.append(("flat", [n], [1], [1], 0, 0, n, n))
+    out.append(("flat-aligned-offset", [4096], [1], [1], 16, 32, 4096 + 16, 4096 + 32))
+    out.append(("offset1", [n], [1], [1], 1, 1, n + 2, n + 2))
+    r, c = 37, 264
+    out.append(("2d-merged", [r, c], [c, 1], [c, 1], 0, 0, r * c, r * c))
+    out.append(("row-bcast-rhs", [r, c], [c, 1], [0, 1], 0, 0, r * c, c))
+    out.append(("col-bcast-rhs", [r, c], [c, 1], [1, 0], 0, 0, r * c, r))
+    out.append(("scalar-bcast-rhs", [r, c], [c, 1], [0, 0], 0, 3, r * c, 8))
+    out.append(("padded-rows", [r, c], [c + 16, 1], [c, 1], 0, 0, r * (c + 16), r * c))
+    out.append(("transposed-lhs-vec", [128, 192], [1, 128], [192, 1], 0, 0, 128 * 192, 128 * 192))
+    out.append(("transposed-lhs-odd", [67, 131], [1, 67], [131, 1], 0, 0, 67 * 131, 67 * 131))
+    out.append(("transposed-both", [96, 80], [1, 96], [1, 96], 0, 0, 96 * 80, 96 * 80))
+    out.append(("transposed-lhs-bcast-rhs", [70, 90], [1, 70], [0, 1], 1, 0, 70 * 90 + 1, 90))
+    out.append(("batched-transpose", [3, 40, 72], [40 * 72, 1, 40], [40 * 72, 72, 1], 0, 0, 3 * 40 * 72, 3 * 40 * 72))
+    out.append(("permuted-3d", [5, 6, 7], [1, 35, 5], [42, 7, 1], 0, 0, 210, 210))
+    out.append(("size1-dims", [1, 9, 1, 11], [99, 11, 11, 1], [0, 11, 0, 1], 0, 0, 99, 99))
+    out.append(("scalar", [], [], [], 2, 1, 4, 4))
+    return out
+
+
+@pytest.mark.parametrize("op", sig.BINARY_ARITH + sig.BINARY_BOOL)
+def test_binary(oracle, cuda, op):
+    rng = np.random.default_rng(abs(hash(op)) % 2**32)
+    dts = D.ALL if op in sig.BINARY_BOOL else D.ARITH
+    for dt in dts:
+        for name, dims, ls, rs, lo, ro, ll, rl in layouts(rng):
+            lhs, rhs = H.full_range_store(rng, dt, ll), H.full_range_store(rng, dt, rl)
+            if dt.kind != "float":  # make equal / zero pairs common enough to matter
+                k = min(ll, rl) // 3
+                rhs[:k] = lhs[:k]
+            ref = H.run_binary(oracle, op, dt, dims, ls, rs, lo, ro, lhs, rhs)
+            got = H.run_binary(cuda, op, dt, dims, ls, rs, lo, ro, lhs, rhs)
+            H.assert_same(op, dt, got, ref, what=name)
+        # NULL metadata = contiguous, no offsets (crates/maidenx_cuda/kernels/ops/binary.cu:20-25)
+        lhs, rhs = H.full_range_store(rng, dt, 5000), H.full_range_store(rng, dt, 5000)
+        ref = H.run_binary(oracle, op, dt, [5000], [1], [1], 0, 0, lhs, rhs, null_meta=True)
+        got = H.run_binary(cuda, op, dt, [5000], [1], [1], 0, 0, lhs, rhs, null_meta=True)
+        H.assert_same(op, dt, got, ref, what="null-meta")
+
+
+def inplace_layouts():
+    """(name, dims, lhs_strides, rhs_strides, lhs_off, rhs_off, lhs_len, rhs_len)"""
+    return [
+        ("flat", [9001], [1], [1], 0, 0, 9001, 9001),
+        ("offset1", [513], [1], [1], 1, 1, 515, 515),
+        ("lhs-transposed", [64, 96], [1, 64], [96, 1], 0, 0, 64 * 96, 64 * 96),
+        ("lhs-transposed-odd", [33, 77], [1, 33], [77, 1], 2, 0, 33 * 77 + 2, 33 * 77),
+        ("rhs-bcast", [20, 48], [48, 1], [0, 1], 0, 0, 960, 48),
+        ("lhs-strided-rows", [10, 16], [32, 1], [16, 1], 0, 0, 320, 160),
+        ("lhs-permuted-3d", [4, 5, 6], [1, 24, 4], [30, 6, 1], 0, 0, 120, 120),
+        # an lhs that overlaps itself: every logical row lands on the same 8 elements, applied in order
+        ("lhs-stride0", [5, 8], [0, 1], [8, 1], 0, 0, 8, 40),
+        ("scalar", [], [], [], 1, 0, 3, 3),
+    ]
+
+
+@pytest.mark.parametrize("op", sig.BINARY_INPLACE)
+def test_binary_inplace(oracle, cuda, op):
+    rng = np.random.default_rng(abs(hash(op)) % 2**32)
+    for dt in D.ARITH:
+        for name, dims, ls, rs, lo, ro, ll, rl in inplace_layouts():
+            if name == "lhs-stride0" and dt.kind == "float":
+                lhs, rhs = H.random_store(rng, dt, ll), H.random_store(rng, dt, rl, lo=0.5, hi=1.5)
+            else:
+                lhs, rhs = H.full_range_store(rng, dt, ll), H.full_range_store(rng, dt, rl)
+            ref = H.run_binary_inplace(oracle, op, dt, dims, ls, rs, lo, ro, lhs, rhs)
+            got = H.run_binary_inplace(cuda, op, dt, dims, ls, rs, lo, ro, lhs, rhs)
+            H.assert_same(op, dt, got, ref, what=name)  # whole buffer: untouched elements must stay untouched
+
+
+def unary_layouts():
+    """(name, dims, strides, off, buffer_len)"""
+    return [
+        ("flat", [10007], [1], 0, 10007),
+        ("offset1", [1000], [1], 1, 1002),
+        ("transposed-vec", [128, 64], [1, 128], 0, 8192),
+        ("transposed-odd", [45, 83], [1, 45], 3, 45 * 83 + 3),
+        ("bcast-row", [33, 64], [0, 1], 0, 64),       # a lone broadcast input: strides [0, 1]
+        ("bcast-col", [33, 64], [1, 0], 0, 33),
+        ("padded-rows", [12, 40], [48, 1], 0, 576),
+        ("permuted-3d", [5, 6, 7], [1, 35, 5], 0, 210),
+        ("every-other", [777], [2], 0, 1554),
+        ("scalar", [], [], 2, 4),
+    ]
+
+
+def unary_input(rng, op, dt, count):
+    if dt.kind == "float":
+        if op in POSITIVE_DOMAIN:
+            return H.random_store(rng, dt, count, lo=0.01, hi=10.0)
+        if op in TRANSCENDENTAL:
+            return H.random_store(rng, dt, count, lo=-4.0, hi=4.0)
+    return H.full_range_store(rng, dt, count)
+
+
+UNARY_TABLE = [(op, fam, d) for op, d, fam in sig.op_table() if fam in ("unary", "unary_bool")]
+
+
+@pytest.mark.parametrize("op", sorted({op for op, _, _ in UNARY_TABLE}))
+def test_unary(oracle, cuda, op):
+    rng = np.random.default_rng(abs(hash(op)) % 2**32)
+    for dt in [d for o, _, d in UNARY_TABLE if o == op]:
+        for name, dims, st, off, blen in unary_layouts():
+            x = unary_input(rng, op, dt, blen)
+            ref = H.run_unary(oracle, op, dt, dims, st, off, x)
+            got = H.run_unary(cuda, op, dt, dims, st, off, x)
+            H.assert_same(op, dt, got, ref, float_rel=float_tol(op, dt), what=name)
+        x = unary_input(rng, op, dt, 3000)
+        ref = H.run_unary(oracle, op, dt, [3000], [1], 0, x, null_meta=True)
+        got = H.run_unary(cuda, op, dt, [3000], [1], 0, x, null_meta=True)
+        H.assert_same(op, dt, got, ref, float_rel=float_tol(op, dt), what="null-meta")
+
+
+CONST_TABLE = [(op, fam, d) for op, d, fam in sig.op_table() if fam in ("unary_const", "unary_const_bool")]
+
+
+def constants_for(op, dt):
+    if dt.kind == "bool":
+        return [True, False]
+    if dt.kind == "float":
+        if op == "pow":
+            return [2.0, 0.5, -1.0, 3.0]
+        return [0.0, 1.5, -2.25, 0.1]
+    info = np.iinfo(dt.np_storage)
+    cs = [0, 1, 3, info.max, info.max // 3]
+    if dt.kind == "sint":
+        cs += [-1, -2, info.min]
+    if op == "pow":
+        cs = [0, 1, 2, 3, 5, 7, 13, 40, 63, 64, 65] + ([-1, -2, -3] if dt.kind == "sint" else [])
+        cs = [c for c in cs if info.min <= c <= info.max]
+    return cs
+
+
+@pytest.mark.parametrize("op", sorted({op for op, _, _ in CONST_TABLE}))
+def test_unary_with_constant(oracle, cuda, op):
+    rng = np.random.default_rng(abs(hash(op)) % 2**32)
+    for dt in [d for o, _, d in CONST_TABLE if o == op]:
+        for c in constants_for(op, dt):
+            for name, dims, st, off, blen in unary_layouts()[:6] + unary_layouts()[-1:]:
+                if dt.kind == "float" and op == "pow":
+                    x = H.random_store(rng, dt, blen, lo=0.1, hi=4.0)
+                elif dt.kind == "float" and op == "elu":
+                    x = H.random_store(rng, dt, blen, lo=-4.0, hi=4.0)
+                else:
+                    x = H.full_range_store(rng, dt, blen)
+                    if dt.kind in ("uint", "sint") and op == "pow":  # small bases too, so powers stay in range
+                        small = rng.integers(-3 if dt.kind == "sint" else 0, 12, blen // 2)
+                        x[: blen // 2] = small.astype(dt.np_storage)
+                ref = H.run_unary(oracle, op, dt, dims, st, off, x, scalar=c)
+                got = H.run_unary(cuda, op, dt, dims, st, off, x, scalar=c)
+                H.assert_same(op, dt, got, ref, float_rel=float_tol(op, dt), what=f"{name} c={c}")
+
+
+def test_host_metadata_matches_device_metadata(oracle, cuda, cuda_hostmeta):
+    """The metadata pointer may be device memory (the reference's convention) or host memory."""
+    rng = np.random.default_rng(7)
+    dt = D.F32
+    lhs, rhs = H.random_store(rng, dt, 67 * 131), H.random_store(rng, dt, 67 * 131)
+    a = H.run_binary(cuda, "add", dt, [67, 131], [1, 67], [131, 1], 0, 0, lhs, rhs)
+    b = H.run_binary(cuda_hostmeta, "add", dt, [67, 131], [1, 67], [131, 1], 0, 0, lhs, rhs)
+    c = H.run_binary(oracle, "add", dt, [67, 131], [1, 67], [131, 1], 0, 0, lhs, rhs)
+    assert np.array_equal(a, b) and np.array_equal(a, c)
+
+
+def test_metadata_uploaded_outside_the_wrappers(cuda):
+    """A metadata block the side table has never seen is read back from the device."""
+    import ctypes
+    from maidenx_b200 import _lib, device
+    lib = _lib.load()
+    n = 1000
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal(n + 1).astype(np.float32)
+    meta = np.array([n, 1, 1], dtype=np.uint64)  # dims | strides | offset = 1
+    mbuf = device.CudaBuffer(meta.nbytes)
+    # stage through a second device buffer so cuda_memcpy_h2d never sees the final address
+    stage = device.CudaBuffer.from_host(np.concatenate([meta, meta]))  # 48 bytes: a different block
+    assert lib.cuda_memcpy_d2d(mbuf.ptr, stage.ptr, meta.nbytes) == 0
+    xin, out = device.CudaBuffer.from_host(x), device.CudaBuffer(n * 4)
+    _lib.op("neg", "f32")(ctypes.c_size_t(n), ctypes.c_size_t(1), mbuf.ptr, xin.ptr, out.ptr)
+    assert device.last_error() is None
+    assert np.array_equal(out.to_host(np.float32, n), -x[1:])
+    for b in (mbuf, stage, xin, out):
+        b.free()
+
+
+def test_inconsistent_metadata_is_reported(cuda):
+    from maidenx_b200 import device
+    rng = np.random.default_rng(1)
+    x = H.random_store(rng, D.F32, 100)
+    with pytest.raises(device.CudaError):
+        # dims say 10 x 9 = 90 elements, num_els says 100
+        be = cuda
+        n = 100
+
+        def build(put, META):
+            import ctypes
+            a, _ = put(x)
+            b, _ = put(x)
+            o, oh = put(np.zeros(n, np.float32))
+            return [ctypes.c_size_t(n), ctypes.c_size_t(2), META, a, b, o], {"out": (oh, np.float32, n)}
+
+        be.call("add", D.F32, [10, 9, 9, 1, 9, 1, 0, 0], build)
