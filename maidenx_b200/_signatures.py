@@ -88,18 +88,27 @@ def argtypes(family: str, d: dt.DType):
     raise KeyError(family)
 
 
-def bind(cdll: ctypes.CDLL, prefix: str, missing_ok: bool = False):
-    """Set argtypes/restype on every op symbol; returns {(op, dtype name): function}."""
-    fns = {}
-    for op, d, family in op_table():
-        name = f"{prefix}{op}_{d.name}"
-        try:
-            fn = getattr(cdll, name)
-        except AttributeError:
-            if missing_ok:
-                continue
-            raise
-        fn.argtypes = argtypes(family, d)
-        fn.restype = None
-        fns[(op, d.name)] = fn
-    return fns
+class Binder:
+    """Resolves `<prefix><op>_<dtype>` on first use and sets its ctypes signature.  A symbol
+    that is not part of the op layer raises KeyError; one that the library fails to export
+    raises AttributeError at the call site."""
+
+    def __init__(self, cdll: ctypes.CDLL, prefix: str):
+        self.cdll = cdll
+        self.prefix = prefix
+        self.family = {(op, d.name): (family, d) for op, d, family in op_table()}
+        self.cache = {}
+
+    def __getitem__(self, key):
+        fn = self.cache.get(key)
+        if fn is None:
+            family, d = self.family[key]
+            fn = getattr(self.cdll, f"{self.prefix}{key[0]}_{key[1]}")
+            fn.argtypes = argtypes(family, d)
+            fn.restype = None
+            self.cache[key] = fn
+        return fn
+
+
+def bind(cdll: ctypes.CDLL, prefix: str) -> Binder:
+    return Binder(cdll, prefix)

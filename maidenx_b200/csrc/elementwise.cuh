@@ -104,40 +104,88 @@ __global__ void __launch_bounds__(kEwThreads) ew_flat_kernel(F f, const T* a, co
 struct EwRowParams {
     int nd_outer;
     uint32_t total_vecs;
-    FastDiv qv_div;                 // vectors per row
+    uint32_t qv;                    // vectors per row
+    uint32_t chunks_per_row;        // long-row mode: blocks per row
+    FastDiv qv_div;                 // short-row mode: vectors per row
+    FastDiv chunk_div;              // long-row mode: blocks per row
     FastDiv outer_div[kMaxDims];    // outer dims, innermost outer dim last
     int64_t st[3][kMaxDims];        // outer strides per operand
     int sq[3];                      // stride along q per operand (1 or 0)
 };
 
+// Long rows (at least one block-load of vectors per row): a block works inside one row, so
+// the row's base offsets are computed once per block and each thread only adds its vector
+// index — the same instruction stream as the flat kernel.
+template <class F, class T, class O, int NIN, int VEC>
+__global__ void __launch_bounds__(kEwThreads, 4) ew_row_long_kernel(F f, const T* a, const T* b, O* out, EwRowParams P) {
+    uint32_t r, chunk;
+    P.chunk_div.divmod(blockIdx.x, r, chunk);
+    int64_t o_out = 0, o_a = 0, o_b = 0;
+    for (int d = P.nd_outer - 1; d >= 0; d--) {  // block-uniform
+        uint32_t c;
+        P.outer_div[d].divmod(r, r, c);
+        o_out += (int64_t)c * P.st[0][d];
+        o_a += (int64_t)c * P.st[1][d];
+        if constexpr (NIN == 2) o_b += (int64_t)c * P.st[2][d];
+    }
+    out += o_out;
+    a += o_a;
+    if constexpr (NIN == 2) b += o_b;
+    const uint32_t v0 = chunk * (kEwThreads * kEwUnroll) + threadIdx.x;
+    Vec<T, VEC> va[kEwUnroll], vb[kEwUnroll];
+    if (P.sq[1]) {
+#pragma unroll
+        for (int u = 0; u < kEwUnroll; u++)
+            if (v0 + u * kEwThreads < P.qv) va[u] = ld_vec<T, VEC>(a + (size_t)(v0 + u * kEwThreads) * VEC);
+    } else {
+        Vec<T, VEC> s = splat<T, VEC>(a[0]);
+#pragma unroll
+        for (int u = 0; u < kEwUnroll; u++) va[u] = s;
+    }
+    if constexpr (NIN == 2) {
+        if (P.sq[2]) {
+#pragma unroll
+            for (int u = 0; u < kEwUnroll; u++)
+                if (v0 + u * kEwThreads < P.qv) vb[u] = ld_vec<T, VEC>(b + (size_t)(v0 + u * kEwThreads) * VEC);
+        } else {
+            Vec<T, VEC> s = splat<T, VEC>(b[0]);
+#pragma unroll
+            for (int u = 0; u < kEwUnroll; u++) vb[u] = s;
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; u++) {
+        uint32_t v = v0 + u * kEwThreads;
+        if (v < P.qv) st_vec<O, VEC>(out + (size_t)v * VEC, apply_vec<F, T, O, NIN, VEC>(f, va[u], vb[u]));
+    }
+}
+
+// Short rows: one fast-divmod per vector to find its row.
 template <class F, class T, class O, int NIN, int VEC>
 __global__ void __launch_bounds__(kEwThreads) ew_row_kernel(F f, const T* a, const T* b, O* out, EwRowParams P) {
     const uint32_t base = blockIdx.x * (kEwThreads * kEwUnroll);
-    Vec<T, VEC> va[kEwUnroll], vb[kEwUnroll];
-    int64_t oo[kEwUnroll];
 #pragma unroll
     for (int u = 0; u < kEwUnroll; u++) {
         uint32_t v = base + u * kEwThreads + threadIdx.x;
-        oo[u] = -1;
         if (v < P.total_vecs) {
             uint32_t r, qv;
             P.qv_div.divmod(v, r, qv);
             int64_t o_out = (int64_t)qv * VEC, o_a = (int64_t)qv * VEC * P.sq[1], o_b = (int64_t)qv * VEC * P.sq[2];
-            for (int d = P.nd_outer - 1; d >= 0; d--) {
-                uint32_t c;
-                P.outer_div[d].divmod(r, r, c);
-                o_out += (int64_t)c * P.st[0][d];
-                o_a += (int64_t)c * P.st[1][d];
-                if constexpr (NIN == 2) o_b += (int64_t)c * P.st[2][d];
+#pragma unroll
+            for (int d = kMaxDims - 1; d >= 0; d--) {
+                if (d < P.nd_outer) {
+                    uint32_t c;
+                    P.outer_div[d].divmod(r, r, c);
+                    o_out += (int64_t)c * P.st[0][d];
+                    o_a += (int64_t)c * P.st[1][d];
+                    if constexpr (NIN == 2) o_b += (int64_t)c * P.st[2][d];
+                }
             }
-            oo[u] = o_out;
-            va[u] = P.sq[1] ? ld_vec<T, VEC>(a + o_a) : splat<T, VEC>(a[o_a]);
-            if constexpr (NIN == 2) vb[u] = P.sq[2] ? ld_vec<T, VEC>(b + o_b) : splat<T, VEC>(b[o_b]);
+            Vec<T, VEC> va = P.sq[1] ? ld_vec<T, VEC>(a + o_a) : splat<T, VEC>(a[o_a]), vb;
+            if constexpr (NIN == 2) vb = P.sq[2] ? ld_vec<T, VEC>(b + o_b) : splat<T, VEC>(b[o_b]);
+            st_vec<O, VEC>(out + o_out, apply_vec<F, T, O, NIN, VEC>(f, va, vb));
         }
     }
-#pragma unroll
-    for (int u = 0; u < kEwUnroll; u++)
-        if (oo[u] >= 0) st_vec<O, VEC>(out + oo[u], apply_vec<F, T, O, NIN, VEC>(f, va[u], vb[u]));
 }
 
 struct EwTileParams {
@@ -149,26 +197,44 @@ struct EwTileParams {
     int64_t st_batch[3][kMaxDims];
     int64_t st_p[3], st_q[3];
     int transposed[3];              // [1], [2]: input goes through shared memory
+    int smem_slot[3];               // [1], [2]: which staging buffer a transposed input uses
 };
 
 template <class T>
 struct EwTile {
     static constexpr int kTile = sizeof(T) == 8 ? 32 : 64;
     static constexpr int kPitch = kTile * (int)sizeof(T) + (sizeof(T) == 8 ? 8 : 4);  // bytes per staged row
+    static constexpr int kBytes = kTile * kPitch;                                     // one staging buffer
 };
 
+// A warp covers 8 vectors x 4 rows (VEC > 1) or 32 elements x 1 row (VEC == 1) of the tile:
+// 128-byte global segments, and shared-memory word accesses that do not collide.
+template <int VPR, int VEC>
+__device__ __forceinline__ void ew_tile_coord(int i, int& row, int& vcol) {
+    if constexpr (VEC > 1 && VPR >= 8) {
+        constexpr int WC = VPR / 8;  // warp-columns per tile row
+        int w = i >> 5, lane = i & 31;
+        vcol = (w % WC) * 8 + (lane & 7);
+        row = (w / WC) * 4 + (lane >> 3);
+    } else {
+        row = i / VPR;
+        vcol = i % VPR;
+    }
+}
+
 template <class F, class T, class O, int NIN, int VEC>
-__global__ void __launch_bounds__(kEwThreads) ew_tile_kernel(F f, const T* a, const T* b, O* out, EwTileParams P) {
+__global__ void __launch_bounds__(kEwThreads, 4) ew_tile_kernel(F f, const T* a, const T* b, O* out, EwTileParams P) {
     constexpr int TILE = EwTile<T>::kTile;
     constexpr int PITCH = EwTile<T>::kPitch;
-    constexpr int VPR = TILE / VEC;  // vectors per tile row
-    __shared__ __align__(16) unsigned char smem[NIN][TILE * PITCH];
+    constexpr int VPR = TILE / VEC;                       // vectors per tile row
+    constexpr int ITER = (TILE * VPR + kEwThreads - 1) / kEwThreads;
+    extern __shared__ __align__(16) unsigned char ew_smem[];
 
     uint32_t t = blockIdx.x, tq, tp, bidx;
     P.tiles_q_div.divmod(t, t, tq);
     P.tiles_p_div.divmod(t, bidx, tp);
     int64_t base[3] = {0, 0, 0};
-    for (int d = P.nd_batch - 1; d >= 0; d--) {
+    for (int d = P.nd_batch - 1; d >= 0; d--) {  // block-uniform
         uint32_t c;
         P.batch_div[d].divmod(bidx, bidx, c);
 #pragma unroll
@@ -179,23 +245,52 @@ __global__ void __launch_bounds__(kEwThreads) ew_tile_kernel(F f, const T* a, co
     for (int k = 0; k < 3; k++) base[k] += (int64_t)p0 * P.st_p[k] + (int64_t)q0 * P.st_q[k];
     const T* in[2] = {a, b};
 
-    // phase 1: transposed inputs, read along p (their unit-stride dim), staged as [q][p]
+    // All global loads of the tile are issued before the barrier: the direct operands in
+    // the phase-2 mapping (rows along p, vectors along q), the transposed operands in the
+    // phase-1 mapping (rows along q, vectors along p, their unit-stride dim).
+    Vec<T, VEC> direct[NIN][ITER];
+    Vec<T, VEC> staged[NIN][ITER];
+#pragma unroll
+    for (int x = 0; x < NIN; x++) {
+        if (P.transposed[x + 1]) {
+            const T* src = in[x] + base[x + 1];
+#pragma unroll
+            for (int it = 0; it < ITER; it++) {
+                int qq, pv;
+                ew_tile_coord<VPR, VEC>(threadIdx.x + it * kEwThreads, qq, pv);
+                if (qq < TILE && q0 + qq < P.Q && p0 + pv * VEC < P.P) staged[x][it] = ld_vec<T, VEC>(src + (int64_t)qq * P.st_q[x + 1] + pv * VEC);
+            }
+        } else {
+            const T* src = in[x] + base[x + 1];
+#pragma unroll
+            for (int it = 0; it < ITER; it++) {
+                int pp, qv;
+                ew_tile_coord<VPR, VEC>(threadIdx.x + it * kEwThreads, pp, qv);
+                if (pp < TILE && p0 + pp < P.P && q0 + qv * VEC < P.Q) {
+                    const T* s = src + (int64_t)pp * P.st_p[x + 1];
+                    direct[x][it] = P.st_q[x + 1] ? ld_vec<T, VEC>(s + qv * VEC) : splat<T, VEC>(s[0]);
+                }
+            }
+        }
+    }
+    // phase 1: stage the transposed inputs as [q][p]
 #pragma unroll
     for (int x = 0; x < NIN; x++) {
         if (!P.transposed[x + 1]) continue;
-        const T* src = in[x] + base[x + 1];
-        for (int i = threadIdx.x; i < TILE * VPR; i += kEwThreads) {
-            int qq = i / VPR, pv = i % VPR;
-            if (q0 + qq < P.Q && p0 + pv * VEC < P.P) {
-                Vec<T, VEC> v = ld_vec<T, VEC>(src + (int64_t)qq * P.st_q[x + 1] + pv * VEC);
-                unsigned char* row = smem[x] + qq * PITCH + pv * VEC * (int)sizeof(T);
+        unsigned char* buf = ew_smem + P.smem_slot[x + 1] * EwTile<T>::kBytes;
+#pragma unroll
+        for (int it = 0; it < ITER; it++) {
+            int qq, pv;
+            ew_tile_coord<VPR, VEC>(threadIdx.x + it * kEwThreads, qq, pv);
+            if (qq < TILE && q0 + qq < P.Q && p0 + pv * VEC < P.P) {
+                unsigned char* row = buf + qq * PITCH + pv * VEC * (int)sizeof(T);
                 if constexpr (VEC * sizeof(T) >= 4 && sizeof(T) < 4) {
-                    const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
+                    const uint32_t* w = reinterpret_cast<const uint32_t*>(&staged[x][it]);
 #pragma unroll
                     for (int j = 0; j < (int)(VEC * sizeof(T) / 4); j++) reinterpret_cast<uint32_t*>(row)[j] = w[j];
                 } else {
 #pragma unroll
-                    for (int j = 0; j < VEC; j++) reinterpret_cast<T*>(row)[j] = v.v[j];
+                    for (int j = 0; j < VEC; j++) reinterpret_cast<T*>(row)[j] = staged[x][it].v[j];
                 }
             }
         }
@@ -203,19 +298,20 @@ __global__ void __launch_bounds__(kEwThreads) ew_tile_kernel(F f, const T* a, co
     __syncthreads();
 
     // phase 2: walk the tile along q (the output's unit-stride dim)
-    for (int i = threadIdx.x; i < TILE * VPR; i += kEwThreads) {
-        int pp = i / VPR, qv = i % VPR;
-        if (p0 + pp >= P.P || q0 + qv * VEC >= P.Q) continue;
+#pragma unroll
+    for (int it = 0; it < ITER; it++) {
+        int pp, qv;
+        ew_tile_coord<VPR, VEC>(threadIdx.x + it * kEwThreads, pp, qv);
+        if (pp >= TILE || p0 + pp >= P.P || q0 + qv * VEC >= P.Q) continue;
         Vec<T, VEC> v[2];
 #pragma unroll
         for (int x = 0; x < NIN; x++) {
             if (P.transposed[x + 1]) {
+                const unsigned char* buf = ew_smem + P.smem_slot[x + 1] * EwTile<T>::kBytes;
 #pragma unroll
-                for (int j = 0; j < VEC; j++)
-                    v[x].v[j] = *reinterpret_cast<const T*>(smem[x] + (qv * VEC + j) * PITCH + pp * (int)sizeof(T));
+                for (int j = 0; j < VEC; j++) v[x].v[j] = *reinterpret_cast<const T*>(buf + (qv * VEC + j) * PITCH + pp * (int)sizeof(T));
             } else {
-                const T* src = in[x] + base[x + 1] + (int64_t)pp * P.st_p[x + 1];
-                v[x] = P.st_q[x + 1] ? ld_vec<T, VEC>(src + qv * VEC) : splat<T, VEC>(src[0]);
+                v[x] = direct[x][it];
             }
         }
         st_vec<O, VEC>(out + base[0] + (int64_t)pp * P.st_p[0] + qv * VEC, apply_vec<F, T, O, NIN, VEC>(f, v[0], v[1]));
@@ -289,16 +385,23 @@ void ew_launch(const EwPlan& pl, const F& f, const T* a, const T* b, O* out, con
         case EW_ROW: {
             EwRowParams P;
             ew_fill_row_params(pl, VEC, P);
-            uint32_t blocks = ceil_div_u32(P.total_vecs, kEwThreads * kEwUnroll);
-            ew_row_kernel<F, T, O, NIN, VEC><<<blocks, kEwThreads, 0, s>>>(f, a, b, out, P);
+            uint64_t rows = P.total_vecs / P.qv;
+            if (P.qv >= (uint32_t)kEwThreads && rows * P.chunks_per_row < 0x7FFFFFFFull) {
+                ew_row_long_kernel<F, T, O, NIN, VEC><<<(uint32_t)(rows * P.chunks_per_row), kEwThreads, 0, s>>>(f, a, b, out, P);
+            } else {
+                uint32_t blocks = ceil_div_u32(P.total_vecs, kEwThreads * kEwUnroll);
+                ew_row_kernel<F, T, O, NIN, VEC><<<blocks, kEwThreads, 0, s>>>(f, a, b, out, P);
+            }
             break;
         }
         case EW_TILE: {
             EwTileParams P;
             uint32_t blocks;
             ew_fill_tile_params(pl, EwTile<T>::kTile, P, blocks);
-            if (pl.vec) ew_tile_kernel<F, T, O, NIN, VEC><<<blocks, kEwThreads, 0, s>>>(f, a, b, out, P);
-            else ew_tile_kernel<F, T, O, NIN, 1><<<blocks, kEwThreads, 0, s>>>(f, a, b, out, P);
+            int nslots = (P.transposed[1] ? 1 : 0) + (P.transposed[2] ? 1 : 0);
+            size_t smem = (size_t)nslots * EwTile<T>::kBytes;
+            if (pl.vec) ew_tile_kernel<F, T, O, NIN, VEC><<<blocks, kEwThreads, smem, s>>>(f, a, b, out, P);
+            else ew_tile_kernel<F, T, O, NIN, 1><<<blocks, kEwThreads, smem, s>>>(f, a, b, out, P);
             break;
         }
         case EW_GENERIC:

@@ -261,7 +261,10 @@ void ew_fill_row_params(const EwPlan& pl, int vec, EwRowParams& P) {
     const int q = pl.nd - 1;
     P.nd_outer = q;
     P.total_vecs = (uint32_t)(pl.n / vec);
-    P.qv_div.init(pl.dim[q] / vec);
+    P.qv = pl.dim[q] / vec;
+    P.chunks_per_row = (P.qv + kEwThreads * kEwUnroll - 1) / (kEwThreads * kEwUnroll);
+    P.qv_div.init(P.qv);
+    P.chunk_div.init(P.chunks_per_row);
     for (int d = 0; d < q; d++) {
         P.outer_div[d].init(pl.dim[d]);
         for (int k = 0; k < 3; k++) P.st[k][d] = pl.st[k][d];
@@ -291,6 +294,9 @@ void ew_fill_tile_params(const EwPlan& pl, int tile, EwTileParams& P, uint32_t& 
         P.st_q[k] = pl.st[k][q];
         P.transposed[k] = pl.transposed[k] ? 1 : 0;
     }
+    P.smem_slot[0] = 0;
+    P.smem_slot[1] = 0;
+    P.smem_slot[2] = pl.transposed[1] ? 1 : 0;
     blocks = (uint32_t)(nb * P.tiles_p * P.tiles_q);
 }
 

@@ -348,10 +348,20 @@ __device__ __forceinline__ f64 gelu_f64(f64 x) {
     f64 t = s * (x + c * x * x * x);
     return 0.5 * x * (1.0 + tanh(t));
 }
+// For 16-bit outputs the same function is evaluated as x * sigmoid(2t): 0.5 * (1 + tanh(t))
+// == 1 / (1 + exp(-2t)).  With the hardware exp2 / reciprocal its error (~1e-6 relative, no
+// cancellation for negative x) is three orders below the bf16 / f16 rounding step, and it
+// costs a third of tanhf, which keeps the 16-bit kernels memory-bound.
+__device__ __forceinline__ f32 gelu_f32_fast(f32 x) {
+    const f32 s = 0.7978845608028654f, c = 0.044715f;
+    f32 t = s * (x + c * x * x * x);
+    return __fdividef(x, 1.0f + __expf(-2.0f * t));
+}
 struct OpGelu {
     template <class T>
     __device__ static T f(T x) {
-        return fp_apply(x, [](f32 v) { return gelu_f32(v); }, [](f64 v) { return gelu_f64(v); });
+        if constexpr (is_half_v<T>) return from_f32<T>(gelu_f32_fast(to_f32(x)));
+        else return fp_apply(x, [](f32 v) { return gelu_f32(v); }, [](f64 v) { return gelu_f64(v); });
     }
 };
 struct OpNeg {
@@ -390,6 +400,11 @@ struct OpSquare {
 struct OpSqrt {
     template <class T>
     __device__ static T f(T x) {
+        // |MIN| wraps back to MIN: the CPU backend then takes sqrt of a negative number, and the
+        // NaN casts to 0.  Tested on x itself so the compiler cannot fold it into abs().
+        if constexpr (is_int_v<T> && std::is_signed<T>::value) {
+            if (x == Lim<T>::min()) return (T)0;
+        }
         if constexpr (std::is_same<T, i64>::value) return sat_cast<T, f64>(sqrt(__ll2double_rn(wrap_abs(x))));
         else if constexpr (std::is_same<T, u64>::value) return sat_cast<T, f32>(sqrtf(__ull2float_rn(x)));
         else if constexpr (is_int_v<T> && std::is_signed<T>::value) return sat_cast<T, f32>(sqrtf((f32)wrap_abs(x)));

@@ -66,7 +66,8 @@ def encode(values, dt: DType) -> np.ndarray:
         return f32_to_bf16_bits(a.astype(np.float32))
     if dt is BOOL:
         return a.astype(np.bool_)
-    return a.astype(dt.np_storage)
+    with np.errstate(over="ignore", invalid="ignore"):
+        return a.astype(dt.np_storage)
 
 
 def decode(stored: np.ndarray, dt: DType) -> np.ndarray:

@@ -270,9 +270,12 @@ def full_range_store(rng, dt: D.DType, count: int):
     return D.encode(v.astype(np.float32) if dt is not D.F64 else v, dt)
 
 
-def assert_same(op, dt, got, ref, float_rel=0.0, what=""):
+def assert_same(op, dt, got, ref, float_rel=0.0, what="", scale=None):
     """Bit-exact for bool / integer outputs; for float outputs exact when float_rel == 0
-    (NaNs compare equal as a class), else |got - ref| <= float_rel * max(|ref|, tiny)."""
+    (NaNs compare equal as a class), else |got - ref| <= float_rel * max(|ref|, scale).
+    `scale` (scalar or per-element) is the magnitude of the intermediate a formula cancels
+    against: 0.5*x*(1 + tanh(t)) loses |x| * eps when tanh(t) is near -1, alpha*(exp(x) - 1)
+    loses alpha * eps near x = 0; the relative bound is taken against that magnitude."""
     assert got.shape == ref.shape, (what, got.shape, ref.shape)
     if got.dtype == np.bool_ or dt.kind in ("uint", "sint", "bool"):
         bad = np.nonzero(got != ref)[0]
@@ -282,13 +285,14 @@ def assert_same(op, dt, got, ref, float_rel=0.0, what=""):
     nan_g, nan_r = np.isnan(g), np.isnan(r)
     assert np.array_equal(nan_g, nan_r), f"{what} {op}_{dt.name}: NaN pattern differs"
     ok = ~nan_g
-    g, r = g[ok], r[ok]
+    sc = np.full(g.shape, 1e-30) if scale is None else np.broadcast_to(np.abs(np.asarray(scale, dtype=np.float64)), g.shape)
+    g, r, sc = g[ok], r[ok], sc[ok]
     inf = np.isinf(r)
     assert np.array_equal(g[inf], r[inf]), f"{what} {op}_{dt.name}: infinities differ"
     assert not np.isinf(g[~inf]).any(), f"{what} {op}_{dt.name}: unexpected infinity"
-    g, r = g[~inf], r[~inf]
+    g, r, sc = g[~inf], r[~inf], sc[~inf]
     if float_rel == 0.0:
         bad = np.nonzero(g != r)[0]
     else:
-        bad = np.nonzero(np.abs(g - r) > float_rel * np.maximum(np.abs(r), 1e-30))[0]
+        bad = np.nonzero(np.abs(g - r) > float_rel * np.maximum(np.abs(r), np.maximum(sc, 1e-30)))[0]
     assert bad.size == 0, f"{what} {op}_{dt.name}: {bad.size} mismatches (rel {float_rel}), first: got {g[bad[:5]]} want {r[bad[:5]]}"

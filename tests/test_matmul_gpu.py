@@ -1,0 +1,136 @@
+"""Parity of matmul / matmul_backward against the CPU oracle, through the C ABI, on a B200.
+
+Bar: integers bit-exact (wrapping); f32 / f64 bit-exact against the oracle's faithful mode
+(element-type accumulation, k ascending — the SIMT kernel keeps that order and does not
+contract multiplies and adds); bf16 / f16 against the oracle's wide mode (f32 accumulation,
+one rounding): bit-exact on the SIMT path, within rel 2e-2 of max(|ref|, sqrt(K)) where the
+tensor-core path (different summation order) takes the call.
+Cases include the reference's index quirks: only strides[0] is used for the batch of
+rank > 3 operands, rank-1 B is indexed by the output column alone, and terms whose linear
+index reaches num_els * k are skipped (crates/maidenx_cpu/src/ops/matmul.rs:55-113).
+"""
+import numpy as np
+import pytest
+
+import harness as H
+from maidenx_b200 import dtypes as D
+
+pytestmark = pytest.mark.gpu
+
+
+def fwd_cases():
+    """(name, out_shape, a_shape, b_shape, a_strides, b_strides, a_off, b_off, a_len, b_len)"""
+    cs = H.contiguous_strides
+    out = []
+
+    def add(name, o, a, b, ast=None, bst=None, aoff=0, boff=0, alen=None, blen=None):
+        ast = ast or cs(a)
+        bst = bst or cs(b)
+        alen = alen or (sum((d - 1) * s for d, s in zip(a, ast)) + 1 + aoff)
+        blen = blen or (sum((d - 1) * s for d, s in zip(b, bst)) + 1 + boff)
+        out.append((name, o, a, b, ast, bst, aoff, boff, alen, blen))
+
+    add("mm-small", [2, 2], [2, 2], [2, 2], aoff=1, boff=1)
+    add("mm-odd", [65, 33], [65, 70], [70, 33])
+    add("mm-tiles", [128, 192], [128, 96], [96, 192])
+    add("mm-tall-k", [7, 5], [7, 1000], [1000, 5])
+    add("nt-linear", [50, 24], [50, 40], [40, 24], bst=[1, 40])            # x . W^T with W [24, 40]
+    add("tn", [30, 20], [30, 16], [16, 20], ast=[1, 30])
+    add("batched", [3, 20, 17], [3, 20, 30], [3, 30, 17])
+    add("batched-span", [5, 50, 9], [5, 50, 8], [5, 8, 9])                 # 64-row tiles span batches
+    add("batch-bcast-b", [4, 10, 6], [4, 10, 7], [4, 7, 6], bst=[0, 6, 1])  # B broadcast over the batch
+    add("rank4", [2, 3, 4, 6], [2, 3, 4, 5], [2, 3, 5, 6])                 # batch index uses strides[0] only
+    add("vec-mat", [1, 9], [1, 12], [12, 9])
+    add("mat-vec", [8, 1], [8, 12], [12, 1])
+    add("rank1-a", [3, 4], [5], [5, 4], alen=5)                            # literal: A indexed by k only
+    add("rank1-b", [6, 4], [6, 5], [4], blen=4)                            # literal: B indexed by n only
+    add("sliced-a-skips", [6, 1], [6, 4], [4, 1], ast=[16, 1])             # indices >= num_els * k are dropped
+    return out
+
+
+def _inputs(rng, dt, n):
+    if dt.kind == "float":
+        return H.random_store(rng, dt, n, dist="normal")
+    return H.full_range_store(rng, dt, n)
+
+
+@pytest.mark.parametrize("dt", D.ARITH, ids=lambda d: d.name)
+def test_matmul_forward(oracle, cuda, dt):
+    from oracle import binding
+    rng = np.random.default_rng(100 + D.ARITH.index(dt))
+    for name, o, a_sh, b_sh, ast, bst, aoff, boff, alen, blen in fwd_cases():
+        meta = H.matmul_metadata(o, a_sh, b_sh, ast, bst, aoff, boff)
+        a, b = _inputs(rng, dt, alen), _inputs(rng, dt, blen)
+        n = H.numel(o)
+        binding.set_wide(dt.name in ("bf16", "f16"))
+        try:
+            ref = H.run_matmul(oracle, dt, meta, n, a, b)
+        finally:
+            binding.set_wide(False)
+        got = H.run_matmul(cuda, dt, meta, n, a, b)
+        if dt.name in ("bf16", "f16"):
+            H.assert_same("matmul", dt, got, ref, float_rel=2e-2, what=name, scale=np.sqrt(a_sh[-1]))
+        else:
+            H.assert_same("matmul", dt, got, ref, what=name)
+
+
+def bwd_cases():
+    """(name, out_shape, a_shape, b_shape, a_off, b_off)"""
+    return [
+        ("mm", [2, 2], [2, 2], [2, 2], 1, 1),
+        ("mm-odd", [37, 21], [37, 45], [45, 21], 0, 0),
+        ("mm-tiles", [128, 64], [128, 96], [96, 64], 0, 0),
+        ("batched", [3, 10, 7], [3, 10, 12], [3, 12, 7], 2, 0),
+        ("mat-vec", [9, 1], [9, 14], [14, 1], 0, 3),
+        ("vec-mat", [1, 6], [1, 11], [11, 6], 0, 0),
+    ]
+
+
+@pytest.mark.parametrize("dt", D.ARITH, ids=lambda d: d.name)
+def test_matmul_backward(oracle, cuda, dt):
+    from oracle import binding
+    rng = np.random.default_rng(200 + D.ARITH.index(dt))
+    cs = H.contiguous_strides
+    for name, o, a_sh, b_sh, aoff, boff in bwd_cases():
+        meta = H.matmul_metadata(o, a_sh, b_sh, cs(a_sh), cs(b_sh), aoff, boff)
+        nea, neb = H.numel(a_sh), H.numel(b_sh)
+        a, b, g = _inputs(rng, dt, nea + aoff), _inputs(rng, dt, neb + boff), _inputs(rng, dt, H.numel(o))
+        for want_a, want_b in ((True, True), (True, False), (False, True)):
+            binding.set_wide(dt.name in ("bf16", "f16"))
+            try:
+                ref = H.run_matmul_backward(oracle, dt, meta, nea, neb, g, a, b, want_a, want_b)
+            finally:
+                binding.set_wide(False)
+            got = H.run_matmul_backward(cuda, dt, meta, nea, neb, g, a, b, want_a, want_b)
+            for key in ref:
+                if dt.name in ("bf16", "f16"):
+                    k = o[-1] if key == "ga" else (o[-2] if len(o) >= 2 else 1)
+                    H.assert_same("matmul_backward", dt, got[key], ref[key], float_rel=2e-2, what=f"{name}/{key}", scale=np.sqrt(k))
+                else:
+                    H.assert_same("matmul_backward", dt, got[key], ref[key], what=f"{name}/{key}")
+
+
+def test_matmul_backward_ignores_strides_of_a_transposed_view(oracle, cuda):
+    """Linear's backward hands matmul_backward the transposed weight view; both backends read it
+    as if it were contiguous (crates/maidenx_cpu/src/ops/matmul.rs:211-217)."""
+    dt = D.F32
+    rng = np.random.default_rng(5)
+    o, a_sh, b_sh = [6, 4], [6, 5], [5, 4]
+    meta = H.matmul_metadata(o, a_sh, b_sh, [5, 1], [1, 5], 0, 0)  # B = W^T view, strides [1, 5]
+    a, b, g = _inputs(rng, dt, 30), _inputs(rng, dt, 20), _inputs(rng, dt, 24)
+    ref = H.run_matmul_backward(oracle, dt, meta, 30, 20, g, a, b)
+    got = H.run_matmul_backward(cuda, dt, meta, 30, 20, g, a, b)
+    for key in ref:
+        H.assert_same("matmul_backward", dt, got[key], ref[key], what=key)
+
+
+def test_matmul_backward_scalar_grad(oracle, cuda):
+    """out_ndim == 0: every gradient row is grad_output[0] times the other operand (matmul.rs:204-207,240-243)."""
+    dt = D.F32
+    rng = np.random.default_rng(6)
+    meta = [0, 1, 1, 7, 7, 1, 1, 0, 0]  # out_ndim 0, a_shape [7], b_shape [7]
+    a, b, g = _inputs(rng, dt, 7), _inputs(rng, dt, 7), _inputs(rng, dt, 1)
+    ref = H.run_matmul_backward(oracle, dt, meta, 7, 7, g, a, b)
+    got = H.run_matmul_backward(cuda, dt, meta, 7, 7, g, a, b)
+    for key in ref:
+        H.assert_same("matmul_backward", dt, got[key], ref[key], what=key)
