@@ -42,8 +42,10 @@ def fwd_cases():
     add("rank4", [2, 3, 4, 6], [2, 3, 4, 5], [2, 3, 5, 6])                 # batch index uses strides[0] only
     add("vec-mat", [1, 9], [1, 12], [12, 9])
     add("mat-vec", [8, 1], [8, 12], [12, 1])
-    add("rank1-a", [3, 4], [5], [5, 4], alen=5)                            # literal: A indexed by k only
-    add("rank1-b", [6, 4], [6, 5], [4], blen=4)                            # literal: B indexed by n only
+    add("rank1-a", [1, 4], [5], [5, 4])                                    # contiguous formulas, m = 1
+    add("rank1-b", [6, 1], [6, 5], [5])                                    # contiguous formulas, n = 1
+    add("rank1-a-strided", [3, 4], [5], [5, 4], ast=[2], alen=9)           # literal: A indexed by k only, rows repeat
+    add("rank1-b-strided", [6, 4], [6, 5], [4], bst=[2], blen=7)           # literal: B indexed by n only
     add("sliced-a-skips", [6, 1], [6, 4], [4, 1], ast=[16, 1])             # indices >= num_els * k are dropped
     return out
 
