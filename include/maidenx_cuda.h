@@ -219,6 +219,9 @@ int mx_last_cuda_error(void);
 const char* mx_last_error_where(void);
 void mx_clear_error(void);
 int mx_device_synchronize(void);
+/* 0, or the wait that gave up (1 producer, 2/3 MMA issuer, 4 epilogue) in the last tensor-core matmul of
+ * this thread's device; a non-zero value is also recorded as status 5.  Call after a synchronisation. */
+int mx_tc_gemm_status(void);
 /* Number of metadata blocks currently remembered by cuda_memcpy_h2d (diagnostics). */
 int mx_metadata_table_size(void);
 

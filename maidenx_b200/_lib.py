@@ -33,6 +33,7 @@ RUNTIME_SIGNATURES = {
     "mx_clear_error": ([], None),
     "mx_device_synchronize": ([], ctypes.c_int),
     "mx_metadata_table_size": ([], ctypes.c_int),
+    "mx_tc_gemm_status": ([], ctypes.c_int),
 }
 
 

@@ -1,10 +1,570 @@
-// Tensor-core (tcgen05 / TMEM / TMA) path for bf16 / f16 matmul.
+// Tensor-core path for bf16 / f16 matmul on sm_100a: tcgen05.mma with the accumulator in
+// tensor memory (TMEM), operands staged in shared memory by TMA, epilogue read back with
+// tcgen05.ld, converted and written with TMA stores.
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of the A [128 x 64]
+//               and B [256 x 64] k-blocks into a 4-stage shared-memory ring (128-byte swizzle);
+//   warp 1      MMA issuer: one lane issues four tcgen05.mma (M128 N256 K16) per k-block into
+//               one of two 256-column TMEM accumulators, commits the stage back to the
+//               producer and, after the last k-block, the accumulator to the epilogue;
+//   warps 2-5   epilogue: each warp owns the 32 TMEM lanes it may address (warp id mod 4),
+//               reads them 64 columns at a time, rounds to bf16 / f16, writes a swizzled
+//               4 KB staging tile and stores it with TMA while the next tile's MMAs run on
+//               the other accumulator.
+// No cluster launch: every CTA issues its own (CTA-local) TMA loads; re-use comes from
+// L2 through the order in which output tiles are handed out (16 row-tiles per column sweep).
+//
+// The kernel computes D[M,N] = sum_k A[m,k] * B[n,k] with both operands K-major (row-major
+// [M,K] and [N,K]); this is the reference's forward x . W^T (crates/maidenx_nn/src/layers/linear.rs:74)
+// and its grad_a = g . B^T (crates/maidenx_cpu/src/ops/matmul.rs:208-216) directly.  Products whose
+// operands are laid out the other way (grad_b = A^T . g, plain [K,N] B) first transpose the
+// MN-major operand into scratch with a tiled copy.
+//
+// Every mbarrier wait is bounded by a clock64() budget; on expiry the thread records an
+// error word, stops issuing work and falls through to the common exit, where TMEM is freed.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
 #include "matmul_tc.cuh"
 
 namespace mx {
 
-bool tc_gemm_bf16_f16(bool, const MmDesc&, int, size_t, size_t, size_t, const void*, const void*, void*, const char*) {
-    return false;  // placeholder until the tcgen05 kernel lands: every call takes the SIMT path
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;    // CTA tile; BK * 2 bytes = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;    // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;    // 32 KB
+constexpr int EPI_WARPS = 4;
+constexpr int EPI_CHUNK_COLS = 64;            // columns per TMA store (128 bytes of 16-bit)
+constexpr int EPI_STAGE_BYTES = 32 * EPI_CHUNK_COLS * 2;  // 4 KB per warp per buffer
+constexpr int TC_THREADS = 32 * (2 + EPI_WARPS);
+constexpr int TMEM_COLS = 512;                // two 256-column f32 accumulators
+constexpr int GROUP_M = 16;                   // row-tiles per column sweep (L2 re-use)
+constexpr long long WAIT_BUDGET_CYCLES = 4000000000ll;  // about two seconds
+
+struct SmemLayout {
+    // offsets inside the dynamic shared memory block (base aligned to 1024 bytes)
+    static constexpr int a = 0;
+    static constexpr int b = a + STAGES * A_STAGE_BYTES;
+    static constexpr int epi = b + STAGES * B_STAGE_BYTES;
+    static constexpr int bars = epi + EPI_WARPS * 2 * EPI_STAGE_BYTES;
+    static constexpr int total = bars + 256;
+};
+constexpr int TC_SMEM_BYTES = SmemLayout::total + 1024;  // slack for the 1024-byte alignment
+
+// ---------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false (and records `code` in *err) when the budget runs out or when
+// another thread has already reported an error.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*reinterpret_cast<volatile int*>(err) != 0) return false;
+        if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
+            atomicCAS(err, 0, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128 bytes with
+// the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the leading
+// byte offset is unused for swizzled K-major layouts.
+__device__ __forceinline__ uint64_t smem_desc_kmajor_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);      // start address, bits [0,14)
+    d |= (uint64_t)1 << 16;                            // leading byte offset (ignored), bits [16,30)
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset, bits [32,46)
+    d |= (uint64_t)1 << 46;                            // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;                            // layout: 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor of tcgen05.mma kind::f16: f32 accumulate, A and B both K-major.
+__host__ __device__ constexpr uint32_t make_idesc(bool is_bf16) {
+    uint32_t d = 0;
+    d |= 1u << 4;                               // D format: f32
+    d |= (is_bf16 ? 1u : 0u) << 7;              // A format: 0 = f16, 1 = bf16
+    d |= (is_bf16 ? 1u : 0u) << 10;             // B format
+    d |= 0u << 15;                              // A major: K
+    d |= 0u << 16;                              // B major: K
+    d |= (uint32_t)(BN >> 3) << 17;             // N / 8
+    d |= (uint32_t)(BM >> 4) << 24;             // M / 16
+    return d;
+}
+
+struct TcParams {
+    int M, N, K;
+    int tiles_m, tiles_n, num_tiles, num_kb;
+    int is_bf16;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, const TcParams& p, int& tm, int& tn) {
+    // sweep GROUP_M row-tiles for each column tile before moving to the next column tile
+    const int group_size = GROUP_M * p.tiles_n;
+    const int group = tile / group_size;
+    const int first_m = group * GROUP_M;
+    const int rows = min(GROUP_M, p.tiles_m - first_m);
+    const int in_group = tile - group * group_size;
+    tm = first_m + in_group % rows;
+    tn = in_group / rows;
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
+    if (is_bf16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_d,
+               TcParams p, int* err) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    // 128-byte swizzled TMA tiles and UMMA descriptors want 1024-byte aligned bases
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_base + SmemLayout::bars;
+    // barrier slots (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then the TMEM base word
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + SmemLayout::bars + 8 * (2 * STAGES + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), EPI_WARPS);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 1) {  // the MMA warp owns the TMEM allocation
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                int tm, tn;
+                tile_coords(tile, p, tm, tn);
+                for (int kb = 0; kb < p.num_kb; kb++) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1, err, 1)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(full_bar(stage), A_STAGE_BYTES + B_STAGE_BYTES);
+                    tma_load_2d(smem_base + SmemLayout::a + stage * A_STAGE_BYTES, &map_a, kb * BK, tm * BM, full_bar(stage));
+                    tma_load_2d(smem_base + SmemLayout::b + stage * B_STAGE_BYTES, &map_b, kb * BK, tn * BN, full_bar(stage));
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(p.is_bf16 != 0);
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, err, 2)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+                for (int kb = 0; kb < p.num_kb; kb++) {
+                    if (!mbar_wait(full_bar(stage), phase, err, 3)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t da = smem_desc_kmajor_sw128(smem_base + SmemLayout::a + stage * A_STAGE_BYTES);
+                    const uint64_t db = smem_desc_kmajor_sw128(smem_base + SmemLayout::b + stage * B_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        // advance 16 elements (32 bytes) along K inside the swizzled row: +2 in the address field
+                        umma_f16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb | k) != 0);
+                    }
+                    umma_commit(empty_bar(stage));  // the stage may be refilled once these MMAs have read it
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(tfull_bar(acc));  // accumulator complete
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;  // TMEM lanes [32 * quarter, 32 * quarter + 32)
+        const int ew = warp - 2;
+        unsigned char* stage_buf = smem + SmemLayout::epi + ew * 2 * EPI_STAGE_BYTES;
+        int acc = 0, buf = 0;
+        uint32_t acc_phase = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+            int tm, tn;
+            tile_coords(tile, p, tm, tn);
+            // the TMEM loads below are warp-collective: leave the loop only as a whole warp
+            const bool ready = mbar_wait(tfull_bar(acc), acc_phase, err, 4);
+            if (!__all_sync(0xFFFFFFFFu, ready)) break;
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / EPI_CHUNK_COLS; c++) {
+                uint32_t v0[32], v1[32];
+                tmem_ld_32x32b_x32(t_row + c * EPI_CHUNK_COLS, v0);
+                tmem_ld_32x32b_x32(t_row + c * EPI_CHUNK_COLS + 32, v1);
+                tmem_ld_wait();
+                if (c == BN / EPI_CHUNK_COLS - 1) {
+                    // every TMEM read of this accumulator is done: hand it back to the MMA warp
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(acc));
+                }
+                // the staging buffer must have been read by its previous TMA store
+                if (lane == 0) tma_store_wait_read<1>();
+                __syncwarp();
+                unsigned char* dst = stage_buf + buf * EPI_STAGE_BYTES + lane * 128;  // row `lane` of the 32 x 64 tile
+#pragma unroll
+                for (int j = 0; j < 8; j++) {  // eight 16-byte chunks per row, XOR-swizzled by the row index
+                    const uint32_t* src = j < 4 ? &v0[j * 8] : &v1[(j - 4) * 8];
+                    uint4 q;
+                    q.x = pack2(__uint_as_float(src[0]), __uint_as_float(src[1]), p.is_bf16);
+                    q.y = pack2(__uint_as_float(src[2]), __uint_as_float(src[3]), p.is_bf16);
+                    q.z = pack2(__uint_as_float(src[4]), __uint_as_float(src[5]), p.is_bf16);
+                    q.w = pack2(__uint_as_float(src[6]), __uint_as_float(src[7]), p.is_bf16);
+                    *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = q;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&map_d, smem_u32(stage_buf + buf * EPI_STAGE_BYTES), tn * BN + c * EPI_CHUNK_COLS, tm * BM + quarter * 32);
+                    tma_store_commit();
+                }
+                buf ^= 1;
+            }
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1;
+            }
+        }
+        if (lane == 0) tma_store_wait_all();
+    }
+
+    // common exit: TMEM is released by the warp that allocated it, after everyone is done with it
+    tc_fence_before();
+    __syncthreads();
+    if (*reinterpret_cast<volatile int*>(err) != 0) {
+        // a wait gave up: give bulk copies still in flight towards this CTA's shared memory time to land
+        const long long t0 = clock64();
+        while (clock64() - t0 < 4000000ll) {
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// K-major copy of an MN-major operand: dst[c][r] = src[r][c] for a [rows, cols] matrix
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) transpose16_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int rows, int cols,
+                                                         long long src_batch, long long dst_batch) {
+    __shared__ uint16_t tile[64][66];
+    src += (long long)blockIdx.z * src_batch;
+    dst += (long long)blockIdx.z * dst_batch;
+    const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        int r = i / 64, c = i % 64;
+        if (r0 + r < rows && c0 + c < cols) tile[r][c] = src[(long long)(r0 + r) * cols + c0 + c];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        int c = i / 64, r = i % 64;
+        if (r0 + r < rows && c0 + c < cols) dst[(long long)(c0 + c) * rows + r0 + r] = tile[r][c];
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// [rows, cols] row-major 16-bit matrix, box = box_rows x 64 columns, 128-byte swizzle
+bool make_map(CUtensorMap* map, bool is_bf16, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+struct DeviceState {
+    int* err = nullptr;       // device error word
+    bool attr_set = false;
+};
+thread_local DeviceState t_state[64];
+
+DeviceState* device_state() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    DeviceState& s = t_state[dev];
+    if (!s.err) {
+        if (cudaMalloc(&s.err, sizeof(int)) != cudaSuccess) return nullptr;
+        cudaMemset(s.err, 0, sizeof(int));
+    }
+    if (!s.attr_set) {
+        if (cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        s.attr_set = true;
+    }
+    return &s;
+}
+
+// D[M,N] = A[M,K] . B[N,K]^T, all row-major and dense.
+bool launch_kmajor(bool is_bf16, const void* A, const void* B, void* D, uint64_t M, uint64_t N, uint64_t K, const char* where) {
+    DeviceState* st = device_state();
+    if (!st) return false;
+    CUtensorMap ma, mb, md;
+    if (!make_map(&ma, is_bf16, A, M, K, BM) || !make_map(&mb, is_bf16, B, N, K, BN) || !make_map(&md, is_bf16, D, M, N, 32)) return false;
+    TcParams p;
+    p.M = (int)M;
+    p.N = (int)N;
+    p.K = (int)K;
+    p.tiles_m = (int)((M + BM - 1) / BM);
+    p.tiles_n = (int)((N + BN - 1) / BN);
+    p.num_tiles = p.tiles_m * p.tiles_n;
+    p.num_kb = (int)((K + BK - 1) / BK);
+    p.is_bf16 = is_bf16 ? 1 : 0;
+    int grid = sm_count();
+    if (grid > p.num_tiles) grid = p.num_tiles;
+    tc_gemm_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx().stream>>>(ma, mb, md, p, st->err);
+    check_launch(where);
+    return true;
+}
+
+bool eligible(uint64_t M, uint64_t N, uint64_t K, const void* a, const void* b, const void* d) {
+    // TMA: 16-byte aligned bases and row pitches; sizes must fit the int coordinates
+    if (M == 0 || N == 0 || K == 0) return false;
+    if (K % 8 != 0 || N % 8 != 0) return false;
+    if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)d) % 16 != 0) return false;
+    if (M > 0x7FFFFFFFull || N > 0x7FFFFFFFull || K > 0x7FFFFFFFull) return false;
+    // small problems are not worth a persistent launch
+    if (M * N * K < (1ull << 24)) return false;
+    return true;
+}
+
+}  // namespace
+
+// Checks the error word of the calling thread's device after a synchronisation point.
+extern "C" int mx_tc_gemm_status(void) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !t_state[dev].err) return 0;
+    int v = 0;
+    if (cudaMemcpy(&v, t_state[dev].err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v != 0) {
+        set_error(kErrDeviceWait, v, "tc_gemm_kernel");
+        cudaMemset(t_state[dev].err, 0, sizeof(int));
+    }
+    return v;
+}
+
+bool tc_gemm_bf16_f16(bool is_bf16, const MmDesc& d, int which, size_t num_els, size_t nea, size_t neb, const void* x, const void* y, void* out,
+                      const char* where) {
+    const size_t es = 2;
+    if (which == 0) {
+        // forward: C[m, n] = sum_k A[m, k] * B[k, n], unbatched, dense operands
+        if (d.out_nd < 2 || d.a_nd < 2 || d.b_nd < 2) return false;
+        const uint64_t m = d.m, n = d.n, k = d.k_fwd;
+        if (num_els != m * n) return false;  // batched products stay on the SIMT path
+        const char* A = static_cast<const char*>(x) + d.a_off * es;
+        const char* B = static_cast<const char*>(y) + d.b_off * es;
+        bool a_kmajor, b_kmajor, b_mnmajor;
+        if (d.a_cont && d.b_cont) {
+            // the reference's contiguous branch: A is [m, k], B is [k, n], both dense
+            a_kmajor = true;
+            b_kmajor = false;
+            b_mnmajor = true;
+        } else {
+            // strided branch: A[m * as1 + k * as2], B[k * bs1 + n * bs2]
+            a_kmajor = d.a_strides[2] == 1 && d.a_strides[1] == (int64_t)k;
+            b_kmajor = d.b_strides[1] == 1 && d.b_strides[2] == (int64_t)k;   // transposed view of a dense [n, k] matrix
+            b_mnmajor = d.b_strides[2] == 1 && d.b_strides[1] == (int64_t)n;  // dense [k, n]
+        }
+        if (!a_kmajor) return false;
+        if (b_kmajor) {
+            if (!eligible(m, n, k, A, B, out)) return false;
+            return launch_kmajor(is_bf16, A, B, out, m, n, k, where);
+        }
+        if (b_mnmajor) {
+            if (!eligible(m, n, k, A, out, out)) return false;
+            dim3 grid((unsigned)((n + 63) / 64), (unsigned)((k + 63) / 64), 1);
+            if (grid.y > 65535) return false;
+            uint16_t* bt = static_cast<uint16_t*>(scratch(n * k * es));
+            if (!bt) return false;
+            transpose16_kernel<<<grid, 256, 0, ctx().stream>>>(reinterpret_cast<const uint16_t*>(B), bt, (int)k, (int)n, 0, 0);
+            return launch_kmajor(is_bf16, A, bt, out, m, n, k, where);
+        }
+        return false;
+    }
+    // backward products read g, A and B as dense row-major matrices (strides ignored)
+    if (d.out_nd != 2) return false;
+    const uint64_t m = d.m, n = d.n, k = d.k_bwd;
+    if (d.g_size != m * n) return false;
+    if (which == 1) {
+        // grad_a[m, k] = sum_n g[m, n] * B[k, n]: both operands K-major (K here is n)
+        if (nea != m * k || neb != k * n) return false;
+        if (!eligible(m, k, n, x, y, out)) return false;
+        return launch_kmajor(is_bf16, x, y, out, m, k, n, where);
+    }
+    // grad_b[k, n] = sum_m A[m, k] * g[m, n]: both operands MN-major; transpose both into scratch
+    if (nea != m * k || neb != k * n) return false;
+    if (!eligible(k, n, m, out, out, out) || m % 8 != 0) return false;
+    uint16_t* buf = static_cast<uint16_t*>(scratch((m * k + m * n) * es + 256));
+    if (!buf) return false;
+    uint16_t* at = buf;                                        // [k, m]
+    uint16_t* gt = buf + ((m * k + 127) / 128) * 128;          // [n, m], 256-byte aligned
+    {
+        dim3 grid((unsigned)((k + 63) / 64), (unsigned)((m + 63) / 64), 1);
+        if (grid.y > 65535) return false;
+        transpose16_kernel<<<grid, 256, 0, ctx().stream>>>(static_cast<const uint16_t*>(y), at, (int)m, (int)k, 0, 0);
+    }
+    {
+        dim3 grid((unsigned)((n + 63) / 64), (unsigned)((m + 63) / 64), 1);
+        if (grid.y > 65535) return false;
+        transpose16_kernel<<<grid, 256, 0, ctx().stream>>>(static_cast<const uint16_t*>(x), gt, (int)m, (int)n, 0, 0);
+    }
+    return launch_kmajor(is_bf16, at, gt, out, k, n, m, where);
 }
 
 }  // namespace mx

@@ -188,7 +188,12 @@ void mx_clear_error(void) {
     c.cuda_error = 0;
     c.where[0] = 0;
 }
-int mx_device_synchronize(void) { return (int)cudaDeviceSynchronize(); }
+int mx_tc_gemm_status(void);
+int mx_device_synchronize(void) {
+    int e = (int)cudaDeviceSynchronize();
+    if (e == 0) mx_tc_gemm_status();  // surfaces a tensor-core kernel whose bounded waits ran out
+    return e;
+}
 int mx_metadata_table_size(void) {
     std::lock_guard<std::mutex> lk(g_meta_mutex);
     return (int)g_meta_table.size();

@@ -47,6 +47,10 @@ def fwd_cases():
     add("rank1-a-strided", [3, 4], [5], [5, 4], ast=[2], alen=9)           # literal: A indexed by k only, rows repeat
     add("rank1-b-strided", [6, 4], [6, 5], [4], bst=[2], blen=7)           # literal: B indexed by n only
     add("sliced-a-skips", [6, 1], [6, 4], [4, 1], ast=[16, 1])             # indices >= num_els * k are dropped
+    # large enough for the tensor-core path (bf16 / f16): ragged M, N, K tiles; NT and NN operand layouts
+    add("tc-nt", [200, 264], [200, 392], [392, 264], bst=[1, 392])
+    add("tc-nt-tiles", [384, 512], [384, 256], [256, 512], bst=[1, 256])
+    add("tc-nn", [136, 520], [136, 320], [320, 520])
     return out
 
 
@@ -85,6 +89,7 @@ def bwd_cases():
         ("batched", [3, 10, 7], [3, 10, 12], [3, 12, 7], 2, 0),
         ("mat-vec", [9, 1], [9, 14], [14, 1], 0, 3),
         ("vec-mat", [1, 6], [1, 11], [11, 6], 0, 0),
+        ("tc", [264, 256], [264, 384], [384, 256], 0, 0),   # tensor-core path for bf16 / f16
     ]
 
 
