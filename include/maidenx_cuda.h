@@ -225,6 +225,39 @@ int mx_tc_gemm_status(void);
 /* Number of metadata blocks currently remembered by cuda_memcpy_h2d (diagnostics). */
 int mx_metadata_table_size(void);
 
+/* ---- fused elementwise passes of the training step (bf16, f16, f32) --------------------------
+ * Each stands for a chain of single-op calls the reference's autograd issues; formulas and the
+ * reference lines they follow are in maidenx_b200/csrc/fused.cu.  All pointers are device memory,
+ * 16-byte aligned; `bias` is one element. */
+#define MX_DECL_FUSED_T(T, ...)                                                                                         \
+    void mx_bias_gelu_##T(size_t n, const mx_##T* z, const mx_##T* bias, mx_##T* u, mx_##T* a /* may be NULL */);        \
+    void mx_gelu_backward_##T(size_t n, const mx_##T* dy, const mx_##T* u, mx_##T* du);                                  \
+    void mx_mse_loss_grad_##T(size_t n, const mx_##T* pred, const mx_##T* target, mx_##T* grad, float* loss);            \
+    void mx_sgd_update_##T(size_t n, float* w32, const mx_##T* grad, mx_##T* w16, float lr, float grad_scale);
+MX_DECL_FUSED_T(bf16, _)
+MX_DECL_FUSED_T(f16, _)
+MX_DECL_FUSED_T(f32, _)
+
+/* ---- MLP training step (the data-parallel workload; maidenx_b200/csrc/mlp.cu) ------------------
+ * L x [Linear(dim -> dim) + scalar bias, GELU between layers], MSE, SGD with f32 master weights.
+ * dtype: 0 = bf16, 1 = f16.  x, y: [batch, dim] device buffers.  The step is forward,
+ * loss_backward, then backward_layer(l) for l = L-1 .. 0 and sgd_layer(l); a data-parallel driver
+ * all-reduces mx_mlp_weight_grad(l) / mx_mlp_bias_grad(l) between the last two. */
+void* mx_mlp_create(int layers, size_t dim, size_t batch, int dtype, uint64_t seed);
+void mx_mlp_destroy(void* mlp);
+void mx_mlp_forward(void* mlp, const void* x);
+void mx_mlp_loss_backward(void* mlp, const void* y);
+void mx_mlp_backward_layer(void* mlp, int layer);
+void mx_mlp_sgd_layer(void* mlp, int layer, float lr, float grad_scale);
+void* mx_mlp_weight_grad(void* mlp, int layer);
+void* mx_mlp_bias_grad(void* mlp, int layer);
+float* mx_mlp_master_weight(void* mlp, int layer);
+float* mx_mlp_master_bias(void* mlp, int layer);
+void* mx_mlp_weight(void* mlp, int layer);
+void* mx_mlp_output(void* mlp);
+float* mx_mlp_loss_ptr(void* mlp);
+float mx_mlp_loss(void* mlp);
+
 #ifdef __cplusplus
 }
 #else

@@ -34,6 +34,20 @@ RUNTIME_SIGNATURES = {
     "mx_device_synchronize": ([], ctypes.c_int),
     "mx_metadata_table_size": ([], ctypes.c_int),
     "mx_tc_gemm_status": ([], ctypes.c_int),
+    "mx_mlp_create": ([ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int, ctypes.c_uint64], ctypes.c_void_p),
+    "mx_mlp_destroy": ([ctypes.c_void_p], None),
+    "mx_mlp_forward": ([ctypes.c_void_p, ctypes.c_void_p], None),
+    "mx_mlp_loss_backward": ([ctypes.c_void_p, ctypes.c_void_p], None),
+    "mx_mlp_backward_layer": ([ctypes.c_void_p, ctypes.c_int], None),
+    "mx_mlp_sgd_layer": ([ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_float], None),
+    "mx_mlp_weight_grad": ([ctypes.c_void_p, ctypes.c_int], ctypes.c_void_p),
+    "mx_mlp_bias_grad": ([ctypes.c_void_p, ctypes.c_int], ctypes.c_void_p),
+    "mx_mlp_master_weight": ([ctypes.c_void_p, ctypes.c_int], ctypes.c_void_p),
+    "mx_mlp_master_bias": ([ctypes.c_void_p, ctypes.c_int], ctypes.c_void_p),
+    "mx_mlp_weight": ([ctypes.c_void_p, ctypes.c_int], ctypes.c_void_p),
+    "mx_mlp_output": ([ctypes.c_void_p], ctypes.c_void_p),
+    "mx_mlp_loss_ptr": ([ctypes.c_void_p], ctypes.c_void_p),
+    "mx_mlp_loss": ([ctypes.c_void_p], ctypes.c_float),
 }
 
 
@@ -54,6 +68,13 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = res
+    P, S, F = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
+    for t in ("bf16", "f16", "f32"):
+        for name, args in (("mx_bias_gelu", [S, P, P, P, P]), ("mx_gelu_backward", [S, P, P, P]),
+                           ("mx_mse_loss_grad", [S, P, P, P, P]), ("mx_sgd_update", [S, P, P, P, F, F])):
+            fn = getattr(lib, f"{name}_{t}")
+            fn.argtypes = args
+            fn.restype = None
     _ops = sig.bind(lib, "cuda_")
     _lib = lib
     return lib

@@ -15,11 +15,12 @@
 // No cluster launch: every CTA issues its own (CTA-local) TMA loads; re-use comes from
 // L2 through the order in which output tiles are handed out (16 row-tiles per column sweep).
 //
-// The kernel computes D[M,N] = sum_k A[m,k] * B[n,k] with both operands K-major (row-major
-// [M,K] and [N,K]); this is the reference's forward x . W^T (crates/maidenx_nn/src/layers/linear.rs:74)
-// and its grad_a = g . B^T (crates/maidenx_cpu/src/ops/matmul.rs:208-216) directly.  Products whose
-// operands are laid out the other way (grad_b = A^T . g, plain [K,N] B) first transpose the
-// MN-major operand into scratch with a tiled copy.
+// The kernel computes D[M,N] = sum_k A[m,k] * B[n,k]; by default both operands are K-major (row-major
+// [M,K] and [N,K]): the reference's forward x . W^T (crates/maidenx_nn/src/layers/linear.rs:74) and
+// its grad_a = g . B^T (crates/maidenx_cpu/src/ops/matmul.rs:208-216).  Either operand may instead be
+// MN-major (row-major [K,M] / [K,N]): it is then loaded as 64-wide column chunks and described
+// to the tensor core with the MN-major descriptor form, which covers grad_b = A^T . g (:244-256)
+// and a plain [K,N] B without any transposed copy.
 //
 // Every mbarrier wait is bounded by a clock64() budget; on expiry the thread records an
 // error word, stops issuing work and falls through to the common exit, where TMEM is freed.
@@ -150,27 +151,35 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128 bytes with
-// the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the leading
-// byte offset is unused for swizzled K-major layouts.
-__device__ __forceinline__ uint64_t smem_desc_kmajor_sw128(uint32_t smem_addr) {
+// Shared-memory matrix descriptors, 128-byte swizzle.  Fields: start address >> 4 in bits
+// [0,14), leading byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), descriptor
+// version 1 (sm_100) at bit 46, layout type 2 (128-byte swizzle) in [61,64).
+//  * K-major tile (rows of 64 K-elements = 128 bytes): groups of 8 rows are 1024 bytes apart
+//    (stride byte offset); the leading byte offset is not used.  Advancing 16 elements along K
+//    stays inside the swizzled row: +32 bytes on the start address.
+//  * MN-major tile, stored as chunks of [64 K-rows x 64 MN-elements] (one TMA box each, 8 KB):
+//    groups of 8 K-rows are 1024 bytes apart (stride byte offset) and the next 64 MN-elements
+//    start 8192 bytes later (leading byte offset).  Advancing 16 elements along K = two groups
+//    of 8 K-rows: +2048 bytes on the start address.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);      // start address, bits [0,14)
-    d |= (uint64_t)1 << 16;                            // leading byte offset (ignored), bits [16,30)
-    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset, bits [32,46)
-    d |= (uint64_t)1 << 46;                            // descriptor version for sm_100
-    d |= (uint64_t)2 << 61;                            // layout: 128-byte swizzle
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(lbo_bytes >> 4) << 16;
+    d |= (uint64_t)(sbo_bytes >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
     return d;
 }
+constexpr int MN_CHUNK_BYTES = 64 * BK * 2;  // one [64 K-rows x 64 MN] box
 
-// Instruction descriptor of tcgen05.mma kind::f16: f32 accumulate, A and B both K-major.
-__host__ __device__ constexpr uint32_t make_idesc(bool is_bf16) {
+// Instruction descriptor of tcgen05.mma kind::f16 with f32 accumulation.
+__host__ __device__ constexpr uint32_t make_idesc(bool is_bf16, bool a_mn_major, bool b_mn_major) {
     uint32_t d = 0;
     d |= 1u << 4;                               // D format: f32
     d |= (is_bf16 ? 1u : 0u) << 7;              // A format: 0 = f16, 1 = bf16
     d |= (is_bf16 ? 1u : 0u) << 10;             // B format
-    d |= 0u << 15;                              // A major: K
-    d |= 0u << 16;                              // B major: K
+    d |= (a_mn_major ? 1u : 0u) << 15;          // A major: 0 = K, 1 = MN
+    d |= (b_mn_major ? 1u : 0u) << 16;          // B major
     d |= (uint32_t)(BN >> 3) << 17;             // N / 8
     d |= (uint32_t)(BM >> 4) << 24;             // M / 16
     return d;
@@ -180,6 +189,7 @@ struct TcParams {
     int M, N, K;
     int tiles_m, tiles_n, num_tiles, num_kb;
     int is_bf16;
+    int a_mn, b_mn;  // operand is MN-major in global memory ([K, MN] row-major) instead of K-major ([MN, K])
 };
 
 __device__ __forceinline__ void tile_coords(int tile, const TcParams& p, int& tm, int& tn) {
@@ -254,8 +264,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         break;
                     }
                     mbar_expect_tx(full_bar(stage), A_STAGE_BYTES + B_STAGE_BYTES);
-                    tma_load_2d(smem_base + SmemLayout::a + stage * A_STAGE_BYTES, &map_a, kb * BK, tm * BM, full_bar(stage));
-                    tma_load_2d(smem_base + SmemLayout::b + stage * B_STAGE_BYTES, &map_b, kb * BK, tn * BN, full_bar(stage));
+                    const uint32_t sa = smem_base + SmemLayout::a + stage * A_STAGE_BYTES;
+                    const uint32_t sb = smem_base + SmemLayout::b + stage * B_STAGE_BYTES;
+                    if (!p.a_mn) {
+                        tma_load_2d(sa, &map_a, kb * BK, tm * BM, full_bar(stage));
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < BM / 64; h++) tma_load_2d(sa + h * MN_CHUNK_BYTES, &map_a, tm * BM + h * 64, kb * BK, full_bar(stage));
+                    }
+                    if (!p.b_mn) {
+                        tma_load_2d(sb, &map_b, kb * BK, tn * BN, full_bar(stage));
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < BN / 64; h++) tma_load_2d(sb + h * MN_CHUNK_BYTES, &map_b, tn * BN + h * 64, kb * BK, full_bar(stage));
+                    }
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1;
@@ -266,7 +288,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = make_idesc(p.is_bf16 != 0);
+            const uint32_t idesc = make_idesc(p.is_bf16 != 0, p.a_mn != 0, p.b_mn != 0);
+            // per-operand descriptor geometry: (leading, stride) byte offsets and the K step in 16-byte units
+            const uint32_t a_lbo = p.a_mn ? MN_CHUNK_BYTES : 16, b_lbo = p.b_mn ? MN_CHUNK_BYTES : 16;
+            const uint64_t a_kstep = p.a_mn ? (2048 >> 4) : (32 >> 4), b_kstep = p.b_mn ? (2048 >> 4) : (32 >> 4);
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
@@ -280,13 +305,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         break;
                     }
                     tc_fence_after();
-                    const uint64_t da = smem_desc_kmajor_sw128(smem_base + SmemLayout::a + stage * A_STAGE_BYTES);
-                    const uint64_t db = smem_desc_kmajor_sw128(smem_base + SmemLayout::b + stage * B_STAGE_BYTES);
+                    const uint64_t da = smem_desc_sw128(smem_base + SmemLayout::a + stage * A_STAGE_BYTES, a_lbo, 1024);
+                    const uint64_t db = smem_desc_sw128(smem_base + SmemLayout::b + stage * B_STAGE_BYTES, b_lbo, 1024);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++) {
-                        // advance 16 elements (32 bytes) along K inside the swizzled row: +2 in the address field
-                        umma_f16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb | k) != 0);
-                    }
+                    for (int k = 0; k < BK / UMMA_K; k++) umma_f16(d_tmem, da + a_kstep * k, db + b_kstep * k, idesc, (kb | k) != 0);
                     umma_commit(empty_bar(stage));  // the stage may be refilled once these MMAs have read it
                     if (++stage == STAGES) {
                         stage = 0;
@@ -376,26 +398,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------
-// K-major copy of an MN-major operand: dst[c][r] = src[r][c] for a [rows, cols] matrix
-// ---------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) transpose16_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int rows, int cols,
-                                                         long long src_batch, long long dst_batch) {
-    __shared__ uint16_t tile[64][66];
-    src += (long long)blockIdx.z * src_batch;
-    dst += (long long)blockIdx.z * dst_batch;
-    const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
-    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
-        int r = i / 64, c = i % 64;
-        if (r0 + r < rows && c0 + c < cols) tile[r][c] = src[(long long)(r0 + r) * cols + c0 + c];
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
-        int c = i / 64, r = i % 64;
-        if (r0 + r < rows && c0 + c < cols) dst[(long long)(c0 + c) * rows + r0 + r] = tile[r][c];
-    }
-}
-
-// ---------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -451,12 +453,15 @@ DeviceState* device_state() {
     return &s;
 }
 
-// D[M,N] = A[M,K] . B[N,K]^T, all row-major and dense.
-bool launch_kmajor(bool is_bf16, const void* A, const void* B, void* D, uint64_t M, uint64_t N, uint64_t K, const char* where) {
+// D[M,N] = sum_k Aop[m,k] * Bop[n,k].  A K-major operand is a dense row-major [MN, K] matrix, an
+// MN-major operand a dense row-major [K, MN] matrix; D is dense row-major [M, N].
+bool launch_gemm(bool is_bf16, const void* A, bool a_mn, const void* B, bool b_mn, void* D, uint64_t M, uint64_t N, uint64_t K, const char* where) {
     DeviceState* st = device_state();
     if (!st) return false;
     CUtensorMap ma, mb, md;
-    if (!make_map(&ma, is_bf16, A, M, K, BM) || !make_map(&mb, is_bf16, B, N, K, BN) || !make_map(&md, is_bf16, D, M, N, 32)) return false;
+    const bool oka = a_mn ? make_map(&ma, is_bf16, A, K, M, 64) : make_map(&ma, is_bf16, A, M, K, BM);
+    const bool okb = b_mn ? make_map(&mb, is_bf16, B, K, N, 64) : make_map(&mb, is_bf16, B, N, K, BN);
+    if (!oka || !okb || !make_map(&md, is_bf16, D, M, N, 32)) return false;
     TcParams p;
     p.M = (int)M;
     p.N = (int)N;
@@ -466,6 +471,8 @@ bool launch_kmajor(bool is_bf16, const void* A, const void* B, void* D, uint64_t
     p.num_tiles = p.tiles_m * p.tiles_n;
     p.num_kb = (int)((K + BK - 1) / BK);
     p.is_bf16 = is_bf16 ? 1 : 0;
+    p.a_mn = a_mn ? 1 : 0;
+    p.b_mn = b_mn ? 1 : 0;
     int grid = sm_count();
     if (grid > p.num_tiles) grid = p.num_tiles;
     tc_gemm_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx().stream>>>(ma, mb, md, p, st->err);
@@ -473,14 +480,15 @@ bool launch_kmajor(bool is_bf16, const void* A, const void* B, void* D, uint64_t
     return true;
 }
 
-bool eligible(uint64_t M, uint64_t N, uint64_t K, const void* a, const void* b, const void* d) {
-    // TMA: 16-byte aligned bases and row pitches; sizes must fit the int coordinates
+// TMA wants 16-byte aligned bases and row pitches: the contiguous extent of every matrix
+// (K for K-major operands, MN for MN-major ones, N for D) must be a multiple of 8 elements.
+bool eligible(uint64_t M, uint64_t N, uint64_t K, bool a_mn, bool b_mn, const void* a, const void* b, const void* d) {
     if (M == 0 || N == 0 || K == 0) return false;
-    if (K % 8 != 0 || N % 8 != 0) return false;
+    if (N % 8 != 0) return false;
+    if ((a_mn ? M : K) % 8 != 0 || (b_mn ? N : K) % 8 != 0) return false;
     if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)d) % 16 != 0) return false;
     if (M > 0x7FFFFFFFull || N > 0x7FFFFFFFull || K > 0x7FFFFFFFull) return false;
-    // small problems are not worth a persistent launch
-    if (M * N * K < (1ull << 24)) return false;
+    if (M * N * K < (1ull << 24)) return false;  // small problems are not worth a persistent launch
     return true;
 }
 
@@ -509,62 +517,37 @@ bool tc_gemm_bf16_f16(bool is_bf16, const MmDesc& d, int which, size_t num_els, 
         if (num_els != m * n) return false;  // batched products stay on the SIMT path
         const char* A = static_cast<const char*>(x) + d.a_off * es;
         const char* B = static_cast<const char*>(y) + d.b_off * es;
-        bool a_kmajor, b_kmajor, b_mnmajor;
+        bool a_kmajor, a_mnmajor, b_kmajor, b_mnmajor;
         if (d.a_cont && d.b_cont) {
             // the reference's contiguous branch: A is [m, k], B is [k, n], both dense
             a_kmajor = true;
+            a_mnmajor = false;
             b_kmajor = false;
             b_mnmajor = true;
         } else {
             // strided branch: A[m * as1 + k * as2], B[k * bs1 + n * bs2]
             a_kmajor = d.a_strides[2] == 1 && d.a_strides[1] == (int64_t)k;
+            a_mnmajor = d.a_strides[1] == 1 && d.a_strides[2] == (int64_t)m;  // transposed view of a dense [k, m] matrix
             b_kmajor = d.b_strides[1] == 1 && d.b_strides[2] == (int64_t)k;   // transposed view of a dense [n, k] matrix
             b_mnmajor = d.b_strides[2] == 1 && d.b_strides[1] == (int64_t)n;  // dense [k, n]
         }
-        if (!a_kmajor) return false;
-        if (b_kmajor) {
-            if (!eligible(m, n, k, A, B, out)) return false;
-            return launch_kmajor(is_bf16, A, B, out, m, n, k, where);
-        }
-        if (b_mnmajor) {
-            if (!eligible(m, n, k, A, out, out)) return false;
-            dim3 grid((unsigned)((n + 63) / 64), (unsigned)((k + 63) / 64), 1);
-            if (grid.y > 65535) return false;
-            uint16_t* bt = static_cast<uint16_t*>(scratch(n * k * es));
-            if (!bt) return false;
-            transpose16_kernel<<<grid, 256, 0, ctx().stream>>>(reinterpret_cast<const uint16_t*>(B), bt, (int)k, (int)n, 0, 0);
-            return launch_kmajor(is_bf16, A, bt, out, m, n, k, where);
-        }
-        return false;
+        if (!(a_kmajor || a_mnmajor) || !(b_kmajor || b_mnmajor)) return false;
+        const bool a_mn = !a_kmajor, b_mn = !b_kmajor;
+        if (!eligible(m, n, k, a_mn, b_mn, A, B, out)) return false;
+        return launch_gemm(is_bf16, A, a_mn, B, b_mn, out, m, n, k, where);
     }
     // backward products read g, A and B as dense row-major matrices (strides ignored)
     if (d.out_nd != 2) return false;
     const uint64_t m = d.m, n = d.n, k = d.k_bwd;
-    if (d.g_size != m * n) return false;
+    if (d.g_size != m * n || nea != m * k || neb != k * n) return false;
     if (which == 1) {
-        // grad_a[m, k] = sum_n g[m, n] * B[k, n]: both operands K-major (K here is n)
-        if (nea != m * k || neb != k * n) return false;
-        if (!eligible(m, k, n, x, y, out)) return false;
-        return launch_kmajor(is_bf16, x, y, out, m, k, n, where);
+        // grad_a[m, k] = sum_n g[m, n] * B[k, n]: reduction over n, both operands K-major
+        if (!eligible(m, k, n, false, false, x, y, out)) return false;
+        return launch_gemm(is_bf16, x, false, y, false, out, m, k, n, where);
     }
-    // grad_b[k, n] = sum_m A[m, k] * g[m, n]: both operands MN-major; transpose both into scratch
-    if (nea != m * k || neb != k * n) return false;
-    if (!eligible(k, n, m, out, out, out) || m % 8 != 0) return false;
-    uint16_t* buf = static_cast<uint16_t*>(scratch((m * k + m * n) * es + 256));
-    if (!buf) return false;
-    uint16_t* at = buf;                                        // [k, m]
-    uint16_t* gt = buf + ((m * k + 127) / 128) * 128;          // [n, m], 256-byte aligned
-    {
-        dim3 grid((unsigned)((k + 63) / 64), (unsigned)((m + 63) / 64), 1);
-        if (grid.y > 65535) return false;
-        transpose16_kernel<<<grid, 256, 0, ctx().stream>>>(static_cast<const uint16_t*>(y), at, (int)m, (int)k, 0, 0);
-    }
-    {
-        dim3 grid((unsigned)((n + 63) / 64), (unsigned)((m + 63) / 64), 1);
-        if (grid.y > 65535) return false;
-        transpose16_kernel<<<grid, 256, 0, ctx().stream>>>(static_cast<const uint16_t*>(x), gt, (int)m, (int)n, 0, 0);
-    }
-    return launch_kmajor(is_bf16, at, gt, out, k, n, m, where);
+    // grad_b[k, n] = sum_m A[m, k] * g[m, n]: reduction over m, both operands MN-major
+    if (!eligible(k, n, m, true, true, y, x, out)) return false;
+    return launch_gemm(is_bf16, y, true, x, true, out, k, n, m, where);
 }
 
 }  // namespace mx

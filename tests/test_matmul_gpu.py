@@ -51,6 +51,8 @@ def fwd_cases():
     add("tc-nt", [200, 264], [200, 392], [392, 264], bst=[1, 392])
     add("tc-nt-tiles", [384, 512], [384, 256], [256, 512], bst=[1, 256])
     add("tc-nn", [136, 520], [136, 320], [320, 520])
+    add("tc-tn", [264, 256], [264, 392], [392, 256], ast=[1, 264])          # A is the transposed view of a [392, 264] matrix
+    add("tc-tt", [256, 264], [256, 384], [384, 264], ast=[1, 256], bst=[1, 384])
     return out
 
 

@@ -1,0 +1,156 @@
+"""The MLP training step (csrc/mlp.cu + fused kernels) checked on a B200:
+  * the fused elementwise passes against the chain of single-op C-ABI calls they stand for,
+    which in turn is checked against the CPU oracle elsewhere;
+  * one whole step (forward, loss, every gradient, SGD update) against an f64 numpy evaluation
+    of the same model from the same seeded weights, within bf16 tolerance;
+  * the loss goes down over a few steps.
+Sizes are small enough for numpy but large enough (M*N*K >= 2^24) that every matrix product
+runs on the tensor-core path.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+import harness as H
+from maidenx_b200 import _lib, device
+from maidenx_b200 import dtypes as D
+
+pytestmark = pytest.mark.gpu
+SZ = ctypes.c_size_t
+
+
+def _splitmix64(x):
+    x = (x + np.uint64(0x9E3779B97F4A7C15))
+    x = (x ^ (x >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+    x = (x ^ (x >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+    return x ^ (x >> np.uint64(31))
+
+
+def init_uniform(seed, n, bound):
+    """The engine's counter-based initialiser (mlp.cu: splitmix64 of seed * 0x100000001B3 + i)."""
+    with np.errstate(over="ignore"):
+        i = np.arange(n, dtype=np.uint64)
+        r = _splitmix64(np.uint64(seed) * np.uint64(0x100000001B3) + i)
+    u = (r >> np.uint64(40)).astype(np.float32) * np.float32(1.0 / 16777216.0)
+    return (np.float32(2.0) * u - np.float32(1.0)) * np.float32(bound)
+
+
+def gelu64(x):
+    return 0.5 * x * (1.0 + np.tanh(0.7978845608028654 * (x + 0.044715 * x ** 3)))
+
+
+def gelu_grad64(x):
+    s, c = 0.7978845608028654, 0.044715
+    t = np.tanh(s * (x + c * x ** 3))
+    return 0.5 * (1 + t) + 0.5 * x * (1 - t * t) * s * (1 + 3 * c * x * x)
+
+
+def bf(x):
+    """Round an array to bf16 and back (f64 result)."""
+    return D.decode(D.encode(np.asarray(x, dtype=np.float32), D.BF16), D.BF16)
+
+
+def test_fused_passes_match_the_single_op_chain(cuda):
+    lib = _lib.load()
+    rng = np.random.default_rng(0)
+    n = 40_000
+    dt = D.BF16
+    z = H.random_store(rng, dt, n, dist="normal")
+    b = D.encode([0.37], dt)
+    # chain: add with a broadcast scalar rhs, then gelu
+    u_ref = H.run_binary(cuda, "add", dt, [n], [1], [0], 0, 0, z, b)
+    a_ref = H.run_unary(cuda, "gelu", dt, [n], [1], 0, u_ref)
+    zb, bb = device.CudaBuffer.from_host(z), device.CudaBuffer.from_host(np.resize(b, 128))
+    ub, ab = device.CudaBuffer(n * 2), device.CudaBuffer(n * 2)
+    lib.mx_bias_gelu_bf16(n, zb.ptr, bb.ptr, ub.ptr, ab.ptr)
+    device.synchronize()
+    assert np.array_equal(ub.to_host(np.uint16, n), u_ref) and np.array_equal(ab.to_host(np.uint16, n), a_ref)
+    # gelu backward against f64
+    dy = H.random_store(rng, dt, n, dist="normal")
+    dyb, dub = device.CudaBuffer.from_host(dy), device.CudaBuffer(n * 2)
+    lib.mx_gelu_backward_bf16(n, dyb.ptr, ub.ptr, dub.ptr)
+    device.synchronize()
+    want = D.decode(dy, dt) * gelu_grad64(D.decode(u_ref, dt))
+    got = D.decode(dub.to_host(np.uint16, n), dt)
+    assert np.all(np.abs(got - want) <= 1e-2 * np.maximum(np.abs(want), np.abs(D.decode(dy, dt)) * 1e-1))
+    # mse: loss and gradient
+    p, t = H.random_store(rng, dt, n, dist="normal"), H.random_store(rng, dt, n, dist="normal")
+    pb, tb, gb, lb = device.CudaBuffer.from_host(p), device.CudaBuffer.from_host(t), device.CudaBuffer(n * 2), device.CudaBuffer(256)
+    lib.mx_mse_loss_grad_bf16(n, pb.ptr, tb.ptr, gb.ptr, lb.ptr)
+    device.synchronize()
+    diff = bf(D.decode(p, dt) - D.decode(t, dt))
+    assert np.isclose(lb.to_host(np.float32, 1)[0], np.mean(diff ** 2), rtol=1e-5)
+    assert np.allclose(D.decode(gb.to_host(np.uint16, n), dt), bf(diff * 2.0 / n), rtol=1e-2, atol=0)
+    # sgd: f32 master minus step, bf16 copy
+    w32 = rng.standard_normal(n).astype(np.float32)
+    wb, w16b = device.CudaBuffer.from_host(w32), device.CudaBuffer(n * 2)
+    lib.mx_sgd_update_bf16(n, wb.ptr, dyb.ptr, w16b.ptr, ctypes.c_float(0.25), ctypes.c_float(0.5))
+    device.synchronize()
+    want32 = w32 - np.float32(0.125) * D.decode(dy, dt).astype(np.float32)
+    got32 = wb.to_host(np.float32, n)
+    assert np.array_equal(got32, want32)
+    assert np.array_equal(w16b.to_host(np.uint16, n), D.encode(want32, dt))
+    for x in (zb, bb, ub, ab, dyb, dub, pb, tb, gb, lb, wb, w16b):
+        x.free()
+    assert device.last_error() is None
+
+
+def test_one_training_step_matches_f64_model(cuda):
+    from maidenx_b200.mlp import Mlp
+    L, Dm, B, seed, lr = 3, 256, 512, 6, 0.05
+    rng = np.random.default_rng(4)
+    dt = D.BF16
+    x, y = H.random_store(rng, dt, B * Dm, dist="normal"), H.random_store(rng, dt, B * Dm, dist="normal")
+    xb, yb = device.CudaBuffer.from_host(x), device.CudaBuffer.from_host(y)
+    m = Mlp(L, Dm, B, "bf16", seed)
+    # reference model in f64 from the same seeded weights (rounded to bf16 as the engine's working copy is)
+    bound = 1.0 / np.sqrt(np.float32(Dm))
+    W32 = [init_uniform(seed + 2 * l, Dm * Dm, bound).reshape(Dm, Dm) for l in range(L)]
+    b32 = [init_uniform(seed + 2 * l + 1, 1, bound)[0] for l in range(L)]
+    W = [bf(w) for w in W32]
+    bs = [float(bf([b])[0]) for b in b32]
+    a = [D.decode(x, dt).reshape(B, Dm)]
+    us = []
+    for l in range(L):
+        u = bf(bf(a[-1] @ W[l].T) + bs[l])
+        us.append(u)
+        a.append(bf(gelu64(u)) if l < L - 1 else u)
+    diff = bf(us[-1] - D.decode(y, dt).reshape(B, Dm))
+    loss = np.mean(diff ** 2)
+    du = bf(diff * 2.0 / (B * Dm))
+    gW, gb = [None] * L, [None] * L
+    for l in reversed(range(L)):
+        if l < L - 1:
+            du = bf(da * gelu_grad64(us[l]))
+        gW[l] = du.T @ a[l]
+        gb[l] = du.sum()
+        da = bf(du @ W[l])
+    m.train_step(xb.ptr, yb.ptr, lr)
+    device.synchronize()
+    assert device.last_error() is None and _lib.load().mx_tc_gemm_status() == 0
+    assert np.isclose(m.loss(), loss, rtol=2e-3)
+    out = D.decode(device_read(m.ptr("output"), np.uint16, B * Dm), dt).reshape(B, Dm)
+    assert np.all(np.abs(out - us[-1]) <= 2e-2 * np.maximum(np.abs(us[-1]), 0.25))
+    for l in range(L):
+        g = D.decode(device_read(m.ptr("weight_grad", l), np.uint16, Dm * Dm), dt).reshape(Dm, Dm)
+        scale = np.abs(gW[l]).max()
+        assert np.all(np.abs(g - gW[l]) <= 2e-2 * np.maximum(np.abs(gW[l]), 0.1 * scale)), f"dW layer {l}"
+        gbias = D.decode(device_read(m.ptr("bias_grad", l), np.uint16, 1), dt)[0]
+        assert abs(gbias - gb[l]) <= 2e-2 * max(abs(gb[l]), 1e-3), f"db layer {l}"
+        w_after = device_read(m.ptr("master_weight", l), np.float32, Dm * Dm).reshape(Dm, Dm)
+        assert np.array_equal(w_after, W32[l] - np.float32(lr) * g.astype(np.float32)), f"SGD layer {l}"
+    # the loss goes down
+    first = m.loss()
+    for _ in range(5):
+        m.train_step(xb.ptr, yb.ptr, lr)
+    assert m.loss() < first
+    m.close()
+    xb.free()
+    yb.free()
+
+
+def device_read(ptr, np_dtype, count):
+    out = np.empty(count, dtype=np_dtype)
+    assert _lib.load().cuda_memcpy_d2h(out.ctypes.data, ptr, out.nbytes) == 0
+    return out
