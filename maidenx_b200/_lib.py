@@ -34,6 +34,7 @@ RUNTIME_SIGNATURES = {
     "mx_device_synchronize": ([], ctypes.c_int),
     "mx_metadata_table_size": ([], ctypes.c_int),
     "mx_tc_gemm_status": ([], ctypes.c_int),
+    "mx_sum_f32_noalloc": ([ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p], None),
     "mx_mlp_create": ([ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int, ctypes.c_uint64], ctypes.c_void_p),
     "mx_mlp_destroy": ([ctypes.c_void_p], None),
     "mx_mlp_forward": ([ctypes.c_void_p, ctypes.c_void_p], None),
