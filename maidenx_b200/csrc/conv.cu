@@ -16,6 +16,7 @@
 // pre-zeroed buffer).  `num_els` bounds the readable part of col: entries at or beyond it
 // are skipped, as the CPU backend does (conv.rs:135).
 #include "abi_common.cuh"
+#include "conv_s1.cuh"
 #include "ops.cuh"
 
 #ifndef MX_T
@@ -161,6 +162,31 @@ void im2col_entry(size_t num_els, const size_t* meta, const T* x, T* col, const 
     const bool vec = ((uintptr_t)col % 16 == 0) && ((uint64_t)P.OH * P.OW) % VEC == 0;
     cudaStream_t s = ctx().stream;
     const unsigned grid = (unsigned)planes_touched;
+    // stride-1 fast path (conv_s1.cuh)
+    if (P.SH == 1 && P.SW == 1 && vec && P.OW % VEC == 0 && num_els == planes * chunk && (int)P.KW - 1 <= VEC &&
+        (uint64_t)P.OW + P.KW == (uint64_t)P.W + 2 * P.PW + 1 && (uint64_t)P.OH + P.KH == (uint64_t)P.H + 2 * P.PH + 1) {
+        ConvS1Params Q;
+        Q.H = P.H; Q.W = P.W; Q.KH = P.KH; Q.OH = P.OH; Q.OW = P.OW; Q.PH = P.PH; Q.PW = P.PW;
+        Q.owv = P.OW / VEC;
+        uint32_t need = (Q.owv + 1) * VEC, wide = (P.W + 2 * P.PW + VEC - 1) / VEC * VEC;
+        Q.pitch = need > wide ? need : wide;
+        Q.num_els = num_els;
+        const size_t smem = (size_t)(P.H + 2 * P.PH) * Q.pitch * sizeof(T);
+        auto go = [&](auto kernel) {
+            if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            kernel<<<grid, kConvS1Threads, smem, s>>>(x, col, Q);
+            check_launch(where);
+        };
+        if (smem <= 200 * 1024) {
+            switch (P.KW) {
+                case 1: go(im2col_s1_kernel<T, VEC, 1>); return;
+                case 3: if (VEC >= 2) { go(im2col_s1_kernel<T, VEC, 3>); return; } break;
+                case 5: if (VEC >= 4) { go(im2col_s1_kernel<T, VEC, 5>); return; } break;
+                case 7: if (VEC >= 8) { go(im2col_s1_kernel<T, VEC, 7>); return; } break;
+                default: break;
+            }
+        }
+    }
     if (plane_bytes <= 200 * 1024) {
         auto launch = [&](auto kernel) {
             if (plane_bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plane_bytes);
@@ -186,8 +212,36 @@ void col2im_entry(size_t num_els, const size_t* meta, const T* col, T* out, cons
         set_error(kErrUnsupported, 0, where);
         return;
     }
-    // grid.y carries the plane index; fold very large plane counts into several launches
     cudaStream_t s = ctx().stream;
+    // stride-1 fast path (conv_s1.cuh)
+    {
+        constexpr int VEC = 16 / sizeof(T);
+        const int kw = (int)P.KW, pw = (int)P.PW;
+        const bool shape_ok = P.SH == 1 && P.SW == 1 && P.W % VEC == 0 && P.OW % VEC == 0 && num_els % VEC == 0 &&
+                              ((uintptr_t)col | (uintptr_t)out) % 16 == 0 && planes <= 65535 && pw < VEC && kw - 1 - pw < VEC && kw - 1 - pw >= 0 &&
+                              (uint64_t)P.OW + P.KW == (uint64_t)P.W + 2 * P.PW + 1 && (uint64_t)P.OH + P.KH == (uint64_t)P.H + 2 * P.PH + 1;
+        if (shape_ok) {
+            ConvS1Params Q;
+            Q.H = P.H; Q.W = P.W; Q.KH = P.KH; Q.OH = P.OH; Q.OW = P.OW; Q.PH = P.PH; Q.PW = P.PW;
+            Q.pitch = 0;
+            Q.owv = P.OW / VEC;
+            Q.num_els = num_els;
+            const uint32_t items = P.H * (P.W / VEC);
+            dim3 grid((items + kConvS1Threads - 1) / kConvS1Threads, (unsigned)planes);
+            bool done = true;
+            if (kw == 1 && pw == 0) col2im_s1_kernel<T, VEC, 1, 0><<<grid, kConvS1Threads, 0, s>>>(col, out, Q);
+            else if (kw == 3 && pw == 1) col2im_s1_kernel<T, VEC, 3, 1><<<grid, kConvS1Threads, 0, s>>>(col, out, Q);
+            else if (kw == 3 && pw == 0 && VEC > 2) col2im_s1_kernel<T, VEC, 3, 0><<<grid, kConvS1Threads, 0, s>>>(col, out, Q);
+            else if (kw == 5 && pw == 2 && VEC > 2) col2im_s1_kernel<T, VEC, 5, 2><<<grid, kConvS1Threads, 0, s>>>(col, out, Q);
+            else if (kw == 7 && pw == 3 && VEC > 3) col2im_s1_kernel<T, VEC, 7, 3><<<grid, kConvS1Threads, 0, s>>>(col, out, Q);
+            else done = false;
+            if (done) {
+                check_launch(where);
+                return;
+            }
+        }
+    }
+    // grid.y carries the plane index; fold very large plane counts into several launches
     const unsigned gx = (unsigned)((HW + kConvThreads - 1) / kConvThreads);
     for (uint64_t p0 = 0; p0 < planes; p0 += 65535) {
         uint64_t cnt = planes - p0 < 65535 ? planes - p0 : 65535;

@@ -66,10 +66,27 @@ __device__ __forceinline__ Vec<T, N> splat(T x) {
 template <class F, class T, class O, int NIN, int VEC>
 __device__ __forceinline__ Vec<O, VEC> apply_vec(const F& f, const Vec<T, VEC>& a, const Vec<T, VEC>& b) {
     Vec<O, VEC> r;
+    if constexpr (F::kCore && VEC % 2 == 0) {
+        // 16-bit floats: unpack / compute in f32 / round two elements at a time
+        const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
+        const uint32_t* bw = reinterpret_cast<const uint32_t*>(&b);
+        uint32_t* rw = reinterpret_cast<uint32_t*>(&r);
 #pragma unroll
-    for (int i = 0; i < VEC; i++) {
-        if constexpr (NIN == 2) r.v[i] = f(a.v[i], b.v[i]);
-        else r.v[i] = f(a.v[i]);
+        for (int i = 0; i < VEC / 2; i++) {
+            float2 x = unpack2<T>(aw[i]);
+            if constexpr (NIN == 2) {
+                float2 y = unpack2<T>(bw[i]);
+                rw[i] = pack2_rn<T>(f.core(x.x, y.x), f.core(x.y, y.y));
+            } else {
+                rw[i] = pack2_rn<T>(f.core(x.x), f.core(x.y));
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; i++) {
+            if constexpr (NIN == 2) r.v[i] = f(a.v[i], b.v[i]);
+            else r.v[i] = f(a.v[i]);
+        }
     }
     return r;
 }
@@ -160,6 +177,31 @@ __global__ void __launch_bounds__(kEwThreads, 4) ew_row_long_kernel(F f, const T
     }
 }
 
+// Unary op whose input is one row broadcast over every outer dim (strides [0, ..., 0, 1]):
+// f(broadcast(x)) == broadcast(f(x)), so each thread evaluates its vectors once and stores
+// them to a slab of output rows — the kernel is a pure store stream.
+template <class F, class T, class O, int VEC>
+__global__ void __launch_bounds__(kEwThreads) ew_bcast_rows_kernel(F f, const T* a, O* out, uint32_t qv, uint32_t rows, uint32_t rows_per_block) {
+    const uint32_t v0 = blockIdx.x * (kEwThreads * kEwUnroll) + threadIdx.x;
+    const uint32_t r0 = blockIdx.y * rows_per_block;
+    const uint32_t r1 = min(rows, r0 + rows_per_block);
+    Vec<O, VEC> res[kEwUnroll];
+    Vec<T, VEC> dummy;
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; u++) {
+        uint32_t v = v0 + u * kEwThreads;
+        if (v < qv) res[u] = apply_vec<F, T, O, 1, VEC>(f, ld_vec<T, VEC>(a + (size_t)v * VEC), dummy);
+    }
+    for (uint32_t r = r0; r < r1; r++) {
+        O* dst = out + (size_t)r * qv * VEC;
+#pragma unroll
+        for (int u = 0; u < kEwUnroll; u++) {
+            uint32_t v = v0 + u * kEwThreads;
+            if (v < qv) st_vec<O, VEC>(dst + (size_t)v * VEC, res[u]);
+        }
+    }
+}
+
 // Short rows: one fast-divmod per vector to find its row.
 template <class F, class T, class O, int NIN, int VEC>
 __global__ void __launch_bounds__(kEwThreads) ew_row_kernel(F f, const T* a, const T* b, O* out, EwRowParams P) {
@@ -245,10 +287,25 @@ __global__ void __launch_bounds__(kEwThreads, 4) ew_tile_kernel(F f, const T* a,
     for (int k = 0; k < 3; k++) base[k] += (int64_t)p0 * P.st_p[k] + (int64_t)q0 * P.st_q[k];
     const T* in[2] = {a, b};
 
+    // Phase-2 work item: RP consecutive p-rows x one vector along q.  For 2-byte types two rows
+    // are handled together, so that one 32-bit shared-memory read (two neighbouring p of one q)
+    // feeds both: half the shared-memory instructions of a row-at-a-time walk.
+    constexpr int RP = (sizeof(T) == 2 && VEC == 8) ? 2 : 1;
+    constexpr int ITER2 = ((TILE / RP) * VPR + kEwThreads - 1) / kEwThreads;
+    auto item_coord = [](int i, int& prow, int& qv) {
+        if constexpr (RP == 2) {  // a warp covers 8 vectors (128 bytes) x 4 row pairs
+            int w = i >> 5, lane = i & 31;
+            qv = lane & 7;
+            prow = (w * 4 + (lane >> 3)) * 2;
+        } else {
+            ew_tile_coord<VPR, VEC>(i, prow, qv);
+        }
+    };
+
     // All global loads of the tile are issued before the barrier: the direct operands in
     // the phase-2 mapping (rows along p, vectors along q), the transposed operands in the
     // phase-1 mapping (rows along q, vectors along p, their unit-stride dim).
-    Vec<T, VEC> direct[NIN][ITER];
+    Vec<T, VEC> direct[NIN][ITER2][RP];
     Vec<T, VEC> staged[NIN][ITER];
 #pragma unroll
     for (int x = 0; x < NIN; x++) {
@@ -263,12 +320,15 @@ __global__ void __launch_bounds__(kEwThreads, 4) ew_tile_kernel(F f, const T* a,
         } else {
             const T* src = in[x] + base[x + 1];
 #pragma unroll
-            for (int it = 0; it < ITER; it++) {
+            for (int it = 0; it < ITER2; it++) {
                 int pp, qv;
-                ew_tile_coord<VPR, VEC>(threadIdx.x + it * kEwThreads, pp, qv);
-                if (pp < TILE && p0 + pp < P.P && q0 + qv * VEC < P.Q) {
-                    const T* s = src + (int64_t)pp * P.st_p[x + 1];
-                    direct[x][it] = P.st_q[x + 1] ? ld_vec<T, VEC>(s + qv * VEC) : splat<T, VEC>(s[0]);
+                item_coord(threadIdx.x + it * kEwThreads, pp, qv);
+#pragma unroll
+                for (int r = 0; r < RP; r++) {
+                    if (pp + r < TILE && p0 + pp + r < P.P && q0 + qv * VEC < P.Q) {
+                        const T* s = src + (int64_t)(pp + r) * P.st_p[x + 1];
+                        direct[x][it][r] = P.st_q[x + 1] ? ld_vec<T, VEC>(s + qv * VEC) : splat<T, VEC>(s[0]);
+                    }
                 }
             }
         }
@@ -299,22 +359,41 @@ __global__ void __launch_bounds__(kEwThreads, 4) ew_tile_kernel(F f, const T* a,
 
     // phase 2: walk the tile along q (the output's unit-stride dim)
 #pragma unroll
-    for (int it = 0; it < ITER; it++) {
+    for (int it = 0; it < ITER2; it++) {
         int pp, qv;
-        ew_tile_coord<VPR, VEC>(threadIdx.x + it * kEwThreads, pp, qv);
+        item_coord(threadIdx.x + it * kEwThreads, pp, qv);
         if (pp >= TILE || p0 + pp >= P.P || q0 + qv * VEC >= P.Q) continue;
-        Vec<T, VEC> v[2];
+        Vec<T, VEC> v[2][RP];
 #pragma unroll
         for (int x = 0; x < NIN; x++) {
             if (P.transposed[x + 1]) {
                 const unsigned char* buf = ew_smem + P.smem_slot[x + 1] * EwTile<T>::kBytes;
+                if constexpr (RP == 2) {
+                    // word j holds (q = qv*8 + j; p = pp, pp + 1): split the halves into the two rows
+                    uint32_t w[VEC];
 #pragma unroll
-                for (int j = 0; j < VEC; j++) v[x].v[j] = *reinterpret_cast<const T*>(buf + (qv * VEC + j) * PITCH + pp * (int)sizeof(T));
+                    for (int j = 0; j < VEC; j++) w[j] = *reinterpret_cast<const uint32_t*>(buf + (qv * VEC + j) * PITCH + pp * 2);
+                    uint32_t* r0 = reinterpret_cast<uint32_t*>(&v[x][0]);
+                    uint32_t* r1 = reinterpret_cast<uint32_t*>(&v[x][1]);
+#pragma unroll
+                    for (int j = 0; j < VEC / 2; j++) {
+                        r0[j] = __byte_perm(w[2 * j], w[2 * j + 1], 0x5410);
+                        r1[j] = __byte_perm(w[2 * j], w[2 * j + 1], 0x7632);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < VEC; j++) v[x][0].v[j] = *reinterpret_cast<const T*>(buf + (qv * VEC + j) * PITCH + pp * (int)sizeof(T));
+                }
             } else {
-                v[x] = direct[x][it];
+#pragma unroll
+                for (int r = 0; r < RP; r++) v[x][r] = direct[x][it][r];
             }
         }
-        st_vec<O, VEC>(out + base[0] + (int64_t)pp * P.st_p[0] + qv * VEC, apply_vec<F, T, O, NIN, VEC>(f, v[0], v[1]));
+#pragma unroll
+        for (int r = 0; r < RP; r++) {
+            if (p0 + pp + r < P.P)
+                st_vec<O, VEC>(out + base[0] + (int64_t)(pp + r) * P.st_p[0] + qv * VEC, apply_vec<F, T, O, NIN, VEC>(f, v[0][r], v[1][r]));
+        }
     }
 }
 
@@ -386,6 +465,20 @@ void ew_launch(const EwPlan& pl, const F& f, const T* a, const T* b, O* out, con
             EwRowParams P;
             ew_fill_row_params(pl, VEC, P);
             uint64_t rows = P.total_vecs / P.qv;
+            bool row_bcast = NIN == 1 && P.nd_outer == 1 && P.sq[1] == 1 && P.st[1][0] == 0 && P.st[0][0] == (int64_t)P.qv * VEC && rows >= 8;
+            if constexpr (NIN == 1) {
+                if (row_bcast) {
+                    // enough blocks to fill the GPU, each storing a slab of rows
+                    uint32_t want = (uint32_t)sm_count() * 8;
+                    uint32_t gy = (want + P.chunks_per_row - 1) / P.chunks_per_row;
+                    if (gy > rows) gy = (uint32_t)rows;
+                    if (gy > 65535) gy = 65535;
+                    uint32_t rpb = (uint32_t)((rows + gy - 1) / gy);
+                    gy = (uint32_t)((rows + rpb - 1) / rpb);
+                    ew_bcast_rows_kernel<F, T, O, VEC><<<dim3(P.chunks_per_row, gy), kEwThreads, 0, s>>>(f, a, out, P.qv, (uint32_t)rows, rpb);
+                    break;
+                }
+            }
             if (P.qv >= (uint32_t)kEwThreads && rows * P.chunks_per_row < 0x7FFFFFFFull) {
                 ew_row_long_kernel<F, T, O, NIN, VEC><<<(uint32_t)(rows * P.chunks_per_row), kEwThreads, 0, s>>>(f, a, b, out, P);
             } else {

@@ -126,7 +126,10 @@ extern "C" void mx_sum_f32_noalloc(size_t num_els, size_t num_dims, size_t num_r
         dim3 grid((u32)splits, (u32)O);
         if (vec) reduce_rows_block_kernel<f32, RED_SUM, VEC><<<grid, kRedThreads, 0, s>>>(inp, out, ws, R, seg, (u32)splits, pl.factor);
         else reduce_rows_block_kernel<f32, RED_SUM, 1><<<grid, kRedThreads, 0, s>>>(inp, out, ws, R, seg, (u32)splits, pl.factor);
-        if (splits > 1) reduce_partials_kernel<f32, RED_SUM><<<(u32)((O + kRedThreads - 1) / kRedThreads), kRedThreads, 0, s>>>(ws, out, O, (u32)splits, 0, pl.factor);
+        if (splits > 1) {  // same second pass as cuda_sum_f32, so both entry points round identically
+            if (O <= 64 && splits >= 64) reduce_partials_block_kernel<f32, RED_SUM><<<(u32)O, kRedThreads, 0, s>>>(ws, out, (u32)splits, pl.factor);
+            else reduce_partials_kernel<f32, RED_SUM><<<(u32)((O + kRedThreads - 1) / kRedThreads), kRedThreads, 0, s>>>(ws, out, O, (u32)splits, 0, pl.factor);
+        }
         check_launch(where);
         return;
     }

@@ -195,6 +195,27 @@ __device__ __forceinline__ bool truthy(T a) {
     return !feq(a, zero_of<T>());
 }
 
+// For bf16 / f16 every arithmetic functor below is "convert to f32, compute, round once".
+// HalfCore<Op> exposes that f32 computation on its own so that the vector kernels can convert
+// and round two elements per instruction (packed cvt) instead of going through the 16-bit
+// element type one value at a time.  The result is identical by construction.
+template <class Op>
+struct HalfCore {
+    static constexpr bool ok = false;
+};
+#define MX_HALF_CORE1(OP, EXPR)                                      \
+    template <>                                                      \
+    struct HalfCore<OP> {                                            \
+        static constexpr bool ok = true;                             \
+        __device__ __forceinline__ static f32 f(f32 v) { return EXPR; } \
+    };
+#define MX_HALF_CORE2(OP, EXPR)                                             \
+    template <>                                                             \
+    struct HalfCore<OP> {                                                   \
+        static constexpr bool ok = true;                                    \
+        __device__ __forceinline__ static f32 f(f32 a, f32 b) { return EXPR; } \
+    };
+
 // ------------------------------------------------------------------ binary
 struct OpAdd {
     template <class T>
@@ -320,7 +341,8 @@ struct OpLXor {
         __device__ static T f(T x) {                                                                                 \
             return fp_apply(x, [](f32 v) -> f32 { return EXPR32; }, [](f64 v) -> f64 { return EXPR64; });             \
         }                                                                                                            \
-    };
+    };                                                                                                               \
+    MX_HALF_CORE1(NAME, EXPR32)
 MX_FP_UNARY(OpSigmoid, 1.0f / (1.0f + expf(-v)), 1.0 / (1.0 + exp(-v)))
 MX_FP_UNARY(OpTanh, tanhf(v), tanh(v))
 MX_FP_UNARY(OpSin, sinf(v), sin(v))
@@ -452,19 +474,62 @@ struct OpElu {
     }
 };
 
+MX_HALF_CORE2(OpAdd, a + b)
+MX_HALF_CORE2(OpSub, a - b)
+MX_HALF_CORE2(OpMul, a * b)
+MX_HALF_CORE2(OpDiv, b == 0.0f ? (a == 0.0f ? 0.0f : INFINITY) : a / b)
+MX_HALF_CORE2(OpMax, a > b ? a : b)
+MX_HALF_CORE2(OpMin, a < b ? a : b)
+MX_HALF_CORE2(OpPow, powf(a, b))
+MX_HALF_CORE2(OpLeakyRelu, a > 0.0f ? a : b * a)
+MX_HALF_CORE2(OpElu, a > 0.0f ? a : b * (expf(a) - 1.0f))
+MX_HALF_CORE1(OpGelu, gelu_f32_fast(v))
+MX_HALF_CORE1(OpNeg, -v)
+MX_HALF_CORE1(OpAbs, fabsf(v))
+MX_HALF_CORE1(OpSquare, v * v)
+MX_HALF_CORE1(OpSqrt, sqrtf(v))
+MX_HALF_CORE1(OpRelu, v > 0.0f ? v : 0.0f)
+MX_HALF_CORE1(OpSign, v > 0.0f ? 1.0f : (v < 0.0f ? -1.0f : 0.0f))
+
+// Two 16-bit floats <-> two f32, one instruction each way where the hardware has it.
+template <class T>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+    if constexpr (std::is_same<T, bf16>::value) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+    else return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+template <class T>
+__device__ __forceinline__ uint32_t pack2_rn(f32 lo, f32 hi) {
+    if constexpr (std::is_same<T, bf16>::value) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    } else {
+        __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+}
+
 // Adapters giving every family the call shape the kernels use.
 template <class Op, class T, class O>
 struct Binary {  // out = Op(a, b)
+    static constexpr bool kCore = HalfCore<Op>::ok && is_half_v<T> && std::is_same<O, T>::value;
     __device__ __forceinline__ O operator()(T a, T b) const { return (O)Op::template f<T>(a, b); }
+    __device__ __forceinline__ f32 core(f32 a, f32 b) const { return HalfCore<Op>::f(a, b); }
 };
 template <class Op, class T, class O>
 struct Unary {  // out = Op(a)
+    static constexpr bool kCore = HalfCore<Op>::ok && is_half_v<T> && std::is_same<O, T>::value;
     __device__ __forceinline__ O operator()(T a) const { return (O)Op::template f<T>(a); }
+    __device__ __forceinline__ f32 core(f32 a) const { return HalfCore<Op>::f(a); }
 };
 template <class Op, class T, class O>
 struct UnaryConst {  // out = Op(a, c)
+    static constexpr bool kCore = HalfCore<Op>::ok && is_half_v<T> && std::is_same<O, T>::value;
     T c;
     __device__ __forceinline__ O operator()(T a) const { return (O)Op::template f<T>(a, c); }
+    __device__ __forceinline__ f32 core(f32 a) const {
+        if constexpr (is_half_v<T>) return HalfCore<Op>::f(a, to_f32(c));
+        else return 0.0f;
+    }
 };
 
 }  // namespace mx

@@ -212,6 +212,18 @@ __global__ void __launch_bounds__(kRedThreads) reduce_partials_kernel(const type
     out[j] = TR::finalize(acc, factor);
 }
 
+// Same fold with one block per output, for few outputs with many partials (a full reduction
+// split over ~1000 blocks): threads stride over the partials, then a fixed-shape block tree.
+template <class T, int KIND>
+__global__ void __launch_bounds__(kRedThreads) reduce_partials_block_kernel(const typename RedTraits<T, KIND>::Acc* partial, T* out, u32 S, u64 factor) {
+    typedef RedTraits<T, KIND> TR;
+    const u64 j = blockIdx.x;
+    typename TR::Acc acc = TR::init();
+    for (u32 s = threadIdx.x; s < S; s += kRedThreads) acc = TR::combine(acc, partial[j * S + s]);
+    acc = block_reduce<TR, kRedThreads>(acc);
+    if (threadIdx.x == 0) out[j] = TR::finalize(acc, factor);
+}
+
 // ---------------------------------------------------------------------------------
 // cols: in[(o * R + r) * I + i], out[o * I + i]
 // ---------------------------------------------------------------------------------
@@ -239,16 +251,18 @@ __global__ void __launch_bounds__(kColLanes* kColRows) reduce_cols_kernel(const 
         if (col < I) {
             const T* p = in + o * R * I + col;
             u64 r = r_begin + ty;
-            for (; r + 3 * kColRows < r_end; r += 4 * kColRows) {
-                Vec<T, VEC> a = *reinterpret_cast<const Vec<T, VEC>*>(p + r * I);
-                Vec<T, VEC> b = *reinterpret_cast<const Vec<T, VEC>*>(p + (r + kColRows) * I);
-                Vec<T, VEC> c = *reinterpret_cast<const Vec<T, VEC>*>(p + (r + 2 * kColRows) * I);
-                Vec<T, VEC> d = *reinterpret_cast<const Vec<T, VEC>*>(p + (r + 3 * kColRows) * I);
+            // eight independent 16-byte loads in flight per thread
+            for (; r + 7 * kColRows < r_end; r += 8 * kColRows) {
+                Vec<T, VEC> x[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) x[q] = *reinterpret_cast<const Vec<T, VEC>*>(p + (r + q * kColRows) * I);
 #pragma unroll
                 for (int j = 0; j < VEC; j++) {
-                    Acc x = TR::combine(TR::load(a.v[j]), TR::load(b.v[j]));
-                    Acc y = TR::combine(TR::load(c.v[j]), TR::load(d.v[j]));
-                    acc[j] = TR::combine(acc[j], TR::combine(x, y));
+                    Acc s01 = TR::combine(TR::load(x[0].v[j]), TR::load(x[1].v[j]));
+                    Acc s23 = TR::combine(TR::load(x[2].v[j]), TR::load(x[3].v[j]));
+                    Acc s45 = TR::combine(TR::load(x[4].v[j]), TR::load(x[5].v[j]));
+                    Acc s67 = TR::combine(TR::load(x[6].v[j]), TR::load(x[7].v[j]));
+                    acc[j] = TR::combine(acc[j], TR::combine(TR::combine(s01, s23), TR::combine(s45, s67)));
                 }
             }
             for (; r < r_end; r += kColRows) {
@@ -449,7 +463,8 @@ void red_launch(const RedPlan& pl, const T* in, T* out, const char* where) {
                 else reduce_rows_block_kernel<T, KIND, 1><<<grid, kRedThreads, 0, s>>>(in, out, part, R, seg, (u32)splits, pl.factor);
                 if (splits > 1) {
                     check_launch(where);
-                    reduce_partials_kernel<T, KIND><<<(u32)((O + kRedThreads - 1) / kRedThreads), kRedThreads, 0, s>>>(part, out, O, (u32)splits, 0, pl.factor);
+                    if (O <= 64 && splits >= 64) reduce_partials_block_kernel<T, KIND><<<(u32)O, kRedThreads, 0, s>>>(part, out, (u32)splits, pl.factor);
+                    else reduce_partials_kernel<T, KIND><<<(u32)((O + kRedThreads - 1) / kRedThreads), kRedThreads, 0, s>>>(part, out, O, (u32)splits, 0, pl.factor);
                 }
             }
         }

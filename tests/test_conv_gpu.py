@@ -26,6 +26,14 @@ def cases():
         ("no-pad", 1, 3, 12, 12, 3, 3, 0, 0, 1, 1),
         ("s3", 1, 1, 20, 17, 3, 3, 1, 1, 3, 3),
         ("big-plane", 1, 2, 56, 56, 3, 3, 1, 1, 1, 1),
+        # stride-1 vector fast paths: widths that are multiples of the 16-byte vector, kw in {1,3,5,7}
+        ("5x5-s1-p2-vec", 2, 2, 16, 24, 5, 5, 2, 2, 1, 1),
+        ("7x7-s1-p3-vec", 1, 1, 16, 16, 7, 7, 3, 3, 1, 1),
+        ("1x1-vec", 2, 3, 8, 16, 1, 1, 0, 0, 1, 1),
+        ("1x3-vec", 1, 2, 9, 16, 1, 3, 0, 1, 1, 1),
+        ("3x1-vec", 1, 2, 9, 16, 3, 1, 1, 0, 1, 1),
+        ("3x3-s1-p0", 1, 2, 10, 10, 3, 3, 0, 0, 1, 1),
+        ("3x3-s1-p1-tall", 3, 2, 40, 8, 3, 3, 1, 1, 1, 1),
     ]
 
 
