@@ -92,8 +92,19 @@ __device__ __forceinline__ void col2im_s1_terms(const T* __restrict__ col, const
     if (a0 >= 0 && (uint32_t)a0 < P.OW && row_base + a0 + VEC <= P.num_els) lo = *reinterpret_cast<const Vec<T, VEC>*>(col + row_base + a0);
     if (E != 0 && a0 + VEC >= 0 && (uint32_t)(a0 + VEC) < P.OW && row_base + a0 + 2 * VEC <= P.num_els)
         hi = *reinterpret_cast<const Vec<T, VEC>*>(col + row_base + a0 + VEC);
+    Vec<T, VEC> term;
 #pragma unroll
-    for (int j = 0; j < VEC; j++) sum.v[j] = conv_s1_add(sum.v[j], window_at<T, VEC>(lo, hi, E + j));
+    for (int j = 0; j < VEC; j++) term.v[j] = window_at<T, VEC>(lo, hi, E + j);
+    if constexpr (is_half_v<T>) {
+        // packed 16-bit adds round exactly like "add in f32, round" (see HalfNative in ops.cuh)
+        uint32_t* sw = reinterpret_cast<uint32_t*>(&sum);
+        const uint32_t* tw = reinterpret_cast<const uint32_t*>(&term);
+#pragma unroll
+        for (int j = 0; j < VEC / 2; j++) sw[j] = HalfNative<OpAdd>::template f<T>(sw[j], tw[j]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < VEC; j++) sum.v[j] = conv_s1_add(sum.v[j], term.v[j]);
+    }
     if constexpr (KWI > 0) col2im_s1_terms<T, VEC, KW, PW, KWI - 1>(col, P, kh_base, w0, OHW, zero_vec, sum);
 }
 

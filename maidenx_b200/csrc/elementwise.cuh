@@ -66,7 +66,40 @@ __device__ __forceinline__ Vec<T, N> splat(T x) {
 template <class F, class T, class O, int NIN, int VEC>
 __device__ __forceinline__ Vec<O, VEC> apply_vec(const F& f, const Vec<T, VEC>& a, const Vec<T, VEC>& b) {
     Vec<O, VEC> r;
-    if constexpr (F::kCore && VEC % 2 == 0) {
+    if constexpr (F::kNative && VEC % 2 == 0 && NIN == 2) {
+        // bf16 / f16 add and sub: the packed hardware instruction rounds exactly as "f32, then round"
+        const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
+        const uint32_t* bw = reinterpret_cast<const uint32_t*>(&b);
+        uint32_t* rw = reinterpret_cast<uint32_t*>(&r);
+#pragma unroll
+        for (int i = 0; i < VEC / 2; i++) rw[i] = f.native(aw[i], bw[i]);
+    } else if constexpr (F::kChecked && VEC % 2 == 0) {
+        // bf16 / f16 division: approximate quotients, and the few elements the check flags are
+        // redone with the exact out-of-line division
+        const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
+        const uint32_t* bw = reinterpret_cast<const uint32_t*>(&b);
+        uint32_t* rw = reinterpret_cast<uint32_t*>(&r);
+        uint32_t mask = 0;
+#pragma unroll
+        for (int i = 0; i < VEC / 2; i++) {
+            float2 x = unpack2<T>(aw[i]);
+            if constexpr (NIN == 2) {
+                float2 y = unpack2<T>(bw[i]);
+                rw[i] = pack2_rn<T>(f.core_checked(x.x, y.x, mask, 2 * i), f.core_checked(x.y, y.y, mask, 2 * i + 1));
+            } else {
+                rw[i] = pack2_rn<T>(f.core_checked(x.x, mask, 2 * i), f.core_checked(x.y, mask, 2 * i + 1));
+            }
+        }
+        if (mask) {
+#pragma unroll
+            for (int i = 0; i < VEC; i++) {
+                if ((mask >> i) & 1u) {
+                    if constexpr (NIN == 2) r.v[i] = f(a.v[i], b.v[i]);
+                    else r.v[i] = f(a.v[i]);
+                }
+            }
+        }
+    } else if constexpr (F::kCore && VEC % 2 == 0) {
         // 16-bit floats: unpack / compute in f32 / round two elements at a time
         const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
         const uint32_t* bw = reinterpret_cast<const uint32_t*>(&b);

@@ -11,7 +11,8 @@
 //   * Arguments are those of cuda_sum_f32, except that `metadata` must be HOST memory
 //     (nothing is copied or cached, so nothing is allocated on the host either).
 //   * No cudaMalloc, cudaFree or other allocating call is made, on any path.
-//   * The workspace is kNoAllocScratchBytes (1 MiB) per GPU, reserved on every GPU that loads
+//   * The workspace is kNoAllocScratchBytes (1 MiB, plus 64 KiB of arrival counters for the
+//     in-launch fold of split reductions) per GPU, reserved on every GPU that loads
 //     the library for as long as the process lives.  A reduction whose partial results do not
 //     fit is rejected: mx_last_error() == 3 (unsupported) and the output is left untouched.
 //     (Rows/columns reductions need splits * outputs * 4 bytes; the scatter path, used for
@@ -33,10 +34,12 @@ namespace mx {
 namespace {
 
 constexpr size_t kNoAllocScratchBytes = 1u << 20;
+constexpr size_t kNoAllocCounters = 16384;  // u32 each, in front of the workspace; static storage starts zeroed
+constexpr size_t kNoAllocCounterBytes = kNoAllocCounters * sizeof(u32);
 
 // In host code this name is only a handle for the runtime's symbol table, not an address a
 // kernel can use: the device address is obtained per device below.
-static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocCounterBytes + kNoAllocScratchBytes];
 
 std::mutex g_setup_mutex;
 void* g_scratch_addr[64] = {nullptr};
@@ -95,8 +98,10 @@ extern "C" void mx_sum_f32_noalloc(size_t num_els, size_t num_dims, size_t num_r
         set_error(kErrBadMetadata, 0, where);
         return;
     }
-    Acc* ws = static_cast<Acc*>(noalloc_scratch(where));
-    if (!ws) return;
+    unsigned char* block = static_cast<unsigned char*>(noalloc_scratch(where));
+    if (!block) return;
+    u32* const all_counters = reinterpret_cast<u32*>(block);
+    Acc* ws = reinterpret_cast<Acc*>(block + kNoAllocCounterBytes);
     const size_t ws_elems = kNoAllocScratchBytes / sizeof(Acc);
     cudaStream_t s = ctx().stream;
     const int sms = sm_count();
@@ -107,7 +112,10 @@ extern "C" void mx_sum_f32_noalloc(size_t num_els, size_t num_dims, size_t num_r
         const u64 O = pl.O, R = pl.R;
         const bool vec = base_aligned && R % VEC == 0;
         const u64 unit = (u64)kRedThreads * VEC * 4;
-        u64 want = O >= (u64)sms * 8 ? 1 : ((u64)sms * 8 + O - 1) / O;
+        // same split selection as cuda_sum_f32, so both entry points round identically
+        static int occ = 0;
+        if (!occ) occ = resident_blocks((const void*)reduce_rows_block_kernel<f32, RED_SUM, VEC>, kRedThreads);
+        u64 want = split_count(O, (u64)sms * occ);
         u64 max_splits = (R + unit - 1) / unit;
         u64 splits = want < max_splits ? want : max_splits;
         if (splits < 1) splits = 1;
@@ -123,11 +131,13 @@ extern "C" void mx_sum_f32_noalloc(size_t num_els, size_t num_dims, size_t num_r
             splits = 1;
             seg = (R + VEC - 1) / VEC * VEC;
         }
+        u32* counters = splits > 1 && O <= kNoAllocCounters ? all_counters : nullptr;
+        const int tree_fold = O <= 64 && splits >= 64;
         dim3 grid((u32)splits, (u32)O);
-        if (vec) reduce_rows_block_kernel<f32, RED_SUM, VEC><<<grid, kRedThreads, 0, s>>>(inp, out, ws, R, seg, (u32)splits, pl.factor);
-        else reduce_rows_block_kernel<f32, RED_SUM, 1><<<grid, kRedThreads, 0, s>>>(inp, out, ws, R, seg, (u32)splits, pl.factor);
-        if (splits > 1) {  // same second pass as cuda_sum_f32, so both entry points round identically
-            if (O <= 64 && splits >= 64) reduce_partials_block_kernel<f32, RED_SUM><<<(u32)O, kRedThreads, 0, s>>>(ws, out, (u32)splits, pl.factor);
+        if (vec) reduce_rows_block_kernel<f32, RED_SUM, VEC><<<grid, kRedThreads, 0, s>>>(inp, out, ws, R, seg, (u32)splits, pl.factor, counters, tree_fold);
+        else reduce_rows_block_kernel<f32, RED_SUM, 1><<<grid, kRedThreads, 0, s>>>(inp, out, ws, R, seg, (u32)splits, pl.factor, counters, tree_fold);
+        if (splits > 1 && !counters) {
+            if (tree_fold) reduce_partials_block_kernel<f32, RED_SUM><<<(u32)O, kRedThreads, 0, s>>>(ws, out, (u32)splits, pl.factor);
             else reduce_partials_kernel<f32, RED_SUM><<<(u32)((O + kRedThreads - 1) / kRedThreads), kRedThreads, 0, s>>>(ws, out, O, (u32)splits, 0, pl.factor);
         }
         check_launch(where);
@@ -139,7 +149,9 @@ extern "C" void mx_sum_f32_noalloc(size_t num_els, size_t num_dims, size_t num_r
         const int v = vec ? VEC : 1;
         u64 gx = (I + (u64)kColLanes * v - 1) / ((u64)kColLanes * v);
         u64 gz = O < 65535 ? O : 65535;
-        u64 want = gx * gz >= (u64)sms * 8 ? 1 : ((u64)sms * 8 + gx * gz - 1) / (gx * gz);
+        static int occ = 0;
+        if (!occ) occ = resident_blocks((const void*)reduce_cols_kernel<f32, RED_SUM, VEC>, kColLanes * kColRows);
+        u64 want = split_count(gx * gz, (u64)sms * occ);
         u64 max_splits = (R + 63) / 64;
         u64 splits = want < max_splits ? want : max_splits;
         if (splits < 1) splits = 1;
@@ -147,10 +159,11 @@ extern "C" void mx_sum_f32_noalloc(size_t num_els, size_t num_dims, size_t num_r
         while (splits > 1 && splits * O * I > ws_elems) splits--;
         u64 seg = (R + splits - 1) / splits;
         splits = (R + seg - 1) / seg;
+        u32* counters = splits > 1 && O * gx <= kNoAllocCounters ? all_counters : nullptr;
         dim3 grid((u32)gx, (u32)splits, (u32)gz);
-        if (vec) reduce_cols_kernel<f32, RED_SUM, VEC><<<grid, kColLanes * kColRows, 0, s>>>(inp, out, ws, O, R, I, seg, (u32)splits, pl.factor);
-        else reduce_cols_kernel<f32, RED_SUM, 1><<<grid, kColLanes * kColRows, 0, s>>>(inp, out, ws, O, R, I, seg, (u32)splits, pl.factor);
-        if (splits > 1) {
+        if (vec) reduce_cols_kernel<f32, RED_SUM, VEC><<<grid, kColLanes * kColRows, 0, s>>>(inp, out, ws, O, R, I, seg, (u32)splits, pl.factor, counters);
+        else reduce_cols_kernel<f32, RED_SUM, 1><<<grid, kColLanes * kColRows, 0, s>>>(inp, out, ws, O, R, I, seg, (u32)splits, pl.factor, counters);
+        if (splits > 1 && !counters) {
             u64 count = O * I;
             reduce_partials_kernel<f32, RED_SUM><<<(u32)((count + kRedThreads - 1) / kRedThreads), kRedThreads, 0, s>>>(ws, out, count, (u32)splits, 1, pl.factor);
         }

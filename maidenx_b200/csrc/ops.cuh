@@ -216,6 +216,40 @@ struct HalfCore {
         __device__ __forceinline__ static f32 f(f32 a, f32 b) { return EXPR; } \
     };
 
+// Division of 16-bit floats.  The CPU backend divides in f32 and rounds once to T; x / 0 is 0 for
+// 0 / 0 and +inf otherwise.  half_div_exact is that definition, kept out of line.
+template <class T>
+__device__ __noinline__ T half_div_exact(T a, T b) {
+    const f32 x = to_f32(a), y = to_f32(b);
+    if (y == 0.0f) return from_f32<T>(x == 0.0f ? 0.0f : INFINITY);
+    return from_f32<T>(x / y);
+}
+
+// Fast path: q = a * rcp(b), within 2 f32 ulp of the true quotient.  Rounding q to T gives the
+// reference's bits whenever no rounding boundary of T lies between q and the IEEE f32 quotient:
+//   * A quotient of two p-bit significands that is dyadic has at most p bits, so it never sits
+//     exactly on a midpoint of T; otherwise its distance to the nearest midpoint is at least
+//     2^-(2p+1) relative.  For bf16 (p = 8) that is 2^-17, far above the 2^-22 error of q: the
+//     fast result is always right.  For f16 (p = 11) the bound is 2^-23, so an f16 quotient whose
+//     dropped 13 bits are within 2 ulp of the midpoint pattern is flagged.
+//   * Zero, subnormal, infinite or NaN q (b = 0, subnormal or huge b, over/underflow, results in
+//     T's subnormal range where the rounding position moves) is flagged.
+// Flagged elements are recomputed with half_div_exact; bit `idx` of `mask` marks them.
+template <class T>
+__device__ __forceinline__ f32 half_div_fast(f32 a, f32 b, uint32_t& mask, int idx) {
+    f32 r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(b));
+    const f32 q = a * r;
+    const uint32_t qb = __float_as_uint(q);
+    constexpr bool kBf = std::is_same<T, bf16>::value;
+    constexpr uint32_t kLo = kBf ? 0x0D800000u /* 2^-100 */ : 0x38800000u /* 2^-14 */;
+    constexpr uint32_t kHi = 0x71800000u;  // 2^100
+    bool bad = (qb << 1) - (kLo << 1) >= ((kHi - kLo) << 1);
+    if constexpr (!kBf) bad = bad || ((qb << 19) - (0x0FFEu << 19)) <= (4u << 19);
+    if (bad) mask |= 1u << idx;
+    return q;
+}
+
 // ------------------------------------------------------------------ binary
 struct OpAdd {
     template <class T>
@@ -258,9 +292,7 @@ struct OpDiv {
             }
             return sat_div(a, b);
         } else if constexpr (is_half_v<T>) {
-            f32 x = to_f32(a), y = to_f32(b);
-            if (y == 0.0f) return from_f32<T>(x == 0.0f ? 0.0f : INFINITY);
-            return from_f32<T>(x / y);
+            return half_div_exact<T>(a, b);
         } else {
             if (b == (T)0) return a == (T)0 ? (T)0 : (T)INFINITY;
             return a / b;
@@ -335,29 +367,37 @@ struct OpLXor {
 };
 
 // ------------------------------------------------------------------ unary
-#define MX_FP_UNARY(NAME, EXPR32, EXPR64)                                                                            \
+// EXPRH is what bf16 / f16 evaluate (in f32, rounded once).  Where it differs from EXPR32 it uses
+// the hardware exp2 / reciprocal approximations: their error (a few f32 ulp) is three orders
+// below the 16-bit rounding step, and the ops stay memory-bound instead of instruction-bound.
+#define MX_FP_UNARY(NAME, EXPR32, EXPR64, EXPRH)                                                                     \
     struct NAME {                                                                                                    \
         template <class T>                                                                                           \
         __device__ static T f(T x) {                                                                                 \
-            return fp_apply(x, [](f32 v) -> f32 { return EXPR32; }, [](f64 v) -> f64 { return EXPR64; });             \
+            if constexpr (is_half_v<T>) {                                                                            \
+                const f32 v = to_f32(x);                                                                             \
+                return from_f32<T>(EXPRH);                                                                           \
+            } else {                                                                                                 \
+                return fp_apply(x, [](f32 v) -> f32 { return EXPR32; }, [](f64 v) -> f64 { return EXPR64; });         \
+            }                                                                                                        \
         }                                                                                                            \
     };                                                                                                               \
-    MX_HALF_CORE1(NAME, EXPR32)
-MX_FP_UNARY(OpSigmoid, 1.0f / (1.0f + expf(-v)), 1.0 / (1.0 + exp(-v)))
-MX_FP_UNARY(OpTanh, tanhf(v), tanh(v))
-MX_FP_UNARY(OpSin, sinf(v), sin(v))
-MX_FP_UNARY(OpCos, cosf(v), cos(v))
-MX_FP_UNARY(OpTan, tanf(v), tan(v))
-MX_FP_UNARY(OpLn, logf(v), log(v))
-MX_FP_UNARY(OpLog10, log10f(v), log10(v))
-MX_FP_UNARY(OpLog2, log2f(v), log2(v))
-MX_FP_UNARY(OpExp, expf(v), exp(v))
-MX_FP_UNARY(OpExp10, powf(10.0f, v), pow(10.0, v))
-MX_FP_UNARY(OpExp2, exp2f(v), exp2(v))
-MX_FP_UNARY(OpSoftplus, logf(1.0f + expf(v)), log(1.0 + exp(v)))
-MX_FP_UNARY(OpRecip, 1.0f / v, 1.0 / v)
-MX_FP_UNARY(OpSqrtF, sqrtf(v), sqrt(v))
-MX_FP_UNARY(OpAbsF, fabsf(v), fabs(v))
+    MX_HALF_CORE1(NAME, EXPRH)
+MX_FP_UNARY(OpSigmoid, 1.0f / (1.0f + expf(-v)), 1.0 / (1.0 + exp(-v)), __fdividef(1.0f, 1.0f + __expf(-v)))
+MX_FP_UNARY(OpTanh, tanhf(v), tanh(v), tanhf(v))
+MX_FP_UNARY(OpSin, sinf(v), sin(v), sinf(v))
+MX_FP_UNARY(OpCos, cosf(v), cos(v), cosf(v))
+MX_FP_UNARY(OpTan, tanf(v), tan(v), tanf(v))
+MX_FP_UNARY(OpLn, logf(v), log(v), logf(v))
+MX_FP_UNARY(OpLog10, log10f(v), log10(v), log10f(v))
+MX_FP_UNARY(OpLog2, log2f(v), log2(v), log2f(v))
+MX_FP_UNARY(OpExp, expf(v), exp(v), __expf(v))
+MX_FP_UNARY(OpExp10, powf(10.0f, v), pow(10.0, v), powf(10.0f, v))
+MX_FP_UNARY(OpExp2, exp2f(v), exp2(v), exp2f(v))
+MX_FP_UNARY(OpSoftplus, logf(1.0f + expf(v)), log(1.0 + exp(v)), logf(1.0f + expf(v)))
+MX_FP_UNARY(OpRecip, 1.0f / v, 1.0 / v, 1.0f / v)
+MX_FP_UNARY(OpSqrtF, sqrtf(v), sqrt(v), sqrtf(v))
+MX_FP_UNARY(OpAbsF, fabsf(v), fabs(v), fabsf(v))
 #undef MX_FP_UNARY
 
 __device__ __forceinline__ f32 gelu_f32(f32 x) {
@@ -375,9 +415,12 @@ __device__ __forceinline__ f64 gelu_f64(f64 x) {
 // cancellation for negative x) is three orders below the bf16 / f16 rounding step, and it
 // costs a third of tanhf, which keeps the 16-bit kernels memory-bound.
 __device__ __forceinline__ f32 gelu_f32_fast(f32 x) {
-    const f32 s = 0.7978845608028654f, c = 0.044715f;
-    f32 t = s * (x + c * x * x * x);
-    return __fdividef(x, 1.0f + __expf(-2.0f * t));
+    // exp(-2t) = 2^(x * (k1 + k2 x^2)), k1 = -2 log2(e) sqrt(2/pi), k2 = 0.044715 k1
+    const f32 k1 = -2.302208198f, k2 = -0.102943240f;
+    f32 e;
+    const f32 arg = x * fmaf(k2, x * x, k1);
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(arg));
+    return __fdividef(x, 1.0f + e);
 }
 struct OpGelu {
     template <class T>
@@ -477,7 +520,6 @@ struct OpElu {
 MX_HALF_CORE2(OpAdd, a + b)
 MX_HALF_CORE2(OpSub, a - b)
 MX_HALF_CORE2(OpMul, a * b)
-MX_HALF_CORE2(OpDiv, b == 0.0f ? (a == 0.0f ? 0.0f : INFINITY) : a / b)
 MX_HALF_CORE2(OpMax, a > b ? a : b)
 MX_HALF_CORE2(OpMin, a < b ? a : b)
 MX_HALF_CORE2(OpPow, powf(a, b))
@@ -490,6 +532,43 @@ MX_HALF_CORE1(OpSquare, v * v)
 MX_HALF_CORE1(OpSqrt, sqrtf(v))
 MX_HALF_CORE1(OpRelu, v > 0.0f ? v : 0.0f)
 MX_HALF_CORE1(OpSign, v > 0.0f ? 1.0f : (v < 0.0f ? -1.0f : 0.0f))
+
+// Sums and differences of two bf16 (or two f16) values: the exact result fits f32 whenever the
+// operands' exponents are within 16 (13) bits, and otherwise the smaller operand is far below
+// half an ulp of the larger, so "add in f32, round to T" and the hardware's correctly rounded
+// packed add give the same bits.  One instruction per two elements.
+template <class Op>
+struct HalfNative {
+    static constexpr bool ok = false;
+};
+template <>
+struct HalfNative<OpAdd> {
+    static constexpr bool ok = true;
+    template <class T>
+    __device__ __forceinline__ static uint32_t f(uint32_t a, uint32_t b) {
+        if constexpr (std::is_same<T, bf16>::value) {
+            __nv_bfloat162 r = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+            return *reinterpret_cast<uint32_t*>(&r);
+        } else {
+            __half2 r = __hadd2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+            return *reinterpret_cast<uint32_t*>(&r);
+        }
+    }
+};
+template <>
+struct HalfNative<OpSub> {
+    static constexpr bool ok = true;
+    template <class T>
+    __device__ __forceinline__ static uint32_t f(uint32_t a, uint32_t b) {
+        if constexpr (std::is_same<T, bf16>::value) {
+            __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+            return *reinterpret_cast<uint32_t*>(&r);
+        } else {
+            __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+            return *reinterpret_cast<uint32_t*>(&r);
+        }
+    }
+};
 
 // Two 16-bit floats <-> two f32, one instruction each way where the hardware has it.
 template <class T>
@@ -512,22 +591,38 @@ __device__ __forceinline__ uint32_t pack2_rn(f32 lo, f32 hi) {
 template <class Op, class T, class O>
 struct Binary {  // out = Op(a, b)
     static constexpr bool kCore = HalfCore<Op>::ok && is_half_v<T> && std::is_same<O, T>::value;
+    static constexpr bool kNative = HalfNative<Op>::ok && is_half_v<T> && std::is_same<O, T>::value;
+    // division of 16-bit floats: fast quotient per element, flagged elements redone exactly
+    static constexpr bool kChecked = std::is_same<Op, OpDiv>::value && is_half_v<T> && std::is_same<O, T>::value;
     __device__ __forceinline__ O operator()(T a, T b) const { return (O)Op::template f<T>(a, b); }
     __device__ __forceinline__ f32 core(f32 a, f32 b) const { return HalfCore<Op>::f(a, b); }
+    __device__ __forceinline__ f32 core_checked(f32 a, f32 b, uint32_t& mask, int idx) const {
+        if constexpr (kChecked) return half_div_fast<T>(a, b, mask, idx);
+        else return 0.0f;
+    }
+    __device__ __forceinline__ uint32_t native(uint32_t a, uint32_t b) const { return HalfNative<Op>::template f<T>(a, b); }
 };
 template <class Op, class T, class O>
 struct Unary {  // out = Op(a)
+    static constexpr bool kNative = false;
+    static constexpr bool kChecked = false;
     static constexpr bool kCore = HalfCore<Op>::ok && is_half_v<T> && std::is_same<O, T>::value;
     __device__ __forceinline__ O operator()(T a) const { return (O)Op::template f<T>(a); }
     __device__ __forceinline__ f32 core(f32 a) const { return HalfCore<Op>::f(a); }
 };
 template <class Op, class T, class O>
 struct UnaryConst {  // out = Op(a, c)
+    static constexpr bool kNative = false;
+    static constexpr bool kChecked = std::is_same<Op, OpDiv>::value && is_half_v<T> && std::is_same<O, T>::value;
     static constexpr bool kCore = HalfCore<Op>::ok && is_half_v<T> && std::is_same<O, T>::value;
     T c;
     __device__ __forceinline__ O operator()(T a) const { return (O)Op::template f<T>(a, c); }
     __device__ __forceinline__ f32 core(f32 a) const {
         if constexpr (is_half_v<T>) return HalfCore<Op>::f(a, to_f32(c));
+        else return 0.0f;
+    }
+    __device__ __forceinline__ f32 core_checked(f32 a, uint32_t& mask, int idx) const {
+        if constexpr (kChecked) return half_div_fast<T>(a, to_f32(c), mask, idx);
         else return 0.0f;
     }
 };

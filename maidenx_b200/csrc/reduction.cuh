@@ -76,9 +76,15 @@ struct RedTraits {
         // max / min: a NaN never wins (the reference's `if val > *out`), whichever side of a
         // pairwise combine it arrives on.
         if constexpr (kIsSum) return a + v;
-        else if constexpr (std::is_floating_point<Acc>::value) {
-            if constexpr (KIND == RED_MAX) return (v > a || a != a) ? v : a;
-            else return (v < a || a != a) ? v : a;
+        else if constexpr (std::is_same<Acc, f32>::value) {
+            // the hardware max / min return the other operand when one is NaN, and the initial
+            // value is never NaN, so a NaN can only survive a combine of two NaNs and then loses
+            // the next one: the same outcome as the reference's comparison, in one instruction
+            if constexpr (KIND == RED_MAX) return fmaxf(a, v);
+            else return fminf(a, v);
+        } else if constexpr (std::is_same<Acc, f64>::value) {
+            if constexpr (KIND == RED_MAX) return fmax(a, v);
+            else return fmin(a, v);
         } else if constexpr (KIND == RED_MAX) return v > a ? v : a;
         else return v < a ? v : a;
     }
@@ -148,20 +154,59 @@ __device__ __forceinline__ typename SrcTR::Acc row_segment(const Src* row, u64 b
     return SrcTR::combine(SrcTR::combine(acc0, acc1), SrcTR::combine(acc2, acc3));
 }
 
+// Arrival counting for split reductions that fold their partials in the same launch: every block
+// publishes its partial (write, __threadfence), then one thread bumps the counter of its output
+// group; the block that sees the last ticket re-reads all partials of the group, folds them in
+// split order (so the result does not depend on which block came last) and writes the output.
+// It also puts the counter back to zero, so the counter array is all-zero between launches.
+__device__ __forceinline__ bool last_arrival(u32* counter, u32 expected) {
+    __shared__ u32 s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const u32 ticket = atomicAdd(counter, 1u);
+        s_last = ticket == expected - 1;
+        if (s_last) *counter = 0;
+    }
+    __syncthreads();
+    const bool last = s_last != 0;
+    if (last) __threadfence();
+    return last;
+}
+template <class Acc>
+__device__ __forceinline__ Acc load_published(const Acc* p) {
+    return *reinterpret_cast<const volatile Acc*>(p);  // not through L1: written by other blocks of this launch
+}
+
+// counters == nullptr: partials are left for a second launch (reduce_partials_*_kernel).
 template <class T, int KIND, int VEC>
 __global__ void __launch_bounds__(kRedThreads) reduce_rows_block_kernel(const T* in, T* out, typename RedTraits<T, KIND>::Acc* partial,
-                                                                      u64 R, u64 seg, u32 splits, u64 factor) {
+                                                                      u64 R, u64 seg, u32 splits, u64 factor, u32* counters, int tree_fold) {
     typedef RedTraits<T, KIND> TR;
+    typedef typename TR::Acc Acc;
     const u64 row = blockIdx.y;
     const u32 split = blockIdx.x;
     const u64 begin = (u64)split * seg;
     u64 end = begin + seg;
     if (end > R) end = R;
-    typename TR::Acc v = begin < end ? row_segment<T, KIND, VEC, T, TR>(in + row * R, begin, end) : TR::init();
+    Acc v = begin < end ? row_segment<T, KIND, VEC, T, TR>(in + row * R, begin, end) : TR::init();
     v = block_reduce<TR, kRedThreads>(v);
     if (threadIdx.x == 0) {
         if (splits == 1) out[row] = TR::finalize(v, factor);
         else partial[row * splits + split] = v;
+    }
+    if (splits == 1 || !counters) return;
+    if (!last_arrival(counters + row, splits)) return;
+    const Acc* mine = partial + row * splits;
+    if (tree_fold) {  // same shape as reduce_partials_block_kernel
+        Acc acc = TR::init();
+        for (u32 s2 = threadIdx.x; s2 < splits; s2 += kRedThreads) acc = TR::combine(acc, load_published(mine + s2));
+        acc = block_reduce<TR, kRedThreads>(acc);
+        if (threadIdx.x == 0) out[row] = TR::finalize(acc, factor);
+    } else if (threadIdx.x == 0) {  // same order as reduce_partials_kernel
+        Acc acc = TR::init();
+        for (u32 s2 = 0; s2 < splits; s2++) acc = TR::combine(acc, load_published(mine + s2));
+        out[row] = TR::finalize(acc, factor);
     }
 }
 
@@ -234,7 +279,7 @@ constexpr int kColRows = 8;    // threads along the reduced dim
 // aligned base.
 template <class T, int KIND, int VEC>
 __global__ void __launch_bounds__(kColLanes* kColRows) reduce_cols_kernel(const T* in, T* out, typename RedTraits<T, KIND>::Acc* partial, u64 O,
-                                                                         u64 R, u64 I, u64 seg, u32 splits, u64 factor) {
+                                                                         u64 R, u64 I, u64 seg, u32 splits, u64 factor, u32* counters) {
     typedef RedTraits<T, KIND> TR;
     typedef typename TR::Acc Acc;
     __shared__ Acc sm[kColRows][kColLanes * VEC + 1];
@@ -283,6 +328,19 @@ __global__ void __launch_bounds__(kColLanes* kColRows) reduce_cols_kernel(const 
                 for (int y = 1; y < kColRows; y++) v = TR::combine(v, sm[y][c]);
                 if (splits == 1) out[o * I + gc] = TR::finalize(v, factor);
                 else partial[((u64)split * O + o) * I + gc] = v;
+            }
+        }
+        if (splits > 1 && counters) {
+            // fold in the same launch: the last block of this (o, column strip) to arrive
+            if (last_arrival(counters + o * gridDim.x + blockIdx.x, splits)) {
+                for (int c = threadIdx.x; c < kColLanes * VEC; c += kColLanes * kColRows) {
+                    u64 gc = (u64)blockIdx.x * kColLanes * VEC + c;
+                    if (gc < I) {
+                        Acc v = TR::init();
+                        for (u32 s2 = 0; s2 < splits; s2++) v = TR::combine(v, load_published(partial + ((u64)s2 * O + o) * I + gc));
+                        out[o * I + gc] = TR::finalize(v, factor);
+                    }
+                }
             }
         }
         __syncthreads();
@@ -412,6 +470,17 @@ struct RedPlan {
     RedGenParams gen;
 };
 
+// How many ways to split each of `groups` independent reductions so that the launch fills the
+// GPU's `capacity` resident blocks in ONE wave: a launch of slightly more blocks than fit pays a
+// second, nearly empty wave, which on these 50-100 us kernels costs 10-20 %.
+inline u64 split_count(u64 groups, u64 capacity) {
+    if (groups == 0 || groups >= capacity) return 1;
+    u64 s = capacity / groups;
+    return s < 1 ? 1 : s;
+}
+int resident_blocks(const void* kernel, int threads);  // occupancy of a kernel (blocks per SM), at least 1
+u32* arrival_counters(u64 count);                      // zeroed counters for last_arrival, or nullptr if count is too large
+
 void red_plan_dims(RedPlan& pl, size_t num_els, size_t num_dims, size_t num_red, const size_t* hm);
 void red_plan_shape(RedPlan& pl, size_t num_els, size_t num_dims, const size_t* hm);
 
@@ -442,7 +511,9 @@ void red_launch(const RedPlan& pl, const T* in, T* out, const char* where) {
             // block per (row, split); split long rows when there are too few rows to fill the GPU
             const bool vec = base_aligned && R % VEC == 0;
             const u64 unit = (u64)kRedThreads * VEC * 4;  // one full unrolled trip of a block
-            u64 want = O >= (u64)sms * 8 ? 1 : ((u64)sms * 8 + O - 1) / O;
+            static int occ = 0;  // resident blocks per SM of this instantiation
+            if (!occ) occ = resident_blocks((const void*)reduce_rows_block_kernel<T, KIND, VEC>, kRedThreads);
+            u64 want = split_count(O, (u64)sms * occ);
             u64 max_splits = (R + unit - 1) / unit;
             u64 splits = want < max_splits ? want : max_splits;
             if (splits < 1) splits = 1;
@@ -454,16 +525,19 @@ void red_launch(const RedPlan& pl, const T* in, T* out, const char* where) {
                 reduce_rows_warp_kernel<T, KIND, 1><<<(u32)blocks, kRedThreads, 0, s>>>(in, out, O, R, pl.factor);
             } else {
                 Acc* part = nullptr;
+                u32* counters = nullptr;
                 if (splits > 1) {
                     part = static_cast<Acc*>(scratch(sizeof(Acc) * O * splits));
                     if (!part) return;
+                    counters = arrival_counters(O);  // nullptr: too many groups, fold in a second launch
                 }
+                const int tree_fold = O <= 64 && splits >= 64;
                 dim3 grid((u32)splits, (u32)O);
-                if (vec) reduce_rows_block_kernel<T, KIND, VEC><<<grid, kRedThreads, 0, s>>>(in, out, part, R, seg, (u32)splits, pl.factor);
-                else reduce_rows_block_kernel<T, KIND, 1><<<grid, kRedThreads, 0, s>>>(in, out, part, R, seg, (u32)splits, pl.factor);
-                if (splits > 1) {
+                if (vec) reduce_rows_block_kernel<T, KIND, VEC><<<grid, kRedThreads, 0, s>>>(in, out, part, R, seg, (u32)splits, pl.factor, counters, tree_fold);
+                else reduce_rows_block_kernel<T, KIND, 1><<<grid, kRedThreads, 0, s>>>(in, out, part, R, seg, (u32)splits, pl.factor, counters, tree_fold);
+                if (splits > 1 && !counters) {
                     check_launch(where);
-                    if (O <= 64 && splits >= 64) reduce_partials_block_kernel<T, KIND><<<(u32)O, kRedThreads, 0, s>>>(part, out, (u32)splits, pl.factor);
+                    if (tree_fold) reduce_partials_block_kernel<T, KIND><<<(u32)O, kRedThreads, 0, s>>>(part, out, (u32)splits, pl.factor);
                     else reduce_partials_kernel<T, KIND><<<(u32)((O + kRedThreads - 1) / kRedThreads), kRedThreads, 0, s>>>(part, out, O, (u32)splits, 0, pl.factor);
                 }
             }
@@ -477,7 +551,9 @@ void red_launch(const RedPlan& pl, const T* in, T* out, const char* where) {
         const int v = vec ? VEC : 1;
         u64 gx = (I + (u64)kColLanes * v - 1) / ((u64)kColLanes * v);
         u64 gz = O < 65535 ? O : 65535;
-        u64 want = gx * gz >= (u64)sms * 8 ? 1 : ((u64)sms * 8 + gx * gz - 1) / (gx * gz);
+        static int occ = 0;
+        if (!occ) occ = resident_blocks((const void*)reduce_cols_kernel<T, KIND, VEC>, kColLanes * kColRows);
+        u64 want = split_count(gx * gz, (u64)sms * occ);
         u64 max_splits = (R + 63) / 64;  // at least 64 rows per split
         u64 splits = want < max_splits ? want : max_splits;
         if (splits < 1) splits = 1;
@@ -485,14 +561,16 @@ void red_launch(const RedPlan& pl, const T* in, T* out, const char* where) {
         u64 seg = (R + splits - 1) / splits;
         splits = (R + seg - 1) / seg;
         Acc* part = nullptr;
+        u32* counters = nullptr;
         if (splits > 1) {
             part = static_cast<Acc*>(scratch(sizeof(Acc) * splits * O * I));
             if (!part) return;
+            counters = arrival_counters(O * gx);
         }
         dim3 grid((u32)gx, (u32)splits, (u32)gz);
-        if (vec) reduce_cols_kernel<T, KIND, VEC><<<grid, kColLanes * kColRows, 0, s>>>(in, out, part, O, R, I, seg, (u32)splits, pl.factor);
-        else reduce_cols_kernel<T, KIND, 1><<<grid, kColLanes * kColRows, 0, s>>>(in, out, part, O, R, I, seg, (u32)splits, pl.factor);
-        if (splits > 1) {
+        if (vec) reduce_cols_kernel<T, KIND, VEC><<<grid, kColLanes * kColRows, 0, s>>>(in, out, part, O, R, I, seg, (u32)splits, pl.factor, counters);
+        else reduce_cols_kernel<T, KIND, 1><<<grid, kColLanes * kColRows, 0, s>>>(in, out, part, O, R, I, seg, (u32)splits, pl.factor, counters);
+        if (splits > 1 && !counters) {
             check_launch(where);
             u64 count = O * I;
             reduce_partials_kernel<T, KIND><<<(u32)((count + kRedThreads - 1) / kRedThreads), kRedThreads, 0, s>>>(part, out, count, (u32)splits, 1, pl.factor);

@@ -93,6 +93,40 @@ const size_t* resolve_metadata(const size_t* meta, size_t count) {
     return t_meta_copy.data();
 }
 
+int resident_blocks(const void* kernel, int threads) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) {
+        cudaGetLastError();
+        n = 1;
+    }
+    return n;
+}
+
+// Arrival counters of the split reductions: kArrivalCounters zeroed words per host thread and
+// device, allocated on first use.  The kernels leave them zeroed.
+constexpr size_t kArrivalCounters = 16384;
+thread_local uint32_t* t_counters[64] = {nullptr};
+
+uint32_t* arrival_counters(uint64_t count) {
+    if (count > kArrivalCounters) return nullptr;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!t_counters[dev]) {
+        void* p = nullptr;
+        if (cudaMalloc(&p, kArrivalCounters * sizeof(uint32_t)) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;  // the caller folds in a second launch instead
+        }
+        if (cudaMemset(p, 0, kArrivalCounters * sizeof(uint32_t)) != cudaSuccess) {
+            cudaGetLastError();
+            cudaFree(p);
+            return nullptr;
+        }
+        t_counters[dev] = static_cast<uint32_t*>(p);
+    }
+    return t_counters[dev];
+}
+
 void* scratch(size_t bytes) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {

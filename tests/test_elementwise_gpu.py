@@ -241,3 +241,31 @@ def test_inconsistent_metadata_is_reported(cuda):
             return [ctypes.c_size_t(n), ctypes.c_size_t(2), META, a, b, o], {"out": (oh, np.float32, n)}
 
         be.call("add", D.F32, [10, 9, 9, 1, 9, 1, 0, 0], build)
+
+
+@pytest.mark.parametrize("op", ["add", "sub", "div", "mul"])
+def test_16bit_float_arithmetic_is_bit_exact_on_random_bit_patterns(oracle, cuda, op):
+    """bf16 / f16 add and sub run on the packed 16-bit adder and div on the approximate reciprocal
+    with an exact fallback near rounding midpoints; both must give the bits of "compute in f32,
+    round once" that the CPU backend produces.  Operands are raw random bit patterns (every
+    exponent, subnormals, infinities, NaNs) plus pairs constructed to have close exponents,
+    where sums cancel and quotients land near 1."""
+    rng = np.random.default_rng(17 + len(op))
+    n = 1 << 21
+    for dt in (D.BF16, D.F16):
+        a = rng.integers(0, 1 << 16, n, dtype=np.uint16)
+        b = rng.integers(0, 1 << 16, n, dtype=np.uint16)
+        # second half: b = a with the low mantissa bits and the sign re-drawn -> same or adjacent binade
+        h = n // 2
+        low_bits = 8 if dt is D.BF16 else 11
+        b[h:] = (a[h:] & np.uint16(0x7FFF & ~((1 << low_bits) - 1))) | rng.integers(0, 1 << low_bits, n - h, dtype=np.uint16) \
+            | (rng.integers(0, 2, n - h, dtype=np.uint16) << np.uint16(15))
+        a, b = a.view(dt.np_storage), b.view(dt.np_storage)
+        ref = H.run_binary(oracle, op, dt, [n], [1], [1], 0, 0, a, b)
+        got = H.run_binary(cuda, op, dt, [n], [1], [1], 0, 0, a, b)
+        H.assert_same(op, dt, got, ref, what="bit-patterns")
+        # the strided kernels share the packed cores: a transposed view of the same data
+        r, c = 1024, n // 1024
+        ref = H.run_binary(oracle, op, dt, [r, c], [1, r], [c, 1], 0, 0, a, b)
+        got = H.run_binary(cuda, op, dt, [r, c], [1, r], [c, 1], 0, 0, a, b)
+        H.assert_same(op, dt, got, ref, what="bit-patterns-transposed")
