@@ -122,6 +122,8 @@ const size_t* resolve_metadata(const size_t* meta, size_t count);
 void* scratch(size_t bytes);
 
 int sm_count();
+// Blocks of `kernel` that stay resident on one SM at this block size and dynamic shared memory (at least 1).
+int resident_blocks(const void* kernel, int threads, size_t dynamic_smem = 0);
 
 inline uint32_t ceil_div_u32(uint64_t a, uint64_t b) { return (uint32_t)((a + b - 1) / b); }
 

@@ -298,7 +298,7 @@ __device__ __forceinline__ void ew_tile_coord(int i, int& row, int& vcol) {
 }
 
 template <class F, class T, class O, int NIN, int VEC>
-__global__ void __launch_bounds__(kEwThreads, 4) ew_tile_kernel(F f, const T* a, const T* b, O* out, EwTileParams P) {
+__global__ void __launch_bounds__(kEwThreads, sizeof(T) == 2 ? 6 : 4) ew_tile_kernel(F f, const T* a, const T* b, O* out, EwTileParams P) {
     constexpr int TILE = EwTile<T>::kTile;
     constexpr int PITCH = EwTile<T>::kPitch;
     constexpr int VPR = TILE / VEC;                       // vectors per tile row

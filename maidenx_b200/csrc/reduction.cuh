@@ -478,7 +478,6 @@ inline u64 split_count(u64 groups, u64 capacity) {
     u64 s = capacity / groups;
     return s < 1 ? 1 : s;
 }
-int resident_blocks(const void* kernel, int threads);  // occupancy of a kernel (blocks per SM), at least 1
 u32* arrival_counters(u64 count);                      // zeroed counters for last_arrival, or nullptr if count is too large
 
 void red_plan_dims(RedPlan& pl, size_t num_els, size_t num_dims, size_t num_red, const size_t* hm);

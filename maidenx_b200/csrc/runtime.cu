@@ -93,9 +93,9 @@ const size_t* resolve_metadata(const size_t* meta, size_t count) {
     return t_meta_copy.data();
 }
 
-int resident_blocks(const void* kernel, int threads) {
+int resident_blocks(const void* kernel, int threads, size_t dynamic_smem) {
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, dynamic_smem) != cudaSuccess || n < 1) {
         cudaGetLastError();
         n = 1;
     }
