@@ -267,6 +267,35 @@ void* mx_mlp_output(void* mlp);
 float* mx_mlp_loss_ptr(void* mlp);
 float mx_mlp_loss(void* mlp);
 
+/* ---- data-parallel exchange fused with the SGD step, over NVLink (maidenx_b200/csrc/dp_sync.cu) --
+ * No counterpart in the reference, which trains on one device; the per-rank arithmetic is its
+ * SGD step (crates/maidenx_nn/src/optimizers/sgd.rs:17-26) applied to the summed gradient.
+ * Every rank provides an "arena" that is mapped into all ranks (peer pointers) and optionally bound
+ * to a multicast address; the library never allocates or exchanges it.
+ *   mx_dp_barrier      flag barrier across ranks, queued on `stream` (NULL: the thread's stream);
+ *                      peer_arenas[p] + flag_offset = `world` zero-initialised u32 flags in rank p's
+ *                      arena; `epoch` grows by one per barrier; a wait gives up after about two
+ *                      seconds and stores 1 + peer in *err (device word).
+ *   mx_dp_reduce_sgd   this rank's shard of one layer: g = sum over ranks of the gradient at
+ *                      grad_offset (multimem.ld_reduce through multicast_arena, or peer loads when
+ *                      it is NULL); master_shard -= step * g; the rounded weights are written to
+ *                      weight_offset of EVERY arena (multimem.st or peer stores).  The scalar bias
+ *                      (gradient slot at bias_grad_offset) is updated by every rank.  dtype 0 = bf16,
+ *                      1 = f16; shard_begin and shard_elems count elements and are multiples of 8.
+ * mx_mlp_create_dp / mx_mlp_train_step_dp run the MLP step on top of these: gradients and 16-bit
+ * weights live in the arena (mx_mlp_dp_arena_bytes, zero-filled, 4 KiB aligned), `batch` is the
+ * rank's share, and each layer's exchange overlaps the backward of the layers below it.
+ * mx_mlp_dp_status waits for the exchange and returns 0 or 1 + the peer a barrier gave up on. */
+void mx_dp_barrier(void* const* peer_arenas, size_t flag_offset, int rank, int world, uint32_t epoch, uint32_t* err, void* stream);
+void mx_dp_reduce_sgd(int dtype, void* const* peer_arenas, void* multicast_arena, int rank, int world, size_t grad_offset, size_t weight_offset,
+                      size_t bias_grad_offset, float* master_shard, size_t shard_begin, size_t shard_elems, float* master_bias, void* bias16,
+                      float step, void* stream);
+size_t mx_mlp_dp_arena_bytes(int layers, size_t dim);
+void* mx_mlp_create_dp(int layers, size_t dim, size_t batch, int dtype, uint64_t seed, int rank, int world, void* const* peer_arenas,
+                       void* multicast_arena);
+void mx_mlp_train_step_dp(void* mlp, const void* x, const void* y, float lr, float grad_scale);
+uint32_t mx_mlp_dp_status(void* mlp);
+
 #ifdef __cplusplus
 }
 #else

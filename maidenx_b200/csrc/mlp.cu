@@ -32,9 +32,14 @@ void mx_mse_loss_grad_bf16(size_t, const mx_bf16*, const mx_bf16*, mx_bf16*, flo
 void mx_mse_loss_grad_f16(size_t, const mx_f16*, const mx_f16*, mx_f16*, float*);
 void mx_sgd_update_bf16(size_t, float*, const mx_bf16*, mx_bf16*, float, float);
 void mx_sgd_update_f16(size_t, float*, const mx_f16*, mx_f16*, float, float);
+void mx_dp_barrier(void* const*, size_t, int, int, uint32_t, uint32_t*, void*);
+void mx_dp_reduce_sgd(int, void* const*, void*, int, int, size_t, size_t, size_t, float*, size_t, size_t, float*, void*, float, void*);
+void mx_mlp_destroy(void*);
 }
 
 namespace mx {
+
+constexpr int kMlpMaxWorld = 16;
 
 struct Mlp {
     int layers = 0;
@@ -51,7 +56,22 @@ struct Mlp {
     const uint16_t* x = nullptr;         // input batch of the current step
     float* loss = nullptr;               // device scalar
     std::vector<void*> owned;
+    // data-parallel mode over peer-mapped arenas (dp_sync.cu); world == 1 and dp == false otherwise
+    bool dp = false;
+    int rank = 0, world = 1;
+    void* peer[kMlpMaxWorld] = {nullptr};  // every rank's arena as mapped here; peer[rank] is the local one
+    void* mc = nullptr;                    // multicast address of the arenas, or NULL
+    std::vector<size_t> gw_off, w_off, gb_off;  // byte offsets of a layer's buffers inside every arena
+    size_t shard_begin = 0, shard_elems = 0;    // this rank's slice of every weight matrix (elements)
+    cudaStream_t side = nullptr;                // the exchange runs here, beside the backward of the layers below
+    std::vector<cudaEvent_t> ev_grad, ev_done;  // per layer: gradient ready (main stream) / new weights landed (side stream)
+    uint32_t epoch = 0;                         // barrier counter, the same sequence on every rank
+    uint32_t* dp_err = nullptr;                 // device word: 0, or 1 + the peer a barrier gave up on
 };
+
+// Arena layout: [flags, 4 KiB][per layer: weight gradient | 16-bit weights | bias-gradient slot], each 4 KiB aligned.
+static size_t arena_align(size_t b) { return (b + 4095) / 4096 * 4096; }
+static size_t arena_layer_bytes(size_t dim) { return 2 * arena_align(dim * dim * 2) + 4096; }
 
 static void* dmalloc(Mlp* m, size_t bytes) {
     void* p = nullptr;
@@ -75,12 +95,14 @@ __host__ __device__ inline float uniform_pm(uint64_t seed, uint64_t i, float bou
     float u = (float)(r >> 40) * (1.0f / 16777216.0f);  // [0, 1)
     return (2.0f * u - 1.0f) * bound;
 }
+// Fills the 16-bit working copy [0, n) (when w16 != NULL) and the f32 master values of
+// [m_begin, m_begin + m_count) into w32[0 .. m_count): the master copy may be just a shard.
 template <class T>
-__global__ void init_weights_kernel(float* w32, T* w16, uint64_t n, uint64_t seed, float bound) {
+__global__ void init_weights_kernel(float* w32, uint64_t m_begin, uint64_t m_count, T* w16, uint64_t n, uint64_t seed, float bound) {
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
         float v = uniform_pm(seed, i, bound);
-        w32[i] = v;
-        w16[i] = from_f32<T>(v);
+        if (i >= m_begin && i - m_begin < m_count) w32[i - m_begin] = v;
+        if (w16) w16[i] = from_f32<T>(v);
     }
 }
 
@@ -97,6 +119,8 @@ static void forward_t(Mlp* m, const T* x) {
     m->x = reinterpret_cast<const uint16_t*>(x);
     const T* prev = x;
     for (int l = 0; l < m->layers; l++) {
+        // data-parallel mode: the layer's weights of the previous step must have landed from every rank
+        if (m->dp) cudaStreamWaitEvent(ctx().stream, m->ev_done[l], 0);
         // out [B, D], A [B, D] strides [D, 1], B = W^T view: shape [D, D] strides [1, D]
         const size_t meta[] = {2, 2, 2, B, D, B, D, D, D, D, 1, 1, D, 0, 0};
         matmul_call<T>(B * D, meta, prev, reinterpret_cast<const T*>(m->w16[l]), reinterpret_cast<T*>(m->z));
@@ -137,14 +161,24 @@ static void backward_layer_t(Mlp* m, int l) {
     }
     const T* a_prev = l == 0 ? reinterpret_cast<const T*>(m->x) : reinterpret_cast<const T*>(m->a[l - 1]);
     // dW [D_out, D_in] = du^T . a_prev: A = transposed view of du (shape [D, B], strides [1, D]), B = a_prev [B, D]
-    {
+    auto weight_grad = [&]() {
         const size_t meta[] = {2, 2, 2, D, D, D, B, B, D, 1, D, D, 1, 0, 0};
         matmul_call<T>(D * D, meta, du, a_prev, reinterpret_cast<T*>(m->gw[l]));
-    }
+    };
     // gradient for the layer below: da_prev [B, D_in] = du [B, D_out] . W [D_out, D_in]
-    if (l > 0) {
+    auto input_grad = [&]() {
+        if (l == 0) return;
         const size_t meta[] = {2, 2, 2, B, D, B, D, D, D, D, 1, D, 1, 0, 0};
         matmul_call<T>(n, meta, du, reinterpret_cast<const T*>(m->w16[l]), reinterpret_cast<T*>(m->d_act));
+    };
+    if (m->dp) {
+        // the input gradient reads W[l], which the exchange overwrites once every rank has its dW[l]:
+        // queue it first, so "dW[l] done" implies "W[l] no longer needed"
+        input_grad();
+        weight_grad();
+    } else {
+        weight_grad();
+        input_grad();
     }
 }
 
@@ -162,29 +196,52 @@ static void sgd_layer_t(Mlp* m, int l, float lr, float grad_scale) {
 
 }  // namespace mx
 
-using namespace mx;
+namespace mx {
 
-extern "C" {
-
-// dtype: 0 = bf16, 1 = f16.  Weights are initialised U(-1/sqrt(dim), 1/sqrt(dim)) from `seed`
-// (Kaiming-uniform with a = sqrt(5)), the scalar biases likewise; identical on every rank.
-void* mx_mlp_create(int layers, size_t dim, size_t batch, int dtype, uint64_t seed) {
+// Shared by mx_mlp_create and mx_mlp_create_dp.  peer == NULL: single-device engine.
+static Mlp* mlp_create_impl(int layers, size_t dim, size_t batch, int dtype, uint64_t seed, int rank, int world, void* const* peer, void* multicast) {
+    const char* where = peer ? "mx_mlp_create_dp" : "mx_mlp_create";
     if (layers <= 0 || dim == 0 || batch == 0 || (dtype != 0 && dtype != 1)) return nullptr;
+    const size_t wn = dim * dim, an = batch * dim;
+    if (peer && (world < 1 || world > kMlpMaxWorld || rank < 0 || rank >= world || wn % (8 * (size_t)world) != 0)) {
+        set_error(kErrBadMetadata, 0, where);
+        return nullptr;
+    }
     Mlp* m = new Mlp();
     m->layers = layers;
     m->dim = dim;
     m->batch = batch;
     m->is_bf16 = dtype == 0;
-    const size_t wn = dim * dim, an = batch * dim;
+    m->dp = peer != nullptr;
+    m->rank = peer ? rank : 0;
+    m->world = peer ? world : 1;
+    m->shard_elems = wn / (size_t)m->world;
+    m->shard_begin = m->shard_elems * (size_t)m->rank;
+    char* arena = nullptr;
+    if (peer) {
+        for (int p = 0; p < world; p++) m->peer[p] = peer[p];
+        m->mc = multicast;
+        arena = static_cast<char*>(peer[rank]);
+    }
     bool ok = true;
     for (int l = 0; l < layers && ok; l++) {
         // biases live in 256-byte slots so that every pointer handed to a vector kernel is aligned
-        m->w32.push_back(static_cast<float*>(dmalloc(m, wn * 4)));
+        m->w32.push_back(static_cast<float*>(dmalloc(m, m->shard_elems * 4)));  // master weights: only this rank's shard
         m->b32.push_back(static_cast<float*>(dmalloc(m, 256)));
-        m->w16.push_back(static_cast<uint16_t*>(dmalloc(m, wn * 2)));
         m->b16.push_back(static_cast<uint16_t*>(dmalloc(m, 256)));
-        m->gw.push_back(static_cast<uint16_t*>(dmalloc(m, wn * 2)));
-        m->gb.push_back(static_cast<uint16_t*>(dmalloc(m, 256)));
+        if (peer) {
+            const size_t base = 4096 + (size_t)l * arena_layer_bytes(dim);
+            m->gw_off.push_back(base);
+            m->w_off.push_back(base + arena_align(wn * 2));
+            m->gb_off.push_back(base + 2 * arena_align(wn * 2));
+            m->gw.push_back(reinterpret_cast<uint16_t*>(arena + m->gw_off[l]));
+            m->w16.push_back(reinterpret_cast<uint16_t*>(arena + m->w_off[l]));
+            m->gb.push_back(reinterpret_cast<uint16_t*>(arena + m->gb_off[l]));
+        } else {
+            m->w16.push_back(static_cast<uint16_t*>(dmalloc(m, wn * 2)));
+            m->gw.push_back(static_cast<uint16_t*>(dmalloc(m, wn * 2)));
+            m->gb.push_back(static_cast<uint16_t*>(dmalloc(m, 256)));
+        }
         m->u.push_back(static_cast<uint16_t*>(dmalloc(m, an * 2)));
         m->a.push_back(l == layers - 1 ? nullptr : static_cast<uint16_t*>(dmalloc(m, an * 2)));
         ok = m->w32[l] && m->b32[l] && m->w16[l] && m->b16[l] && m->gw[l] && m->gb[l] && m->u[l] && (l == layers - 1 || m->a[l]);
@@ -193,32 +250,78 @@ void* mx_mlp_create(int layers, size_t dim, size_t batch, int dtype, uint64_t se
     m->d_act = static_cast<uint16_t*>(dmalloc(m, an * 2));
     m->d_pre = static_cast<uint16_t*>(dmalloc(m, an * 2));
     m->loss = static_cast<float*>(dmalloc(m, 256));
-    ok = ok && m->z && m->d_act && m->d_pre && m->loss;
+    m->dp_err = static_cast<uint32_t*>(dmalloc(m, 256));
+    ok = ok && m->z && m->d_act && m->d_pre && m->loss && m->dp_err;
+    if (ok && peer) {
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);
+        ok = cudaStreamCreateWithPriority(&m->side, cudaStreamNonBlocking, hi) == cudaSuccess;
+        for (int l = 0; l < layers && ok; l++) {
+            cudaEvent_t e1 = nullptr, e2 = nullptr;
+            ok = cudaEventCreateWithFlags(&e1, cudaEventDisableTiming) == cudaSuccess && cudaEventCreateWithFlags(&e2, cudaEventDisableTiming) == cudaSuccess;
+            m->ev_grad.push_back(e1);
+            m->ev_done.push_back(e2);
+        }
+    }
     if (!ok) {
-        for (void* p : m->owned) cudaFree(p);
-        delete m;
+        set_error(kErrCuda, (int)cudaGetLastError(), where);
+        mx_mlp_destroy(m);
         return nullptr;
     }
     const float bound = 1.0f / std::sqrt((float)dim);
+    cudaStream_t s = ctx().stream;
+    cudaMemsetAsync(m->dp_err, 0, 256, s);
     for (int l = 0; l < layers; l++) {
-        cudaMemsetAsync(m->b32[l], 0, 256, ctx().stream);
-        cudaMemsetAsync(m->b16[l], 0, 256, ctx().stream);
-        cudaMemsetAsync(m->gb[l], 0, 256, ctx().stream);
+        cudaMemsetAsync(m->b32[l], 0, 256, s);
+        cudaMemsetAsync(m->b16[l], 0, 256, s);
+        cudaMemsetAsync(m->gb[l], 0, 256, s);
         if (m->is_bf16) {
-            init_weights_kernel<bf16><<<1024, 256, 0, ctx().stream>>>(m->w32[l], reinterpret_cast<bf16*>(m->w16[l]), wn, seed + 2 * l, bound);
-            init_weights_kernel<bf16><<<1, 32, 0, ctx().stream>>>(m->b32[l], reinterpret_cast<bf16*>(m->b16[l]), 1, seed + 2 * l + 1, bound);
+            init_weights_kernel<bf16><<<1024, 256, 0, s>>>(m->w32[l], m->shard_begin, m->shard_elems, reinterpret_cast<bf16*>(m->w16[l]), wn, seed + 2 * l, bound);
+            init_weights_kernel<bf16><<<1, 32, 0, s>>>(m->b32[l], 0, 1, reinterpret_cast<bf16*>(m->b16[l]), 1, seed + 2 * l + 1, bound);
         } else {
-            init_weights_kernel<f16><<<1024, 256, 0, ctx().stream>>>(m->w32[l], reinterpret_cast<f16*>(m->w16[l]), wn, seed + 2 * l, bound);
-            init_weights_kernel<f16><<<1, 32, 0, ctx().stream>>>(m->b32[l], reinterpret_cast<f16*>(m->b16[l]), 1, seed + 2 * l + 1, bound);
+            init_weights_kernel<f16><<<1024, 256, 0, s>>>(m->w32[l], m->shard_begin, m->shard_elems, reinterpret_cast<f16*>(m->w16[l]), wn, seed + 2 * l, bound);
+            init_weights_kernel<f16><<<1, 32, 0, s>>>(m->b32[l], 0, 1, reinterpret_cast<f16*>(m->b16[l]), 1, seed + 2 * l + 1, bound);
         }
     }
-    check_launch("mx_mlp_create");
+    check_launch(where);
     return m;
+}
+
+}  // namespace mx
+
+using namespace mx;
+
+extern "C" {
+
+// dtype: 0 = bf16, 1 = f16.  Weights are initialised U(-1/sqrt(dim), 1/sqrt(dim)) from `seed`
+// (Kaiming-uniform with a = sqrt(5)), the scalar biases likewise; identical on every rank.
+void* mx_mlp_create(int layers, size_t dim, size_t batch, int dtype, uint64_t seed) {
+    return mlp_create_impl(layers, dim, batch, dtype, seed, 0, 1, nullptr, nullptr);
+}
+
+// Bytes of the peer-mapped arena every rank must provide to mx_mlp_create_dp.
+size_t mx_mlp_dp_arena_bytes(int layers, size_t dim) { return 4096 + (size_t)(layers > 0 ? layers : 0) * arena_layer_bytes(dim); }
+
+// Data-parallel engine.  peer_arenas[p]: rank p's arena (mx_mlp_dp_arena_bytes bytes, zero-filled,
+// 4 KiB aligned) as mapped into this process; multicast_arena: the multicast address bound to all of
+// them, or NULL (then the exchange uses peer loads and stores).  `batch` is this rank's share of the
+// global batch.  Gradients, 16-bit weights and the barrier flags live in the arena; dim * dim must be
+// a multiple of 8 * world.  The arenas must stay mapped until mx_mlp_destroy.
+void* mx_mlp_create_dp(int layers, size_t dim, size_t batch, int dtype, uint64_t seed, int rank, int world, void* const* peer_arenas,
+                       void* multicast_arena) {
+    if (!peer_arenas) return nullptr;
+    return mlp_create_impl(layers, dim, batch, dtype, seed, rank, world, peer_arenas, multicast_arena);
 }
 
 void mx_mlp_destroy(void* h) {
     Mlp* m = static_cast<Mlp*>(h);
     if (!m) return;
+    if (m->side) {
+        cudaStreamSynchronize(m->side);
+        cudaStreamDestroy(m->side);
+    }
+    for (cudaEvent_t e : m->ev_grad) if (e) cudaEventDestroy(e);
+    for (cudaEvent_t e : m->ev_done) if (e) cudaEventDestroy(e);
     for (void* p : m->owned) cudaFree(p);
     delete m;
 }
@@ -242,9 +345,50 @@ void mx_mlp_backward_layer(void* h, int l) {
 void mx_mlp_sgd_layer(void* h, int l, float lr, float grad_scale) {
     Mlp* m = static_cast<Mlp*>(h);
     if (l < 0 || l >= m->layers) return;
+    if (m->dp) {  // the master weights are sharded: the update belongs to mx_mlp_train_step_dp
+        set_error(kErrUnsupported, 0, "mx_mlp_sgd_layer");
+        return;
+    }
     if (m->is_bf16) sgd_layer_t<bf16>(m, l, lr, grad_scale);
     else sgd_layer_t<f16>(m, l, lr, grad_scale);
 }
+// One whole data-parallel training step: forward, loss, backward, and per layer the fused
+// gradient exchange + SGD update (dp_sync.cu) on a side stream, so that the exchange of layer l
+// runs beside the backward of the layers below it.  `grad_scale` multiplies the summed gradient
+// (1 / world for the mean over the global batch).  Every rank must make the same sequence of calls.
+void mx_mlp_train_step_dp(void* h, const void* x, const void* y, float lr, float grad_scale) {
+    Mlp* m = static_cast<Mlp*>(h);
+    if (!m->dp) {
+        set_error(kErrUnsupported, 0, "mx_mlp_train_step_dp");
+        return;
+    }
+    cudaStream_t main_stream = ctx().stream;
+    mx_mlp_forward(h, x);
+    mx_mlp_loss_backward(h, y);
+    const size_t flag_off = 0;
+    for (int l = m->layers - 1; l >= 0; l--) {
+        mx_mlp_backward_layer(h, l);
+        cudaEventRecord(m->ev_grad[l], main_stream);
+        cudaStreamWaitEvent(m->side, m->ev_grad[l], 0);
+        mx_dp_barrier(m->peer, flag_off, m->rank, m->world, ++m->epoch, m->dp_err, m->side);
+        mx_dp_reduce_sgd(m->is_bf16 ? 0 : 1, m->peer, m->mc, m->rank, m->world, m->gw_off[l], m->w_off[l], m->gb_off[l], m->w32[l], m->shard_begin,
+                         m->shard_elems, m->b32[l], m->b16[l], lr * grad_scale, m->side);
+        mx_dp_barrier(m->peer, flag_off, m->rank, m->world, ++m->epoch, m->dp_err, m->side);
+        cudaEventRecord(m->ev_done[l], m->side);
+    }
+    check_launch("mx_mlp_train_step_dp");
+}
+
+// Waits for the exchange of the last step and returns 0, or 1 + the peer rank a barrier stopped waiting for.
+uint32_t mx_mlp_dp_status(void* h) {
+    Mlp* m = static_cast<Mlp*>(h);
+    uint32_t v = 0;
+    if (!m->dp) return 0;
+    cudaStreamSynchronize(m->side);
+    cudaMemcpy(&v, m->dp_err, sizeof(v), cudaMemcpyDeviceToHost);
+    return v;
+}
+
 // Device pointers for the data-parallel driver (gradient all-reduce) and for parity checks.
 void* mx_mlp_weight_grad(void* h, int l) { return static_cast<Mlp*>(h)->gw[l]; }
 void* mx_mlp_bias_grad(void* h, int l) { return static_cast<Mlp*>(h)->gb[l]; }

@@ -6,6 +6,13 @@ as soon as that layer's backward has been queued, so the transfer overlaps the b
 layers below.  Ranks hold identical weights (same seed) and different batch shards; the
 gradient of the global-batch mean loss is the average of the local gradients, applied as
 `grad_scale = 1 / world` inside the fused SGD update.
+
+`DpMlp` is the NVLink-native variant: gradients and 16-bit weights live in a symmetric-memory
+arena that every rank maps, and the library's own kernels (csrc/dp_sync.cu) do the exchange fused
+with the optimizer step - in-switch reduction and multicast stores when the arena has a multicast
+address, peer loads and stores otherwise.  torch.distributed only allocates and exchanges the
+arena.  `make_mlp` picks it for world > 1 and falls back to the NCCL all-reduce driver when the
+arena cannot be set up.
 """
 from __future__ import annotations
 
@@ -24,6 +31,7 @@ class Mlp:
         if not self.h:
             raise RuntimeError("mx_mlp_create failed (out of memory or bad arguments)")
         self._grad_views = None
+        self.exchange = "none"
 
     def close(self):
         if self.h:
@@ -87,6 +95,74 @@ class Mlp:
         else:
             for l in range(self.layers):
                 self.sgd_layer(l, lr, 1.0)
+
+
+class DpMlp(Mlp):
+    """Data-parallel engine over a peer-mapped arena (see csrc/dp_sync.cu).  Collective: every rank
+    of the default process group must construct it, and call train_step, in the same order."""
+
+    def __init__(self, layers: int, dim: int, batch: int, dtype: str, seed: int, torch, dist, multicast: bool = True):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.lib = _lib.load()
+        self.layers, self.dim, self.batch, self.dtype = layers, dim, batch, dtype
+        self._grad_views = None
+        self.h = None
+        self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        nbytes = int(self.lib.mx_mlp_dp_arena_bytes(layers, dim))
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self._arena = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+        self._hdl = symm_mem.rendezvous(self._arena, dist.group.WORLD.group_name)
+        self._arena.zero_()  # barrier flags and gradient slots start from zero on every rank ...
+        torch.cuda.synchronize()
+        dist.barrier()       # ... before any rank's first barrier kernel can write into them
+        peers = (ctypes.c_void_p * self.world)(*[int(p) for p in self._hdl.buffer_ptrs])
+        mc = int(self._hdl.multicast_ptr) if multicast else 0
+        self.exchange = "multimem" if mc else "peer"
+        self.h = self.lib.mx_mlp_create_dp(layers, dim, batch, DTYPE_ID[dtype], seed, self.rank, self.world, peers, mc or None)
+        if not self.h:
+            raise RuntimeError("mx_mlp_create_dp failed (out of memory or bad arguments)")
+        torch.cuda.synchronize()
+        dist.barrier()       # every rank's weights are initialised before anyone's first exchange
+
+    def train_step(self, x_ptr: int, y_ptr: int, lr: float, torch=None, dist=None, world: int = 1):
+        self.lib.mx_mlp_train_step_dp(self.h, x_ptr, y_ptr, lr, 1.0 / self.world)
+
+    def status(self) -> int:
+        """0, or 1 + the rank a barrier stopped waiting for (waits for the exchange to finish)."""
+        return int(self.lib.mx_mlp_dp_status(self.h))
+
+    def close(self):
+        if self.h:
+            self.lib.mx_mlp_dp_status(self.h)  # drain the side stream before the arena goes away
+        super().close()
+        self._hdl = None
+        self._arena = None
+
+
+def make_mlp(layers: int, dim: int, batch: int, dtype: str, seed: int, torch=None, dist=None, world: int = 1, exchange: str = "auto"):
+    """The engine for `world` ranks: Mlp for one rank, DpMlp for several (exchange "auto",
+    "multimem" or "peer"), Mlp driven with NCCL all-reduces for exchange == "nccl" or when the
+    symmetric-memory arena cannot be set up (every rank takes the same branch: the outcome of the
+    setup is agreed on with an all-reduce)."""
+    if world <= 1:
+        return Mlp(layers, dim, batch, dtype, seed)
+    if exchange != "nccl":
+        m, ok = None, 1
+        try:
+            m = DpMlp(layers, dim, batch, dtype, seed, torch, dist, multicast=exchange != "peer")
+        except Exception as e:  # noqa: BLE001 - any setup failure selects the NCCL driver
+            import sys
+            print(f"[maidenx_b200] symmetric-memory exchange unavailable ({type(e).__name__}: {e}); using NCCL all-reduce", file=sys.stderr)
+            ok = 0
+        flag = torch.tensor([ok], device="cuda", dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 1:
+            return m
+        if m is not None:
+            m.close()
+    m = Mlp(layers, dim, batch, dtype, seed)
+    m.exchange = "nccl"
+    return m
 
 
 class _CudaArray:
