@@ -256,15 +256,33 @@ MLP_LAYERS, MLP_DIM, MLP_GLOBAL_BATCH, MLP_LR = 4, 8192, 16384, 1e-3
 MLP_GEMMS_PER_STEP = 3 * MLP_LAYERS - 1       # dX of the first layer is not needed and not computed
 # kernels launched per step: 11 GEMMs + 4 bias(/gelu) passes + 2 (mse, mse finish) + 3 gelu backward
 # + 8 (bias-gradient sums, two passes each) + 8 SGD updates (weights and bias per layer)
+GEMM_DRAM_BYTES_PER_FLOP = 655.2e6 / 5.4976e11
 MLP_KERNELS_PER_STEP = MLP_GEMMS_PER_STEP + MLP_LAYERS + 2 + (MLP_LAYERS - 1) + 2 * MLP_LAYERS + 2 * MLP_LAYERS
+
+
+EXCHANGE_TEXT = {
+    "none": "none (one rank)",
+    "multimem": "own kernels over NVLink, fused with the SGD step: per layer a flag barrier, multimem.ld_reduce of this rank's 1/N shard of "
+                "the bf16 gradients (in-switch f32 sum), f32 master update, multimem.st of the new bf16 weights to every rank; on a side "
+                "stream beside the backward of the layers below",
+    "peer": "own kernels over NVLink, fused with the SGD step: per layer a flag barrier, peer loads of this rank's 1/N shard of every rank's "
+            "bf16 gradients, f32 master update, peer stores of the new bf16 weights to every rank; on a side stream beside the backward",
+    "multimem-exclusive": "own kernel over NVLink, fused with the SGD step, on SMs of its own (the step's GEMMs run on the remaining SMs): per layer a "
+                          "flag barrier, multimem.ld_reduce of this rank's 1/N shard of the bf16 gradients (in-switch f32 sum), f32 master update, "
+                          "multimem.st of the new bf16 weights to every rank; on a side stream beside the backward of the layers below",
+    "copy": "per layer, on a side stream beside the backward of the layers below: flag barrier, device-to-device copies (copy engines) of this "
+            "rank's 1/N shard of every peer's bf16 gradients, one local kernel (f32 sum in rank order, f32 master update, new bf16 weights), "
+            "copies of the new shard to every peer, flag barrier; no SM waits on NVLink",
+    "nccl": "NCCL all-reduce, one bf16 bucket per layer, overlapped with backward; full-size SGD update on every rank",
+}
 
 
 def mlp_flops(batch):
     return MLP_GEMMS_PER_STEP * 2.0 * batch * MLP_DIM * MLP_DIM
 
 
-def mlp_setup(torch, rank, world):
-    from maidenx_b200.mlp import Mlp
+def mlp_setup(torch, rank, world, dist=None, exchange="auto", exclusive_sms=8):
+    from maidenx_b200.mlp import make_mlp
     local = MLP_GLOBAL_BATCH // world
     g = torch.Generator(device="cuda")
     g.manual_seed(4)
@@ -275,7 +293,7 @@ def mlp_setup(torch, rank, world):
     y = y_all[rank * local:(rank + 1) * local].contiguous()
     del x_all, y_all
     torch.cuda.empty_cache()
-    return Mlp(MLP_LAYERS, MLP_DIM, local, "bf16", seed=6), x, y, local
+    return make_mlp(MLP_LAYERS, MLP_DIM, local, "bf16", 6, torch, dist, world, exchange, exclusive_sms), x, y, local
 
 
 def time_gemm(torch, lib_mod, local_batch, iters=10):
@@ -355,6 +373,11 @@ def main():
     ap.add_argument("--no-sweeps", action="store_true", help="skip the per-case tables (reductions, conv)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--global-batch", type=int, default=None,
+                    help="tuning aid: another global batch than the benchmark's 16384 (the JSON line says so; not a headline number)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "multimem-exclusive", "copy", "multimem", "peer", "nccl"],
+                    help="N > 1: how gradients are exchanged (auto: the library's NVLink kernels, NCCL if symmetric memory is unavailable)")
+    ap.add_argument("--exchange-sms", type=int, default=8, help="multimem-exclusive: SMs given to the exchange kernel")
     ap.add_argument("--only-case", default=None, help="profiling aid: launch just this sweep case --steps times and exit")
     ap.add_argument("--small", action="store_true", help="profiling aid: 8192x8192 / quarter-size tensors for ncu captures")
     args = ap.parse_args()
@@ -382,9 +405,12 @@ def main():
         return
 
     args.warmup = max(args.warmup, 3)
+    if args.global_batch:
+        global MLP_GLOBAL_BATCH
+        MLP_GLOBAL_BATCH = args.global_batch
     if MLP_GLOBAL_BATCH % world != 0:
         raise SystemExit("the global batch must divide evenly over the ranks")
-    mlp, x, y, local_batch = mlp_setup(torch, rank, world)
+    mlp, x, y, local_batch = mlp_setup(torch, rank, world, dist if world > 1 else None, args.exchange, args.exchange_sms)
 
     def step():
         mlp.train_step(x.data_ptr(), y.data_ptr(), MLP_LR, torch, dist, world)
@@ -401,6 +427,8 @@ def main():
     s.record()
     for _ in range(args.steps):
         step()
+    if hasattr(mlp, "join"):
+        mlp.join()  # the exchange of the last step runs on a side stream: the closing event waits for it
     e.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -411,6 +439,9 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_step = float(t.item())
     loss = mlp.loss()
+    mlp_exchange = mlp.exchange
+    if hasattr(mlp, "status") and mlp.status() != 0:
+        raise RuntimeError(f"a cross-rank barrier gave up waiting for rank {mlp.status() - 1}")
     lib.mx_device_synchronize()
     if lib.mx_last_error():
         raise RuntimeError(f"op library reported status {lib.mx_last_error()} at {lib.mx_last_error_where().decode()}")
@@ -424,12 +455,10 @@ def main():
     sweeps_out, roofline, cpu = {}, None, None
     if rank == 0:
         achieved = gemm_flops / gemm_ms / 1e9
-        traffic = None
-        tp = ROOT / "profiles" / "ncu_traffic.json"
-        if tp.exists():
-            per_launch = json.loads(tp.read_text()).get("tc_gemm_kernel", {}).get("dram_bytes_per_flop")
-            if per_launch:
-                traffic = int(per_launch * gemm_flops)
+        # DRAM bytes per launch: the ncu capture of this kernel at [8192, 4096] x 8192 read 595.1 MB and
+        # wrote 60.1 MB for 5.4976e11 flop; same K, tile shape and tile order here, so traffic scales
+        # with the number of output tiles, i.e. with the flops
+        traffic = int(GEMM_DRAM_BYTES_PER_FLOP * gemm_flops)
         roofline = {"bound": "tensor", "kernel": "tc_gemm_kernel", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                     "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": peaks["source"] + " (burst: kernel timed alone)",
                     "launch_shape": f"[{local_batch},{MLP_DIM}] x [{MLP_DIM},{MLP_DIM}]^T bf16", "flops_per_launch": gemm_flops,
@@ -467,9 +496,9 @@ def main():
                 "dtype": "bf16 (f32 accumulate, f32 master weights)",
                 "data": "synthetic (seeded N(0,1) inputs and targets, Kaiming-uniform weights U(-1/sqrt(8192), 1/sqrt(8192)))",
                 "config": {"workload": "MLP data-parallel training step: 4 x Linear(8192->8192) + GELU, MSE, SGD lr=1e-3", "global_batch": MLP_GLOBAL_BATCH,
-                           "per_gpu_batch": local_batch, "parallelism": f"dp{world}", "allreduce": "NCCL, one bf16 bucket per layer, overlapped with backward",
+                           "per_gpu_batch": local_batch, "parallelism": f"dp{world}", "allreduce": EXCHANGE_TEXT[mlp_exchange],
                            "l2": "per-step working set (weights 0.5 GB + activations 2 GB per GPU at N=1) far exceeds the 126 MB L2"},
-                "loss": loss, "clocks": clocks, "gpu_launches": MLP_KERNELS_PER_STEP * args.steps, "roofline": roofline, "e2e": e2e, "cpu_baseline": cpu,
+                "loss": loss, "clocks": clocks, "gpu_launches": (MLP_KERNELS_PER_STEP + (3 * MLP_LAYERS - 2 * MLP_LAYERS if mlp_exchange in ("multimem", "multimem-exclusive", "peer", "copy") else 0)) * args.steps, "roofline": roofline, "e2e": e2e, "cpu_baseline": cpu,
                 "sweeps": sweeps_out}
         print(json.dumps(line))
 

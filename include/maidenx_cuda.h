@@ -282,19 +282,32 @@ float mx_mlp_loss(void* mlp);
  *                      weight_offset of EVERY arena (multimem.st or peer stores).  The scalar bias
  *                      (gradient slot at bias_grad_offset) is updated by every rank.  dtype 0 = bf16,
  *                      1 = f16; shard_begin and shard_elems count elements and are multiples of 8.
+ *                      staged_grads != NULL: the peers' gradient shards were copied to local memory
+ *                      (copy engines) and the weights are written to the local arena only; the caller
+ *                      copies them to the peers.  exclusive_sms = k > 0 (multicast form): k blocks of
+ *                      1024 threads that share their SMs with no GEMM block.
  * mx_mlp_create_dp / mx_mlp_train_step_dp run the MLP step on top of these: gradients and 16-bit
  * weights live in the arena (mx_mlp_dp_arena_bytes, zero-filled, 4 KiB aligned), `batch` is the
  * rank's share, and each layer's exchange overlaps the backward of the layers below it.
- * mx_mlp_dp_status waits for the exchange and returns 0 or 1 + the peer a barrier gave up on. */
+ * mx_mlp_dp_join makes the calling thread's stream wait for the exchange of the last step;
+ * mx_mlp_dp_status waits on the host and returns 0 or 1 + the peer a barrier gave up on. */
 void mx_dp_barrier(void* const* peer_arenas, size_t flag_offset, int rank, int world, uint32_t epoch, uint32_t* err, void* stream);
-void mx_dp_reduce_sgd(int dtype, void* const* peer_arenas, void* multicast_arena, int rank, int world, size_t grad_offset, size_t weight_offset,
-                      size_t bias_grad_offset, float* master_shard, size_t shard_begin, size_t shard_elems, float* master_bias, void* bias16,
-                      float step, void* stream);
+void mx_dp_reduce_sgd(int dtype, void* const* peer_arenas, void* multicast_arena, const void* const* staged_grads, int rank, int world,
+                      size_t grad_offset, size_t weight_offset, size_t bias_grad_offset, float* master_shard, size_t shard_begin, size_t shard_elems,
+                      float* master_bias, void* bias16, float step, int exclusive_sms, void* stream);
 size_t mx_mlp_dp_arena_bytes(int layers, size_t dim);
 void* mx_mlp_create_dp(int layers, size_t dim, size_t batch, int dtype, uint64_t seed, int rank, int world, void* const* peer_arenas,
                        void* multicast_arena);
 void mx_mlp_train_step_dp(void* mlp, const void* x, const void* y, float lr, float grad_scale);
 uint32_t mx_mlp_dp_status(void* mlp);
+void mx_mlp_dp_join(void* mlp);
+/* mode 0: the exchange runs in the library's NVLink kernel (multimem or peer form); exclusive_sms = k > 0 runs the
+ * multimem form as k blocks that keep k SMs to themselves while every GEMM of the step uses the others.
+ * mode 1: transfers by device-to-device copies (copy engines), sum and update in a local kernel.  Returns 0 or -1. */
+int mx_mlp_dp_set_exchange(void* mlp, int mode, int exclusive_sms);
+/* The tensor-core GEMM of the calling thread launches at most `sms` CTAs (0: all SMs), leaving the other SMs to a
+ * concurrent kernel such as the exchange above. */
+void mx_set_gemm_sm_limit(int sms);
 
 #ifdef __cplusplus
 }

@@ -50,13 +50,16 @@ RUNTIME_SIGNATURES = {
     "mx_mlp_loss_ptr": ([ctypes.c_void_p], ctypes.c_void_p),
     "mx_mlp_loss": ([ctypes.c_void_p], ctypes.c_float),
     "mx_dp_barrier": ([ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p], None),
-    "mx_dp_reduce_sgd": ([ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t,
-                          ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p], None),
+    "mx_dp_reduce_sgd": ([ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t,
+                          ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_int, ctypes.c_void_p], None),
     "mx_mlp_dp_arena_bytes": ([ctypes.c_int, ctypes.c_size_t], ctypes.c_size_t),
     "mx_mlp_create_dp": ([ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int, ctypes.c_uint64, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
                           ctypes.c_void_p], ctypes.c_void_p),
     "mx_mlp_train_step_dp": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_float], None),
     "mx_mlp_dp_status": ([ctypes.c_void_p], ctypes.c_uint32),
+    "mx_mlp_dp_join": ([ctypes.c_void_p], None),
+    "mx_mlp_dp_set_exchange": ([ctypes.c_void_p, ctypes.c_int, ctypes.c_int], ctypes.c_int),
+    "mx_set_gemm_sm_limit": ([ctypes.c_int], None),
 }
 
 

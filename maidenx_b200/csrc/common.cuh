@@ -104,6 +104,7 @@ struct ThreadCtx {
     int status = kOk;         // sticky: first error since the last mx_clear_error
     int cuda_error = 0;
     char where[96] = {0};
+    int gemm_sm_limit = 0;    // > 0: the tensor-core GEMM launches at most this many CTAs (SMs left free for a concurrent exchange kernel)
 };
 ThreadCtx& ctx();
 void set_error(int status, int cuda_error, const char* where);

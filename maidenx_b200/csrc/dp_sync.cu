@@ -31,6 +31,8 @@
 // One barrier before the exchange (every rank's gradient of the layer is complete, and nobody
 // still reads the old weights) and one after it (every shard of the new weights has landed).
 // The waiting kernels run on different GPUs, one per GPU, so they are always co-resident.
+#include <cstdlib>
+
 #include "abi_common.cuh"
 #include "ops.cuh"
 
@@ -95,6 +97,11 @@ __device__ __forceinline__ void multimem_st<f16>(void* mc_addr, uint4 v) {
 }
 
 constexpr int kDpThreads = 256;
+constexpr int kDpMaxThreads = 1024;
+// A CTA that asks for this much shared memory cannot share an SM with a CTA of the tensor-core GEMM (about
+// 200 KB), nor with a second one of its own kind: with the GEMM launched on sm_count - k CTAs, k such CTAs get k
+// SMs to themselves and the GEMM's own waits are never queued behind NVLink round trips.
+constexpr int kDpExclusiveSmem = 120 * 1024;
 constexpr int kDpUnroll = 4;  // 16-byte vectors in flight per thread: NVLink round trips are several microseconds
 
 struct DpLayer {
@@ -103,40 +110,81 @@ struct DpLayer {
     size_t shard_begin, shard_elems;             // in elements; both multiples of 8
     float* master_bias;                          // f32 master bias (every rank keeps the scalar)
     void* bias16;                                // local 16-bit working copy of the bias
+    const void* staged[kDpMaxWorld];             // kStaged: local copies of the peers' gradient shards ([rank] unused)
 };
 
-// MC: sums and broadcasts go through the multicast address; otherwise through one peer pointer per rank
-// (ranks are added in rank order, so every run and every rank rounds the same way).
-template <class T, bool MC>
-__global__ void __launch_bounds__(kDpThreads) dp_reduce_sgd_kernel(DpPeers peers, char* mc_base, DpLayer L, int rank, int world, float step) {
+enum { kMulticast = 0, kPeer = 1, kStaged = 2 };
+
+// MODE kMulticast: sums and broadcasts go through the multicast address.
+// MODE kPeer: one peer load and one peer store per rank.
+// MODE kStaged: the peers' shards were copied into local memory beforehand (copy engines) and the new
+// weights are written to the local arena only (the host pushes them to the peers afterwards); the SMs
+// then never wait on NVLink.
+// In the last two, ranks are added in rank order, so every run and every rank rounds the same way.
+template <class T, int MODE>
+__global__ void __launch_bounds__(MODE == kMulticast ? kDpMaxThreads : kDpThreads) dp_reduce_sgd_kernel(DpPeers peers, char* mc_base, DpLayer L, int rank, int world, float step, int) {
+    constexpr int UNROLL = MODE == kMulticast ? kDpUnroll : 2;
     const size_t nvec = L.shard_elems / 8;
-    const size_t stride = (size_t)gridDim.x * kDpThreads;
-    for (size_t v0 = (size_t)blockIdx.x * kDpThreads + threadIdx.x; v0 < nvec; v0 += stride * kDpUnroll) {
-        uint4 g[kDpUnroll];
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t v0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v0 < nvec; v0 += stride * UNROLL) {
+        uint4 g[UNROLL];
+        if constexpr (MODE == kMulticast) {
 #pragma unroll
-        for (int u = 0; u < kDpUnroll; u++) {
-            const size_t v = v0 + u * stride;
-            if (v >= nvec) break;
-            const size_t byte = L.grad_off + (L.shard_begin + v * 8) * 2;
-            if constexpr (MC) {
-                g[u] = multimem_ld_reduce<T>(mc_base + byte);
-            } else {
-                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                for (int p = 0; p < world; p++) {
-                    const uint4 x = __ldcv(reinterpret_cast<const uint4*>(static_cast<const char*>(peers.base[p]) + byte));
-                    const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+            for (int u = 0; u < UNROLL; u++) {
+                const size_t v = v0 + u * stride;
+                if (v < nvec) g[u] = multimem_ld_reduce<T>(mc_base + L.grad_off + (L.shard_begin + v * 8) * 2);
+            }
+        } else {
+            // all loads of the trip first (up to 8 ranks x UNROLL vectors in flight), then the sums
+            constexpr int W = 8;
+            for (int p0 = 0; p0 < world; p0 += W) {
+                uint4 x[UNROLL][W];
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const float2 f = unpack2<T>(w[j]);
-                        acc[2 * j] += f.x;
-                        acc[2 * j + 1] += f.y;
+                for (int u = 0; u < UNROLL; u++) {
+                    const size_t v = v0 + u * stride;
+#pragma unroll
+                    for (int q = 0; q < W; q++) {
+                        const int p = p0 + q;
+                        if (p < world && v < nvec) {
+                            const char* src = (MODE == kStaged && p != rank) ? static_cast<const char*>(L.staged[p]) + v * 16
+                                                                            : static_cast<const char*>(peers.base[p]) + L.grad_off + (L.shard_begin + v * 8) * 2;
+                            x[u][q] = __ldcv(reinterpret_cast<const uint4*>(src));
+                        }
                     }
                 }
-                g[u] = make_uint4(pack2_rn<T>(acc[0], acc[1]), pack2_rn<T>(acc[2], acc[3]), pack2_rn<T>(acc[4], acc[5]), pack2_rn<T>(acc[6], acc[7]));
+#pragma unroll
+                for (int u = 0; u < UNROLL; u++) {
+                    float acc[8];
+                    if (p0 == 0) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) acc[j] = 0.0f;
+                    } else {  // more than 8 ranks: continue from the running sum (kept as f32 bit patterns would cost registers; re-expand)
+                        const uint32_t w[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const float2 f = unpack2<T>(w[j]);
+                            acc[2 * j] = f.x;
+                            acc[2 * j + 1] = f.y;
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < W; q++) {
+                        if (p0 + q < world) {
+                            const uint32_t w[4] = {x[u][q].x, x[u][q].y, x[u][q].z, x[u][q].w};
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                const float2 f = unpack2<T>(w[j]);
+                                acc[2 * j] += f.x;
+                                acc[2 * j + 1] += f.y;
+                            }
+                        }
+                    }
+                    g[u] = make_uint4(pack2_rn<T>(acc[0], acc[1]), pack2_rn<T>(acc[2], acc[3]), pack2_rn<T>(acc[4], acc[5]), pack2_rn<T>(acc[6], acc[7]));
+                }
             }
         }
 #pragma unroll
-        for (int u = 0; u < kDpUnroll; u++) {
+        for (int u = 0; u < UNROLL; u++) {
             const size_t v = v0 + u * stride;
             if (v >= nvec) break;
             float4* m = reinterpret_cast<float4*>(L.master_shard + v * 8);
@@ -161,10 +209,12 @@ __global__ void __launch_bounds__(kDpThreads) dp_reduce_sgd_kernel(DpPeers peers
             m[1] = m1;
             const uint4 out = make_uint4(pack2_rn<T>(m0.x, m0.y), pack2_rn<T>(m0.z, m0.w), pack2_rn<T>(m1.x, m1.y), pack2_rn<T>(m1.z, m1.w));
             const size_t byte = L.weight_off + (L.shard_begin + v * 8) * 2;
-            if constexpr (MC) {
+            if constexpr (MODE == kMulticast) {
                 multimem_st<T>(mc_base + byte, out);
-            } else {
+            } else if constexpr (MODE == kPeer) {
                 for (int p = 0; p < world; p++) __stwt(reinterpret_cast<uint4*>(static_cast<char*>(peers.base[p]) + byte), out);
+            } else {
+                *reinterpret_cast<uint4*>(static_cast<char*>(peers.base[rank]) + byte) = out;
             }
         }
     }
@@ -184,18 +234,31 @@ __global__ void __launch_bounds__(kDpThreads) dp_reduce_sgd_kernel(DpPeers peers
 }
 
 template <class T>
-static void dp_reduce_sgd_launch(const DpPeers& peers, void* mc_base, const DpLayer& L, int rank, int world, float step, cudaStream_t s, const char* where) {
+static void dp_reduce_sgd_launch(const DpPeers& peers, void* mc_base, const DpLayer& L, bool staged, int exclusive_sms, int rank, int world, float step,
+                                 cudaStream_t s, const char* where) {
     if (world < 1 || world > kDpMaxWorld || rank < 0 || rank >= world || L.shard_elems % 8 || L.shard_begin % 8) {
         set_error(kErrBadMetadata, 0, where);
         return;
     }
     const size_t nvec = L.shard_elems / 8;
-    size_t blocks = (nvec + (size_t)kDpThreads * kDpUnroll - 1) / ((size_t)kDpThreads * kDpUnroll);
-    const size_t cap = (size_t)sm_count() * 2;
+    if (exclusive_sms > 0 && !staged && mc_base) {
+        // k CTAs of 1024 threads, one per SM, kept apart from the GEMM by their shared-memory request
+        static bool opted_in = false;
+        if (!opted_in) {
+            cudaFuncSetAttribute(dp_reduce_sgd_kernel<T, kMulticast>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDpExclusiveSmem);
+            opted_in = true;
+        }
+        dp_reduce_sgd_kernel<T, kMulticast><<<exclusive_sms, kDpMaxThreads, kDpExclusiveSmem, s>>>(peers, static_cast<char*>(mc_base), L, rank, world, step, 0);
+        check_launch(where);
+        return;
+    }
+    size_t blocks = (nvec + (size_t)kDpThreads * 2 - 1) / ((size_t)kDpThreads * 2);
+    size_t cap = (size_t)sm_count() * 2;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    if (mc_base) dp_reduce_sgd_kernel<T, true><<<(unsigned)blocks, kDpThreads, 0, s>>>(peers, static_cast<char*>(mc_base), L, rank, world, step);
-    else dp_reduce_sgd_kernel<T, false><<<(unsigned)blocks, kDpThreads, 0, s>>>(peers, nullptr, L, rank, world, step);
+    if (staged) dp_reduce_sgd_kernel<T, kStaged><<<(unsigned)blocks, kDpThreads, 0, s>>>(peers, nullptr, L, rank, world, step, 0);
+    else if (mc_base) dp_reduce_sgd_kernel<T, kMulticast><<<(unsigned)blocks, kDpThreads, 0, s>>>(peers, static_cast<char*>(mc_base), L, rank, world, step, 0);
+    else dp_reduce_sgd_kernel<T, kPeer><<<(unsigned)blocks, kDpThreads, 0, s>>>(peers, nullptr, L, rank, world, step, 0);
     check_launch(where);
 }
 
@@ -222,10 +285,15 @@ void mx_dp_barrier(void* const* peer_arenas, size_t flag_offset, int rank, int w
 
 // The fused exchange + SGD step of one layer for this rank's shard (see the top of this file).
 // dtype: 0 = bf16, 1 = f16.  multicast_arena: the arenas' multicast address, or NULL to use peer
-// loads and stores.  step = lr * grad_scale.  Offsets are bytes inside every arena.
-void mx_dp_reduce_sgd(int dtype, void* const* peer_arenas, void* multicast_arena, int rank, int world, size_t grad_offset, size_t weight_offset,
-                      size_t bias_grad_offset, float* master_shard, size_t shard_begin, size_t shard_elems, float* master_bias, void* bias16,
-                      float step, void* stream) {
+// loads and stores.  staged_grads: NULL, or `world` pointers to local copies of the ranks' gradient
+// shards (entry [rank] is ignored: the own shard is read in place); then the new weights are written
+// to the local arena only and the caller copies them to the peers.  step = lr * grad_scale.  Offsets
+// are bytes inside every arena.  exclusive_sms: 0 = blocks spread over all SMs; k > 0 = k blocks of 1024
+// threads that keep an SM each to themselves (multicast form only; see kDpExclusiveSmem; pair it with
+// mx_set_gemm_sm_limit).
+void mx_dp_reduce_sgd(int dtype, void* const* peer_arenas, void* multicast_arena, const void* const* staged_grads, int rank, int world,
+                      size_t grad_offset, size_t weight_offset, size_t bias_grad_offset, float* master_shard, size_t shard_begin, size_t shard_elems,
+                      float* master_bias, void* bias16, float step, int exclusive_sms, void* stream) {
     DpPeers peers;
     for (int p = 0; p < kDpMaxWorld; p++) peers.base[p] = (p < world && world <= kDpMaxWorld) ? peer_arenas[p] : nullptr;
     DpLayer L;
@@ -237,9 +305,11 @@ void mx_dp_reduce_sgd(int dtype, void* const* peer_arenas, void* multicast_arena
     L.shard_elems = shard_elems;
     L.master_bias = master_bias;
     L.bias16 = bias16;
+    for (int p = 0; p < kDpMaxWorld; p++) L.staged[p] = (staged_grads && p < world && world <= kDpMaxWorld) ? staged_grads[p] : nullptr;
+    const bool staged = staged_grads != nullptr;
     cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : ctx().stream;
-    if (dtype == 0) dp_reduce_sgd_launch<bf16>(peers, multicast_arena, L, rank, world, step, s, "mx_dp_reduce_sgd");
-    else if (dtype == 1) dp_reduce_sgd_launch<f16>(peers, multicast_arena, L, rank, world, step, s, "mx_dp_reduce_sgd");
+    if (dtype == 0) dp_reduce_sgd_launch<bf16>(peers, multicast_arena, L, staged, exclusive_sms, rank, world, step, s, "mx_dp_reduce_sgd");
+    else if (dtype == 1) dp_reduce_sgd_launch<f16>(peers, multicast_arena, L, staged, exclusive_sms, rank, world, step, s, "mx_dp_reduce_sgd");
     else set_error(kErrUnsupported, 0, "mx_dp_reduce_sgd");
 }
 

@@ -474,6 +474,7 @@ bool launch_gemm(bool is_bf16, const void* A, bool a_mn, const void* B, bool b_m
     p.a_mn = a_mn ? 1 : 0;
     p.b_mn = b_mn ? 1 : 0;
     int grid = sm_count();
+    if (ctx().gemm_sm_limit > 0 && ctx().gemm_sm_limit < grid) grid = ctx().gemm_sm_limit;
     if (grid > p.num_tiles) grid = p.num_tiles;
     tc_gemm_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx().stream>>>(ma, mb, md, p, st->err);
     check_launch(where);

@@ -17,6 +17,8 @@
 //
 // The step is split so that a data-parallel driver can overlap the gradient all-reduce of layer
 // l with the backward of layer l-1: forward, loss_backward, backward_layer(l), sgd_layer(l).
+#include <cstdio>
+#include <cstdlib>
 #include <cmath>
 #include <cstring>
 #include <vector>
@@ -33,7 +35,7 @@ void mx_mse_loss_grad_f16(size_t, const mx_f16*, const mx_f16*, mx_f16*, float*)
 void mx_sgd_update_bf16(size_t, float*, const mx_bf16*, mx_bf16*, float, float);
 void mx_sgd_update_f16(size_t, float*, const mx_f16*, mx_f16*, float, float);
 void mx_dp_barrier(void* const*, size_t, int, int, uint32_t, uint32_t*, void*);
-void mx_dp_reduce_sgd(int, void* const*, void*, int, int, size_t, size_t, size_t, float*, size_t, size_t, float*, void*, float, void*);
+void mx_dp_reduce_sgd(int, void* const*, void*, const void* const*, int, int, size_t, size_t, size_t, float*, size_t, size_t, float*, void*, float, int, void*);
 void mx_mlp_destroy(void*);
 }
 
@@ -67,6 +69,11 @@ struct Mlp {
     std::vector<cudaEvent_t> ev_grad, ev_done;  // per layer: gradient ready (main stream) / new weights landed (side stream)
     uint32_t epoch = 0;                         // barrier counter, the same sequence on every rank
     uint32_t* dp_err = nullptr;                 // device word: 0, or 1 + the peer a barrier gave up on
+    // copy-engine exchange: the peers' gradient shards are pulled into `staging`, summed locally, and the new
+    // weights pushed back with plain device-to-device copies, so no SM ever waits on NVLink
+    bool copy_engines = false;
+    int exclusive_sms = 0;  // > 0: the multimem exchange kernel keeps this many SMs to itself and the step's GEMMs use the rest
+    void* staging[kMlpMaxWorld] = {nullptr};
 };
 
 // Arena layout: [flags, 4 KiB][per layer: weight gradient | 16-bit weights | bias-gradient slot], each 4 KiB aligned.
@@ -363,20 +370,93 @@ void mx_mlp_train_step_dp(void* h, const void* x, const void* y, float lr, float
         return;
     }
     cudaStream_t main_stream = ctx().stream;
+    const int saved_limit = ctx().gemm_sm_limit;
+    if (!m->copy_engines && m->mc && m->exclusive_sms > 0 && m->exclusive_sms < sm_count()) ctx().gemm_sm_limit = sm_count() - m->exclusive_sms;
+    // TRACE (temporary): device timeline of one step
+    static int trace = -1;
+    if (trace < 0) trace = getenv("MX_DP_TRACE") ? atoi(getenv("MX_DP_TRACE")) : 0;
+    static int step_no = 0;
+    const bool tr = trace && (++step_no == trace);
+    cudaEvent_t t0 = nullptr, tg[8], tb1[8], tr2[8], tb2[8], tend = nullptr;
+    if (tr) {
+        cudaDeviceSynchronize();
+        cudaEventCreate(&t0); cudaEventCreate(&tend);
+        for (int l = 0; l < m->layers; l++) { cudaEventCreate(&tg[l]); cudaEventCreate(&tb1[l]); cudaEventCreate(&tr2[l]); cudaEventCreate(&tb2[l]); }
+        cudaEventRecord(t0, main_stream);
+    }
     mx_mlp_forward(h, x);
     mx_mlp_loss_backward(h, y);
     const size_t flag_off = 0;
     for (int l = m->layers - 1; l >= 0; l--) {
         mx_mlp_backward_layer(h, l);
         cudaEventRecord(m->ev_grad[l], main_stream);
+        if (tr) cudaEventRecord(tg[l], main_stream);
         cudaStreamWaitEvent(m->side, m->ev_grad[l], 0);
         mx_dp_barrier(m->peer, flag_off, m->rank, m->world, ++m->epoch, m->dp_err, m->side);
-        mx_dp_reduce_sgd(m->is_bf16 ? 0 : 1, m->peer, m->mc, m->rank, m->world, m->gw_off[l], m->w_off[l], m->gb_off[l], m->w32[l], m->shard_begin,
-                         m->shard_elems, m->b32[l], m->b16[l], lr * grad_scale, m->side);
+        if (tr) cudaEventRecord(tb1[l], m->side);
+        const size_t shard_bytes = m->shard_elems * 2, shard_byte0 = m->shard_begin * 2;
+        if (m->copy_engines) {
+            // pull my shard of every peer's gradient, starting with the next rank so that no peer is asked by everyone at once
+            for (int k = 1; k < m->world; k++) {
+                const int p = (m->rank + k) % m->world;
+                cudaMemcpyAsync(m->staging[p], static_cast<const char*>(m->peer[p]) + m->gw_off[l] + shard_byte0, shard_bytes, cudaMemcpyDeviceToDevice, m->side);
+            }
+            mx_dp_reduce_sgd(m->is_bf16 ? 0 : 1, m->peer, nullptr, m->staging, m->rank, m->world, m->gw_off[l], m->w_off[l], m->gb_off[l], m->w32[l],
+                             m->shard_begin, m->shard_elems, m->b32[l], m->b16[l], lr * grad_scale, 0, m->side);
+            // push my shard of the new weights to every peer
+            const char* mine = static_cast<const char*>(m->peer[m->rank]) + m->w_off[l] + shard_byte0;
+            for (int k = 1; k < m->world; k++) {
+                const int p = (m->rank + k) % m->world;
+                cudaMemcpyAsync(static_cast<char*>(m->peer[p]) + m->w_off[l] + shard_byte0, mine, shard_bytes, cudaMemcpyDeviceToDevice, m->side);
+            }
+        } else {
+            mx_dp_reduce_sgd(m->is_bf16 ? 0 : 1, m->peer, m->mc, nullptr, m->rank, m->world, m->gw_off[l], m->w_off[l], m->gb_off[l], m->w32[l],
+                             m->shard_begin, m->shard_elems, m->b32[l], m->b16[l], lr * grad_scale, m->mc ? m->exclusive_sms : 0, m->side);
+        }
+        if (tr) cudaEventRecord(tr2[l], m->side);
         mx_dp_barrier(m->peer, flag_off, m->rank, m->world, ++m->epoch, m->dp_err, m->side);
+        if (tr) cudaEventRecord(tb2[l], m->side);
         cudaEventRecord(m->ev_done[l], m->side);
     }
+    if (tr) {
+        cudaEventRecord(tend, main_stream);
+        cudaDeviceSynchronize();
+        float a, b, c, d, e;
+        cudaEventElapsedTime(&e, t0, tend);
+        fprintf(stderr, "[trace rank %d] main stream end %.3f ms\n", m->rank, e);
+        for (int l = m->layers - 1; l >= 0; l--) {
+            cudaEventElapsedTime(&a, t0, tg[l]); cudaEventElapsedTime(&b, t0, tb1[l]); cudaEventElapsedTime(&c, t0, tr2[l]); cudaEventElapsedTime(&d, t0, tb2[l]);
+            fprintf(stderr, "[trace rank %d] layer %d: grad ready %.3f  barrier1 done %.3f  reduce done %.3f  barrier2 done %.3f\n", m->rank, l, a, b, c, d);
+        }
+    }
+    ctx().gemm_sm_limit = saved_limit;
     check_launch("mx_mlp_train_step_dp");
+}
+
+// How mx_mlp_train_step_dp moves the data: 0 = the library's kernel over NVLink (multimem when the engine
+// has a multicast address, peer loads and stores otherwise; exclusive_sms = k > 0 gives the multimem form k SMs
+// of its own and the step's GEMMs the rest), 1 = copy engines for the transfers and a local kernel for the sum
+// and the update.  Returns 0, or -1 when the staging buffers cannot be allocated.
+int mx_mlp_dp_set_exchange(void* h, int mode, int exclusive_sms) {
+    Mlp* m = static_cast<Mlp*>(h);
+    if (!m->dp || (mode != 0 && mode != 1) || exclusive_sms < 0) return -1;
+    m->exclusive_sms = mode == 0 ? exclusive_sms : 0;
+    if (mode == 1) {
+        for (int p = 0; p < m->world; p++) {
+            if (p == m->rank || m->staging[p]) continue;
+            m->staging[p] = dmalloc(m, m->shard_elems * 2);
+            if (!m->staging[p]) return -1;
+        }
+    }
+    m->copy_engines = mode == 1;
+    return 0;
+}
+
+// The calling thread's stream waits (on the device) for the exchange of the last step.
+void mx_mlp_dp_join(void* h) {
+    Mlp* m = static_cast<Mlp*>(h);
+    if (!m->dp) return;
+    for (int l = 0; l < m->layers; l++) cudaStreamWaitEvent(ctx().stream, m->ev_done[l], 0);
 }
 
 // Waits for the exchange of the last step and returns 0, or 1 + the peer rank a barrier stopped waiting for.

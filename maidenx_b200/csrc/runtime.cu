@@ -211,6 +211,7 @@ int cuda_pointer_get_attributes(MxCudaPointerAttributes* attributes, const void*
 const char* cuda_error_string(int error_code) { return cudaGetErrorString((cudaError_t)error_code); }
 
 // ---- additive exports ------------------------------------------------------------
+void mx_set_gemm_sm_limit(int sms) { mx::ctx().gemm_sm_limit = sms > 0 ? sms : 0; }
 void mx_set_stream(void* stream) { ctx().stream = reinterpret_cast<cudaStream_t>(stream); }
 void* mx_get_stream(void) { return reinterpret_cast<void*>(ctx().stream); }
 int mx_last_error(void) { return ctx().status; }

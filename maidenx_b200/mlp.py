@@ -101,7 +101,7 @@ class DpMlp(Mlp):
     """Data-parallel engine over a peer-mapped arena (see csrc/dp_sync.cu).  Collective: every rank
     of the default process group must construct it, and call train_step, in the same order."""
 
-    def __init__(self, layers: int, dim: int, batch: int, dtype: str, seed: int, torch, dist, multicast: bool = True):
+    def __init__(self, layers: int, dim: int, batch: int, dtype: str, seed: int, torch, dist, multicast: bool = True, copy_engines: bool = False, exclusive_sms: int = 0):
         import torch.distributed._symmetric_memory as symm_mem
         self.lib = _lib.load()
         self.layers, self.dim, self.batch, self.dtype = layers, dim, batch, dtype
@@ -121,11 +121,23 @@ class DpMlp(Mlp):
         self.h = self.lib.mx_mlp_create_dp(layers, dim, batch, DTYPE_ID[dtype], seed, self.rank, self.world, peers, mc or None)
         if not self.h:
             raise RuntimeError("mx_mlp_create_dp failed (out of memory or bad arguments)")
+        if copy_engines:
+            if self.lib.mx_mlp_dp_set_exchange(self.h, 1, 0) != 0:
+                raise RuntimeError("mx_mlp_dp_set_exchange failed (out of memory)")
+            self.exchange = "copy"
+        elif mc and exclusive_sms > 0:
+            self.lib.mx_mlp_dp_set_exchange(self.h, 0, exclusive_sms)
+            self.exchange = "multimem-exclusive"
+        self.exclusive_sms = exclusive_sms if self.exchange == "multimem-exclusive" else 0
         torch.cuda.synchronize()
         dist.barrier()       # every rank's weights are initialised before anyone's first exchange
 
     def train_step(self, x_ptr: int, y_ptr: int, lr: float, torch=None, dist=None, world: int = 1):
         self.lib.mx_mlp_train_step_dp(self.h, x_ptr, y_ptr, lr, 1.0 / self.world)
+
+    def join(self):
+        """Make the calling thread's stream wait for the exchange of the last step (no host wait)."""
+        self.lib.mx_mlp_dp_join(self.h)
 
     def status(self) -> int:
         """0, or 1 + the rank a barrier stopped waiting for (waits for the exchange to finish)."""
@@ -139,9 +151,10 @@ class DpMlp(Mlp):
         self._arena = None
 
 
-def make_mlp(layers: int, dim: int, batch: int, dtype: str, seed: int, torch=None, dist=None, world: int = 1, exchange: str = "auto"):
+def make_mlp(layers: int, dim: int, batch: int, dtype: str, seed: int, torch=None, dist=None, world: int = 1, exchange: str = "auto",
+             exclusive_sms: int = 8):
     """The engine for `world` ranks: Mlp for one rank, DpMlp for several (exchange "auto",
-    "multimem" or "peer"), Mlp driven with NCCL all-reduces for exchange == "nccl" or when the
+    "copy", "multimem" or "peer"), Mlp driven with NCCL all-reduces for exchange == "nccl" or when the
     symmetric-memory arena cannot be set up (every rank takes the same branch: the outcome of the
     setup is agreed on with an all-reduce)."""
     if world <= 1:
@@ -149,7 +162,8 @@ def make_mlp(layers: int, dim: int, batch: int, dtype: str, seed: int, torch=Non
     if exchange != "nccl":
         m, ok = None, 1
         try:
-            m = DpMlp(layers, dim, batch, dtype, seed, torch, dist, multicast=exchange != "peer")
+            m = DpMlp(layers, dim, batch, dtype, seed, torch, dist, multicast=exchange in ("auto", "multimem", "multimem-exclusive"),
+                      copy_engines=exchange == "copy", exclusive_sms=exclusive_sms if exchange in ("auto", "multimem-exclusive") else 0)
         except Exception as e:  # noqa: BLE001 - any setup failure selects the NCCL driver
             import sys
             print(f"[maidenx_b200] symmetric-memory exchange unavailable ({type(e).__name__}: {e}); using NCCL all-reduce", file=sys.stderr)

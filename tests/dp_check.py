@@ -4,13 +4,17 @@ per GPU); run it as
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port 29533 tests/dp_check.py [--dim 1024 --batch 2048 --layers 3 --steps 3]
 
-Every rank trains the same seeded model on its shard of a seeded global batch with three drivers:
-the NVLink exchange through the multicast address ("multimem"), the same kernels with peer loads
-and stores ("peer"), and the NCCL all-reduce driver ("nccl").  Checked on every rank:
+Every rank trains the same seeded model on its shard of a seeded global batch with these drivers
+("multimem-exclusive" is "multimem" with the exchange kernel on SMs of its own):
+copy-engine transfers around a local sum-and-update kernel ("copy"), the NVLink exchange kernel through
+the multicast address ("multimem"), the same kernel with peer loads and stores ("peer"), and the NCCL
+all-reduce driver ("nccl").  Checked on every rank:
   * no barrier gave up, no library error;
   * within one driver all ranks end with bit-identical 16-bit weights (checksums are all-gathered);
-  * multimem and peer agree with nccl on the weight CHANGE of every layer within 2 % of its
-    largest entry (the three sum the ranks' 16-bit gradients in different orders and precisions);
+  * multimem and peer agree with nccl on the CHANGE of the f32 master weights (this rank's shard
+    of every layer) within 2 % of its largest entry (the three sum the ranks' 16-bit gradients in
+    different orders and precisions; the 16-bit weights themselves move by at most a rounding step
+    in a few steps, so they cannot show the difference);
   * the loss is the same to 1e-3 and decreases.
 Rank 0 prints one JSON line with the verdict.
 """
@@ -37,6 +41,18 @@ def weights_of(m, lib, dim):
     return out
 
 
+def master_shard_of(m, lib, dim, rank, world):
+    """This rank's slice of every layer's f32 master weights (the DP engine holds only that slice)."""
+    n = dim * dim // world
+    out = []
+    for l in range(m.layers):
+        host = np.empty(n, dtype=np.float32)
+        base = m.ptr("master_weight", l) + (0 if hasattr(m, "status") else rank * n * 4)
+        assert lib.cuda_memcpy_d2h(host.ctypes.data, base, host.nbytes) == 0
+        out.append(host)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--dim", type=int, default=1024)
@@ -58,15 +74,12 @@ def main():
     x = x_all[rank * local:(rank + 1) * local].contiguous()
     y = y_all[rank * local:(rank + 1) * local].contiguous()
 
-    def bf16_to_f32(u16):
-        return (u16.astype(np.uint32) << 16).view(np.float32)
-
     results, problems = {}, []
-    for mode in ("multimem", "peer", "nccl"):
+    for mode in ("multimem-exclusive", "copy", "multimem", "peer", "nccl"):
         m = make_mlp(args.layers, args.dim, local, "bf16", 6, torch, dist, world, exchange=mode)
         if m.exchange != mode:
             problems.append(f"{mode}: driver fell back to {m.exchange}")
-        w0 = weights_of(m, lib, args.dim)
+        w0 = master_shard_of(m, lib, args.dim, rank, world)
         losses = []
         for _ in range(args.steps):
             m.train_step(x.data_ptr(), y.data_ptr(), args.lr, torch, dist, world)
@@ -86,10 +99,11 @@ def main():
         dist.all_gather(allsums, sums)
         if any(not torch.equal(allsums[0], s) for s in allsums):
             problems.append(f"{mode}: ranks hold different weights")
-        results[mode] = {"delta": [bf16_to_f32(a) - bf16_to_f32(b) for a, b in zip(w, w0)], "losses": losses}
+        w1 = master_shard_of(m, lib, args.dim, rank, world)
+        results[mode] = {"delta": [a - b for a, b in zip(w1, w0)], "losses": losses}
         m.close()
         dist.barrier()
-    for mode in ("multimem", "peer"):
+    for mode in ("multimem-exclusive", "copy", "multimem", "peer"):
         for l, (d, dn) in enumerate(zip(results[mode]["delta"], results["nccl"]["delta"])):
             scale = float(np.abs(dn).max())
             err = float(np.abs(d - dn).max())

@@ -56,8 +56,8 @@ def test_reduce_sgd_emulated_ranks(cuda, world, dt):
         shards.append(device.CudaBuffer.from_host(master[r * shard:(r + 1) * shard].copy()))
         biases32.append(device.CudaBuffer.from_host(np.full(64, mbias, dtype=np.float32)))
         biases16.append(device.CudaBuffer(256))
-        lib.mx_dp_reduce_sgd(0 if dt is D.BF16 else 1, peers, None, r, world, grad_off, w_off, gb_off, shards[r].ptr, r * shard, shard,
-                             biases32[r].ptr, biases16[r].ptr, ctypes.c_float(step), None)
+        lib.mx_dp_reduce_sgd(0 if dt is D.BF16 else 1, peers, None, None, r, world, grad_off, w_off, gb_off, shards[r].ptr, r * shard, shard,
+                             biases32[r].ptr, biases16[r].ptr, ctypes.c_float(step), 0, None)
     device.synchronize()
     assert device.last_error() is None
     # expected: f32 sum in rank order, rounded to the 16-bit type, then the f32 update, then one rounding
@@ -81,6 +81,59 @@ def test_reduce_sgd_emulated_ranks(cuda, world, dt):
         assert np.array_equal(got16, want16.view(np.uint16)), f"weights in the arena of rank {p}"
     for b in arenas + shards + biases32 + biases16:
         b.free()
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_reduce_sgd_staged_form_matches_peer_form(cuda, world):
+    """The copy-engine route: the peers' shards are copied next to the kernel first and only the own
+    arena receives the new weights.  Same sums in the same order as the peer form, so the same bits."""
+    lib = _lib.load()
+    dt = D.BF16
+    rng = np.random.default_rng(100 + world)
+    n = 8 * world * 520
+    shard = n // world
+    grad_off, w_off, gb_off = 4096, 4096 + n * 2 + 512, 4096 + 2 * (n * 2 + 512)
+    arena_bytes = gb_off + 256
+    grads = [H.random_store(rng, dt, n, dist="normal") for _ in range(world)]
+    master = rng.standard_normal(n).astype(np.float32)
+    step = np.float32(0.01)
+
+    def run(staged_form):
+        arenas = []
+        for p in range(world):
+            host = np.zeros(arena_bytes, dtype=np.uint8)
+            host[grad_off:grad_off + n * 2] = grads[p].view(np.uint8)
+            arenas.append(device.CudaBuffer.from_host(host))
+        peers = (ctypes.c_void_p * world)(*[a.ptr for a in arenas])
+        out32, out16, keep = [], [], []
+        for r in range(world):
+            sh = device.CudaBuffer.from_host(master[r * shard:(r + 1) * shard].copy())
+            b32, b16 = device.CudaBuffer.from_host(np.zeros(64, dtype=np.float32)), device.CudaBuffer(256)
+            staged = None
+            if staged_form:
+                bufs = [device.CudaBuffer.from_host(grads[p][r * shard:(r + 1) * shard].copy()) if p != r else None for p in range(world)]
+                keep += [b for b in bufs if b is not None]
+                staged = (ctypes.c_void_p * world)(*[b.ptr if b is not None else None for b in bufs])
+            lib.mx_dp_reduce_sgd(0, peers, None, staged, r, world, grad_off, w_off, gb_off, sh.ptr, r * shard, shard, b32.ptr, b16.ptr,
+                                 ctypes.c_float(step), 0, None)
+            device.synchronize()
+            out32.append(sh.to_host(np.float32, shard))
+            # the staged form writes the new weights to the own arena only
+            out16.append(_read(arenas[r].ptr + w_off + r * shard * 2, np.uint16, shard))
+            if staged_form:
+                for p in range(world):
+                    if p != r:
+                        assert not _read(arenas[p].ptr + w_off + r * shard * 2, np.uint16, shard).any(), "staged form wrote to a peer"
+            keep += [sh, b32, b16]
+        for b in arenas + keep:
+            b.free()
+        return out32, out16
+
+    peer32, peer16 = run(False)
+    st32, st16 = run(True)
+    for r in range(world):
+        assert np.array_equal(peer32[r], st32[r]) and np.array_equal(peer16[r], st16[r])
+    assert device.last_error() is None
 
 
 def test_barrier_world_one_and_a_peer_that_never_arrives(cuda):
