@@ -54,7 +54,8 @@ struct Mlp {
     std::vector<uint16_t*> u, a;         // pre-activation (z + b) and activation, [batch*dim]; a[L-1] unused
     uint16_t* z = nullptr;               // GEMM output before the bias add (reused by every layer)
     uint16_t* d_act = nullptr;           // gradient w.r.t. the current layer's output
-    uint16_t* d_pre = nullptr;           // gradient w.r.t. the current layer's pre-activation
+    uint16_t* du[2] = {nullptr, nullptr};  // gradient w.r.t. a layer's pre-activation; layer l uses du[l & 1], so the
+                                         // data-parallel step can finish layer 0 before it computes layer 1's weight gradient
     const uint16_t* x = nullptr;         // input batch of the current step
     float* loss = nullptr;               // device scalar
     std::vector<void*> owned;
@@ -145,14 +146,16 @@ template <class T>
 static void loss_backward_t(Mlp* m, const T* y) {
     const size_t n = m->batch * m->dim;
     const T* pred = reinterpret_cast<const T*>(m->u[m->layers - 1]);
-    if constexpr (std::is_same<T, bf16>::value) mx_mse_loss_grad_bf16(n, pred, y, reinterpret_cast<T*>(m->d_pre), m->loss);
-    else mx_mse_loss_grad_f16(n, pred, y, reinterpret_cast<T*>(m->d_pre), m->loss);
+    if constexpr (std::is_same<T, bf16>::value) mx_mse_loss_grad_bf16(n, pred, y, reinterpret_cast<T*>(m->du[(m->layers - 1) & 1]), m->loss);
+    else mx_mse_loss_grad_f16(n, pred, y, reinterpret_cast<T*>(m->du[(m->layers - 1) & 1]), m->loss);
 }
 
+// Backward of layer l, first part: the gradient w.r.t. the pre-activation, the bias gradient, and the gradient
+// handed to the layer below (which reads W[l]).
 template <class T>
-static void backward_layer_t(Mlp* m, int l) {
+static void backward_input_t(Mlp* m, int l) {
     const size_t B = m->batch, D = m->dim, n = B * D;
-    T* du = reinterpret_cast<T*>(m->d_pre);
+    T* du = reinterpret_cast<T*>(m->du[l & 1]);
     if (l != m->layers - 1) {
         // d_act holds the gradient w.r.t. a[l]; turn it into the gradient w.r.t. u[l]
         if constexpr (std::is_same<T, bf16>::value)
@@ -166,27 +169,29 @@ static void backward_layer_t(Mlp* m, int l) {
         if constexpr (std::is_same<T, bf16>::value) cuda_sum_bf16(n, 1, 1, meta, du, reinterpret_cast<T*>(m->gb[l]));
         else cuda_sum_f16(n, 1, 1, meta, du, reinterpret_cast<T*>(m->gb[l]));
     }
-    const T* a_prev = l == 0 ? reinterpret_cast<const T*>(m->x) : reinterpret_cast<const T*>(m->a[l - 1]);
-    // dW [D_out, D_in] = du^T . a_prev: A = transposed view of du (shape [D, B], strides [1, D]), B = a_prev [B, D]
-    auto weight_grad = [&]() {
-        const size_t meta[] = {2, 2, 2, D, D, D, B, B, D, 1, D, D, 1, 0, 0};
-        matmul_call<T>(D * D, meta, du, a_prev, reinterpret_cast<T*>(m->gw[l]));
-    };
     // gradient for the layer below: da_prev [B, D_in] = du [B, D_out] . W [D_out, D_in]
-    auto input_grad = [&]() {
-        if (l == 0) return;
+    if (l > 0) {
         const size_t meta[] = {2, 2, 2, B, D, B, D, D, D, D, 1, D, 1, 0, 0};
         matmul_call<T>(n, meta, du, reinterpret_cast<const T*>(m->w16[l]), reinterpret_cast<T*>(m->d_act));
-    };
-    if (m->dp) {
-        // the input gradient reads W[l], which the exchange overwrites once every rank has its dW[l]:
-        // queue it first, so "dW[l] done" implies "W[l] no longer needed"
-        input_grad();
-        weight_grad();
-    } else {
-        weight_grad();
-        input_grad();
     }
+}
+
+// Second part: dW [D_out, D_in] = du^T . a_prev: A = transposed view of du (shape [D, B], strides [1, D]),
+// B = a_prev [B, D].  Queued after the first part, so "dW[l] done" implies "W[l] no longer needed" - the
+// data-parallel exchange overwrites W[l] as soon as every rank has its dW[l].
+template <class T>
+static void backward_weight_t(Mlp* m, int l) {
+    const size_t B = m->batch, D = m->dim;
+    const T* du = reinterpret_cast<const T*>(m->du[l & 1]);
+    const T* a_prev = l == 0 ? reinterpret_cast<const T*>(m->x) : reinterpret_cast<const T*>(m->a[l - 1]);
+    const size_t meta[] = {2, 2, 2, D, D, D, B, B, D, 1, D, D, 1, 0, 0};
+    matmul_call<T>(D * D, meta, du, a_prev, reinterpret_cast<T*>(m->gw[l]));
+}
+
+template <class T>
+static void backward_layer_t(Mlp* m, int l) {
+    backward_input_t<T>(m, l);
+    backward_weight_t<T>(m, l);
 }
 
 template <class T>
@@ -255,10 +260,11 @@ static Mlp* mlp_create_impl(int layers, size_t dim, size_t batch, int dtype, uin
     }
     m->z = static_cast<uint16_t*>(dmalloc(m, an * 2));
     m->d_act = static_cast<uint16_t*>(dmalloc(m, an * 2));
-    m->d_pre = static_cast<uint16_t*>(dmalloc(m, an * 2));
+    m->du[0] = static_cast<uint16_t*>(dmalloc(m, an * 2));
+    m->du[1] = static_cast<uint16_t*>(dmalloc(m, an * 2));
     m->loss = static_cast<float*>(dmalloc(m, 256));
     m->dp_err = static_cast<uint32_t*>(dmalloc(m, 256));
-    ok = ok && m->z && m->d_act && m->d_pre && m->loss && m->dp_err;
+    ok = ok && m->z && m->d_act && m->du[0] && m->du[1] && m->loss && m->dp_err;
     if (ok && peer) {
         int lo = 0, hi = 0;
         cudaDeviceGetStreamPriorityRange(&lo, &hi);
@@ -387,8 +393,8 @@ void mx_mlp_train_step_dp(void* h, const void* x, const void* y, float lr, float
     mx_mlp_forward(h, x);
     mx_mlp_loss_backward(h, y);
     const size_t flag_off = 0;
-    for (int l = m->layers - 1; l >= 0; l--) {
-        mx_mlp_backward_layer(h, l);
+    // Exchange of layer l, queued on the side stream behind "dW[l] done".
+    auto exchange = [&](int l) {
         cudaEventRecord(m->ev_grad[l], main_stream);
         if (tr) cudaEventRecord(tg[l], main_stream);
         cudaStreamWaitEvent(m->side, m->ev_grad[l], 0);
@@ -417,6 +423,34 @@ void mx_mlp_train_step_dp(void* h, const void* x, const void* y, float lr, float
         mx_dp_barrier(m->peer, flag_off, m->rank, m->world, ++m->epoch, m->dp_err, m->side);
         if (tr) cudaEventRecord(tb2[l], m->side);
         cudaEventRecord(m->ev_done[l], m->side);
+    };
+    auto input_part = [&](int l) {
+        if (m->is_bf16) backward_input_t<bf16>(m, l);
+        else backward_input_t<f16>(m, l);
+    };
+    auto weight_part = [&](int l) {
+        if (m->is_bf16) backward_weight_t<bf16>(m, l);
+        else backward_weight_t<f16>(m, l);
+    };
+    // Layers L-1 .. 2 in the natural order.  The last two are finished in the order 0, 1: the next forward
+    // needs W[0] first, so its exchange starts one GEMM earlier and runs beside dW[1], and the exchange of
+    // layer 1 - now the last - runs beside the next step's first layer instead of in front of it.
+    for (int l = m->layers - 1; l >= 2; l--) {
+        input_part(l);
+        weight_part(l);
+        exchange(l);
+    }
+    if (m->layers >= 2) {
+        input_part(1);
+        input_part(0);
+        weight_part(0);
+        exchange(0);
+        weight_part(1);
+        exchange(1);
+    } else {
+        input_part(0);
+        weight_part(0);
+        exchange(0);
     }
     if (tr) {
         cudaEventRecord(tend, main_stream);
