@@ -378,28 +378,14 @@ void mx_mlp_train_step_dp(void* h, const void* x, const void* y, float lr, float
     cudaStream_t main_stream = ctx().stream;
     const int saved_limit = ctx().gemm_sm_limit;
     if (!m->copy_engines && m->mc && m->exclusive_sms > 0 && m->exclusive_sms < sm_count()) ctx().gemm_sm_limit = sm_count() - m->exclusive_sms;
-    // TRACE (temporary): device timeline of one step
-    static int trace = -1;
-    if (trace < 0) trace = getenv("MX_DP_TRACE") ? atoi(getenv("MX_DP_TRACE")) : 0;
-    static int step_no = 0;
-    const bool tr = trace && (++step_no == trace);
-    cudaEvent_t t0 = nullptr, tg[8], tb1[8], tr2[8], tb2[8], tend = nullptr;
-    if (tr) {
-        cudaDeviceSynchronize();
-        cudaEventCreate(&t0); cudaEventCreate(&tend);
-        for (int l = 0; l < m->layers; l++) { cudaEventCreate(&tg[l]); cudaEventCreate(&tb1[l]); cudaEventCreate(&tr2[l]); cudaEventCreate(&tb2[l]); }
-        cudaEventRecord(t0, main_stream);
-    }
     mx_mlp_forward(h, x);
     mx_mlp_loss_backward(h, y);
     const size_t flag_off = 0;
     // Exchange of layer l, queued on the side stream behind "dW[l] done".
     auto exchange = [&](int l) {
         cudaEventRecord(m->ev_grad[l], main_stream);
-        if (tr) cudaEventRecord(tg[l], main_stream);
         cudaStreamWaitEvent(m->side, m->ev_grad[l], 0);
         mx_dp_barrier(m->peer, flag_off, m->rank, m->world, ++m->epoch, m->dp_err, m->side);
-        if (tr) cudaEventRecord(tb1[l], m->side);
         const size_t shard_bytes = m->shard_elems * 2, shard_byte0 = m->shard_begin * 2;
         if (m->copy_engines) {
             // pull my shard of every peer's gradient, starting with the next rank so that no peer is asked by everyone at once
@@ -419,9 +405,7 @@ void mx_mlp_train_step_dp(void* h, const void* x, const void* y, float lr, float
             mx_dp_reduce_sgd(m->is_bf16 ? 0 : 1, m->peer, m->mc, nullptr, m->rank, m->world, m->gw_off[l], m->w_off[l], m->gb_off[l], m->w32[l],
                              m->shard_begin, m->shard_elems, m->b32[l], m->b16[l], lr * grad_scale, m->mc ? m->exclusive_sms : 0, m->side);
         }
-        if (tr) cudaEventRecord(tr2[l], m->side);
         mx_dp_barrier(m->peer, flag_off, m->rank, m->world, ++m->epoch, m->dp_err, m->side);
-        if (tr) cudaEventRecord(tb2[l], m->side);
         cudaEventRecord(m->ev_done[l], m->side);
     };
     auto input_part = [&](int l) {
@@ -451,17 +435,6 @@ void mx_mlp_train_step_dp(void* h, const void* x, const void* y, float lr, float
         input_part(0);
         weight_part(0);
         exchange(0);
-    }
-    if (tr) {
-        cudaEventRecord(tend, main_stream);
-        cudaDeviceSynchronize();
-        float a, b, c, d, e;
-        cudaEventElapsedTime(&e, t0, tend);
-        fprintf(stderr, "[trace rank %d] main stream end %.3f ms\n", m->rank, e);
-        for (int l = m->layers - 1; l >= 0; l--) {
-            cudaEventElapsedTime(&a, t0, tg[l]); cudaEventElapsedTime(&b, t0, tb1[l]); cudaEventElapsedTime(&c, t0, tr2[l]); cudaEventElapsedTime(&d, t0, tb2[l]);
-            fprintf(stderr, "[trace rank %d] layer %d: grad ready %.3f  barrier1 done %.3f  reduce done %.3f  barrier2 done %.3f\n", m->rank, l, a, b, c, d);
-        }
     }
     ctx().gemm_sm_limit = saved_limit;
     check_launch("mx_mlp_train_step_dp");

@@ -161,9 +161,14 @@ def make_mlp(layers: int, dim: int, batch: int, dtype: str, seed: int, torch=Non
         return Mlp(layers, dim, batch, dtype, seed)
     if exchange != "nccl":
         m, ok = None, 1
+        if exchange == "auto":
+            # two ranks: a rank's shard is half of every layer, which a few SMs cannot move in time, while the
+            # exchange is short against the step - the spread peer form wins; more ranks: the multimem form on
+            # SMs of its own (peer form when the arena has no multicast address)
+            exchange = "peer" if world == 2 else "multimem-exclusive"
         try:
-            m = DpMlp(layers, dim, batch, dtype, seed, torch, dist, multicast=exchange in ("auto", "multimem", "multimem-exclusive"),
-                      copy_engines=exchange == "copy", exclusive_sms=exclusive_sms if exchange in ("auto", "multimem-exclusive") else 0)
+            m = DpMlp(layers, dim, batch, dtype, seed, torch, dist, multicast=exchange in ("multimem", "multimem-exclusive"),
+                      copy_engines=exchange == "copy", exclusive_sms=exclusive_sms if exchange == "multimem-exclusive" else 0)
         except Exception as e:  # noqa: BLE001 - any setup failure selects the NCCL driver
             import sys
             print(f"[maidenx_b200] symmetric-memory exchange unavailable ({type(e).__name__}: {e}); using NCCL all-reduce", file=sys.stderr)
