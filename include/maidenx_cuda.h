@@ -207,8 +207,44 @@ MX_DTYPES_ARITH(MX_DECL_MATMUL_T, _)
 MX_DTYPES_FLOAT(MX_DECL_CONV_T, _)
 
 /* ======================================================================================
+ * fold, padding, softmax - the remaining families of the crate; generic kernels, not tuned
+ * (declarations: crates/maidenx_cuda/src/ops/reduction.rs "fold", src/ops/padding.rs:6-91,
+ * src/nn/activation/softmax.rs:6-31; CPU semantics: crates/maidenx_cpu/src/ops/reduction.rs:274-381,
+ * src/ops/padding.rs, src/nn/activation/softmax.rs).
+ *   fold:     metadata = [dims(n) | strides(n) | fold_dim, window_dim, fold_size, step, window_size, offset];
+ *             out[.., w*step + p, ..] = sum of in[.., w, .., p, ..] (the backward of unfold); num_els = input elements
+ *   padding:  metadata = [in_dims(n) | in_strides(n) | in_offset | out_dims(n) | (before, after) x n];
+ *             forward (num_els_in, num_els_out, ..., inp, out[, pad_value]); backward (.., grad_out, grad_in) overwrites
+ *             grad_in[in_offset .. in_offset + num_els_in) with the sums of the grad_out elements read from each position
+ *   softmax:  metadata = [dims(n) | strides(n) | offset]; along `dim` (>= num_dims means the last); floats only
+ * ====================================================================================== */
+#define MX_DECL_EXTRA_ARITH_T(T, ...)                                                                                                              \
+    void cuda_fold_##T(size_t num_els, size_t num_dims, const size_t* metadata, const mx_##T* inp, mx_##T* out);                                   \
+    void cuda_pad_with_constant_##T(size_t num_els_in, size_t num_els_out, size_t num_dims, const size_t* metadata, const mx_##T* inp, mx_##T* out, \
+                                    mx_##T##_arg pad_value);                                                                                       \
+    void cuda_pad_with_reflection_##T(size_t num_els_in, size_t num_els_out, size_t num_dims, const size_t* metadata, const mx_##T* inp, mx_##T* out); \
+    void cuda_pad_with_replication_##T(size_t num_els_in, size_t num_els_out, size_t num_dims, const size_t* metadata, const mx_##T* inp, mx_##T* out); \
+    void cuda_pad_with_constant_backward_##T(size_t num_els_in, size_t num_els_out, size_t num_dims, const size_t* metadata, const mx_##T* grad_out,  \
+                                             mx_##T* grad_in);                                                                                     \
+    void cuda_pad_with_reflection_backward_##T(size_t num_els_in, size_t num_els_out, size_t num_dims, const size_t* metadata, const mx_##T* grad_out, \
+                                               mx_##T* grad_in);                                                                                   \
+    void cuda_pad_with_replication_backward_##T(size_t num_els_in, size_t num_els_out, size_t num_dims, const size_t* metadata,                     \
+                                                const mx_##T* grad_out, mx_##T* grad_in);
+MX_DTYPES_ARITH(MX_DECL_EXTRA_ARITH_T, _)
+#define MX_DECL_SOFTMAX_T(T, ...) \
+    void cuda_softmax_##T(size_t num_els, size_t num_dims, size_t dim, const size_t* metadata, const mx_##T* input, mx_##T* output);
+MX_DTYPES_FLOAT(MX_DECL_SOFTMAX_T, _)
+
+/* ======================================================================================
  * Additive exports (no counterpart in the reference).
  * ====================================================================================== */
+/* Tensor::contiguous() on the device: out[i] = in[offset + strided_index(i)], out dense.  The reference copies a
+ * non-contiguous CUDA tensor to the host, walks it element by element and copies it back
+ * (crates/maidenx_tensor/src/f.rs:11-40); this is the same gather in one launch, through the elementwise
+ * engine (transposed views go through the tiled kernel).  metadata = [dims(n) | strides(n) | offset]. */
+#define MX_DECL_CONTIGUOUS_T(T, ...) void mx_contiguous_##T(size_t num_els, size_t num_dims, const size_t* metadata, const mx_##T* inp, mx_##T* out);
+MX_DTYPES_ALL(MX_DECL_CONTIGUOUS_T, _)
+
 /* Stream used by this thread's subsequent op launches (NULL = legacy default stream). */
 void mx_set_stream(void* stream);
 void* mx_get_stream(void);

@@ -92,6 +92,14 @@ def load() -> ctypes.CDLL:
     return lib
 
 
+def contiguous(dtype_name: str):
+    """`mx_contiguous_<dtype>(num_els, num_dims, metadata, in, out)`: strided view -> dense copy on the device."""
+    fn = getattr(load(), f"mx_contiguous_{dtype_name}")
+    fn.argtypes = [ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    fn.restype = None
+    return fn
+
+
 def op(name: str, dtype_name: str):
     """The `cuda_<name>_<dtype>` entry point."""
     load()

@@ -25,12 +25,14 @@ UNARY_CONST_FLOAT = ["leaky_relu", "elu"]
 UNARY_CONST_BOOL = ["eq_scalar", "ne_scalar", "lt_scalar", "le_scalar", "gt_scalar", "ge_scalar"]
 REDUCE_ARITH = ["sum", "max", "min"]
 REDUCE_FLOAT = ["mean"]
+PAD_FORWARD = ["pad_with_reflection", "pad_with_replication"]
+PAD_BACKWARD = ["pad_with_constant_backward", "pad_with_reflection_backward", "pad_with_replication_backward"]
 
 
 def op_table():
     """Yield (op, dtype, family) for every op entry point the dispatch layer of the
     reference uses (crates/maidenx_core/src/be/ops/{binary,unary,reduction,matmul}.rs,
-    be/nn/conv.rs)."""
+    be/nn/conv.rs, be/ops/padding.rs, be/nn/activation.rs)."""
     for d in dt.ARITH:
         for op in BINARY_ARITH:
             yield op, d, "binary"
@@ -43,6 +45,10 @@ def op_table():
         for op in REDUCE_ARITH:
             yield op, d, "reduce"
         yield "sum_to_shape", d, "sum_to_shape"
+        yield "fold", d, "sum_to_shape"
+        yield "pad_with_constant", d, "pad_const"
+        for op in PAD_FORWARD + PAD_BACKWARD:
+            yield op, d, "pad"
         yield "matmul", d, "matmul"
         yield "matmul_backward", d, "matmul_backward"
     for d in dt.ALL:
@@ -64,6 +70,7 @@ def op_table():
             yield op, d, "reduce"
         yield "conv2d_im2col", d, "conv"
         yield "conv2d_col2im", d, "conv"
+        yield "softmax", d, "softmax"
 
 
 def argtypes(family: str, d: dt.DType):
@@ -79,6 +86,12 @@ def argtypes(family: str, d: dt.DType):
         return [SZ, SZ, SZ, PTR, PTR, PTR]
     if family == "sum_to_shape":
         return [SZ, SZ, PTR, PTR, PTR]
+    if family == "pad":         # (num_els_in, num_els_out, num_dims, metadata, in | grad_out, out | grad_in)
+        return [SZ, SZ, SZ, PTR, PTR, PTR]
+    if family == "pad_const":   # ... plus the pad value
+        return [SZ, SZ, SZ, PTR, PTR, PTR, d.c_arg]
+    if family == "softmax":     # (num_els, num_dims, dim, metadata, in, out)
+        return [SZ, SZ, SZ, PTR, PTR, PTR]
     if family == "matmul":
         return [SZ, PTR, PTR, PTR, PTR]
     if family == "matmul_backward":

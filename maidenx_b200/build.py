@@ -43,7 +43,7 @@ SINGLE_SOURCES = ["runtime.cu", "ew_plan.cu"]
 
 def _register_optional():
     """Families added as the library grows; only listed when the file exists."""
-    for name, dts in (("reduction.cu", ARITH), ("matmul_simt.cu", ARITH), ("conv.cu", FLOATS)):
+    for name, dts in (("reduction.cu", ARITH), ("matmul_simt.cu", ARITH), ("conv.cu", FLOATS), ("extras.cu", ARITH)):
         if (CSRC / name).exists():
             PER_DTYPE_SOURCES[name] = dts
     for name in ("reduce_plan.cu", "matmul_plan.cu", "matmul_tc.cu", "fused.cu", "mlp.cu", "noalloc.cu", "dp_sync.cu"):

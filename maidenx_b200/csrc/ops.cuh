@@ -429,6 +429,12 @@ struct OpGelu {
         else return fp_apply(x, [](f32 v) { return gelu_f32(v); }, [](f64 v) { return gelu_f64(v); });
     }
 };
+struct OpIdentity {  // the strided-to-dense copy behind mx_contiguous_<T>
+    template <class T>
+    __device__ static T f(T x) {
+        return x;
+    }
+};
 struct OpNeg {
     template <class T>
     __device__ static T f(T x) {

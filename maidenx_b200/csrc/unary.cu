@@ -47,6 +47,7 @@ typedef OpLt Op_lt_scalar;
 typedef OpLe Op_le_scalar;
 typedef OpGt Op_gt_scalar;
 typedef OpGe Op_ge_scalar;
+typedef OpIdentity Op_contiguous;
 }  // namespace mx
 
 #define DEF_UNARY_(op, T)                                                                                          \
@@ -65,6 +66,12 @@ typedef OpGe Op_ge_scalar;
     void cuda_##op##_##T(size_t n, size_t nd, const size_t* m, const mx_##T* i, mx_##T##_arg c, mx_bool* o) {      \
         mx::unary_const_entry<mx::Op_##op, mx_##T, bool>(n, nd, m, i, mx::scalar_arg<mx_##T>(c), o, "cuda_" #op "_" #T); \
     }
+// additive: Tensor::contiguous() on the device (the reference round-trips through the host, crates/maidenx_tensor/src/f.rs:11-40)
+#define DEF_CONTIGUOUS_(T)                                                                                         \
+    void mx_contiguous_##T(size_t n, size_t nd, const size_t* m, const mx_##T* i, mx_##T* o) {                     \
+        mx::unary_entry<mx::Op_contiguous, mx_##T, mx_##T>(n, nd, m, i, o, "mx_contiguous_" #T);                   \
+    }
+#define DEF_CONTIGUOUS(T) DEF_CONTIGUOUS_(T)
 #define DEF_UNARY(op, T) DEF_UNARY_(op, T)
 #define DEF_UNARY_BOOL(op, T) DEF_UNARY_BOOL_(op, T)
 #define DEF_UNARY_CONST(op, T) DEF_UNARY_CONST_(op, T)
@@ -84,4 +91,5 @@ MX_UNARY_CONST_ARITH_OPS(DEF_UNARY_CONST, MX_T)
 #endif
 DEF_UNARY_BOOL(logical_not, MX_T)
 MX_UNARY_CONST_BOOL_OPS(DEF_UNARY_CONST_BOOL, MX_T)
+DEF_CONTIGUOUS(MX_T)
 }

@@ -1075,3 +1075,247 @@ FOR_ARITH12(DEF_MM)
     extern "C" void conv2d_im2col_##SUF(size_t n, const size_t* m, const T* i, T* o) { im2col_op<T>(n, m, i, o); }         \
     extern "C" void conv2d_col2im_##SUF(size_t n, const size_t* m, const T* i, T* o) { col2im_op<T>(n, m, i, o); }
 FOR_FLOAT4(DEF_CONV)
+
+// ---------------------------------------------------------------------------------
+// fold (the backward of unfold): crates/maidenx_cpu/src/ops/reduction.rs:274-381
+// metadata: [dims(n) | strides(n) | fold_dim, window_dim, fold_size, step, window_size, offset]
+// ---------------------------------------------------------------------------------
+template <class T, class A>
+static void fold_impl(size_t num_els, size_t num_dims, const size_t* meta, const T* inp, T* out) {
+    const size_t* dims = meta;
+    const size_t* strides = meta + num_dims;
+    const size_t fold_dim = meta[2 * num_dims], window_dim = meta[2 * num_dims + 1], fold_size = meta[2 * num_dims + 2];
+    const size_t step = meta[2 * num_dims + 3], offset = meta[2 * num_dims + 5];
+    const T* input = inp + offset;
+    size_t out_size = 1;  // :310-319
+    for (size_t d = 0; d < num_dims; d++) {
+        if (d == window_dim) continue;
+        out_size *= d == fold_dim ? fold_size : dims[d];
+    }
+    std::vector<A> acc(out_size, A());
+    std::vector<size_t> coords(num_dims ? num_dims : 1);
+    for (size_t i = 0; i < num_els; i++) {  // ascending i: one legal schedule of the reference's parallel loop
+        size_t r = i;
+        for (size_t d = num_dims; d-- > 0;) {  // :323-339 (both branches are the same row-major split)
+            coords[d] = r % dims[d];
+            r /= dims[d];
+        }
+        size_t src = 0;
+        for (size_t d = 0; d < num_dims; d++) src += coords[d] * strides[d];
+        src %= num_els;  // :345
+        const size_t orig_pos = coords[fold_dim] * step + coords[window_dim];
+        if (orig_pos >= fold_size) continue;
+        size_t dst = 0;
+        for (size_t d = 0; d < num_dims; d++) {
+            if (d == window_dim) continue;
+            dst = d == fold_dim ? dst * fold_size + orig_pos : dst * dims[d] + coords[d];
+        }
+        acc_add(acc[dst], to_acc<A, T>(input[src]));
+    }
+    for (size_t j = 0; j < out_size; j++) out[j] = from_acc<T, A>(acc[j]);
+}
+template <class T>
+static void fold_op(size_t num_els, size_t num_dims, const size_t* meta, const T* inp, T* out) {
+    if (g_wide) fold_impl<T, typename WideAcc<T>::type>(num_els, num_dims, meta, inp, out);
+    else fold_impl<T, T>(num_els, num_dims, meta, inp, out);
+}
+#define DEF_FOLD(SUF, T) \
+    extern "C" void fold_##SUF(size_t n, size_t nd, const size_t* m, const T* i, T* o) { fold_op<T>(n, nd, m, i, o); }
+FOR_ARITH12(DEF_FOLD)
+
+// ---------------------------------------------------------------------------------
+// padding: crates/maidenx_cpu/src/ops/padding.rs
+// metadata: [in_dims(n) | in_strides(n) | in_offset | out_dims(n) | (before, after) x n]
+// ---------------------------------------------------------------------------------
+enum { P_CONSTANT = 0, P_REFLECTION = 1, P_REPLICATION = 2 };
+
+// Input coordinate of output coordinate `oc` along one dim; false = outside (constant padding only).
+template <int MODE>
+static inline bool pad_source(long long oc, long long pad_before, long long dim_size, size_t* ic) {
+    long long pos = oc - pad_before;
+    if (MODE == P_CONSTANT) {  // :71-80
+        if (pos < 0 || pos >= dim_size) return false;
+    } else if (MODE == P_REFLECTION) {  // :178-196; the tensor layer rejects pads >= dim size, the loop is bounded here all the same
+        for (int guard = 0; (pos < 0 || pos >= dim_size) && guard < 64; guard++) pos = pos < 0 ? -pos : 2 * dim_size - pos - 2;
+        if (pos < 0 || pos >= dim_size) pos = 0;
+    } else {  // :289-295
+        pos = pos < 0 ? 0 : (pos > dim_size - 1 ? dim_size - 1 : pos);
+    }
+    *ic = (size_t)pos;
+    return true;
+}
+
+template <int MODE>
+static inline bool pad_in_index(size_t i, size_t nd, const size_t* in_dims, const size_t* in_strides, const size_t* out_dims, const size_t* pads,
+                                bool cont, size_t* in_idx) {
+    size_t oc[16], ic[16];
+    size_t r = i;
+    for (size_t d = nd; d-- > 0;) {
+        oc[d] = r % out_dims[d];
+        r /= out_dims[d];
+    }
+    for (size_t d = 0; d < nd; d++)
+        if (!pad_source<MODE>((long long)oc[d], (long long)pads[2 * d], (long long)in_dims[d], &ic[d])) return false;
+    size_t idx = 0;
+    if (cont) {  // :84-92
+        size_t stride = 1;
+        for (size_t d = nd; d-- > 0;) {
+            idx += ic[d] * stride;
+            stride *= in_dims[d];
+        }
+    } else {
+        for (size_t d = 0; d < nd; d++) idx += ic[d] * in_strides[d];
+    }
+    *in_idx = idx;
+    return true;
+}
+
+template <class T, int MODE>
+static void pad_forward(size_t num_els_in, size_t num_els_out, size_t nd, const size_t* meta, const T* inp, T* out, T pad_value) {
+    (void)num_els_in;
+    if (nd > 16) return;
+    const size_t* in_dims = meta;
+    const size_t* in_strides = meta + nd;
+    const size_t in_off = meta[2 * nd];
+    const size_t* out_dims = meta + 2 * nd + 1;
+    const size_t* pads = meta + 3 * nd + 1;
+    const bool cont = is_contiguous(nd, in_dims, in_strides);
+    const T* input = inp + in_off;
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < (long long)num_els_out; i++) {
+        size_t idx;
+        out[i] = pad_in_index<MODE>((size_t)i, nd, in_dims, in_strides, out_dims, pads, cont, &idx) ? input[idx] : pad_value;
+    }
+}
+
+// :327-436, :438-558, :560-664: grad_in[in_offset + in_idx] accumulates every grad_out element that maps to it;
+// the whole block of num_els_in elements is overwritten (zeros where nothing maps).
+template <class T, int MODE, class A>
+static void pad_backward_impl(size_t num_els_in, size_t num_els_out, size_t nd, const size_t* meta, const T* grad_out, T* grad_in) {
+    if (nd > 16) return;
+    const size_t* in_dims = meta;
+    const size_t* in_strides = meta + nd;
+    const size_t in_off = meta[2 * nd];
+    const size_t* out_dims = meta + 2 * nd + 1;
+    const size_t* pads = meta + 3 * nd + 1;
+    const bool cont = is_contiguous(nd, in_dims, in_strides);
+    std::vector<A> acc(num_els_in, A());
+    for (size_t i = 0; i < num_els_out; i++) {
+        size_t idx;
+        if (pad_in_index<MODE>(i, nd, in_dims, in_strides, out_dims, pads, cont, &idx) && idx < num_els_in) acc_add(acc[idx], to_acc<A, T>(grad_out[i]));
+    }
+    for (size_t j = 0; j < num_els_in; j++) grad_in[in_off + j] = from_acc<T, A>(acc[j]);
+}
+template <class T, int MODE>
+static void pad_backward(size_t ni, size_t no, size_t nd, const size_t* meta, const T* go, T* gi) {
+    if (g_wide) pad_backward_impl<T, MODE, typename WideAcc<T>::type>(ni, no, nd, meta, go, gi);
+    else pad_backward_impl<T, MODE, T>(ni, no, nd, meta, go, gi);
+}
+#define DEF_PAD(SUF, T)                                                                                                                        \
+    extern "C" void pad_with_constant_##SUF(size_t ni, size_t no, size_t nd, const size_t* m, const T* i, T* o, CArg<T>::type c) {              \
+        pad_forward<T, P_CONSTANT>(ni, no, nd, m, i, o, CArg<T>::get(c));                                                                      \
+    }                                                                                                                                          \
+    extern "C" void pad_with_reflection_##SUF(size_t ni, size_t no, size_t nd, const size_t* m, const T* i, T* o) {                             \
+        pad_forward<T, P_REFLECTION>(ni, no, nd, m, i, o, zero_of<T>());                                                                       \
+    }                                                                                                                                          \
+    extern "C" void pad_with_replication_##SUF(size_t ni, size_t no, size_t nd, const size_t* m, const T* i, T* o) {                            \
+        pad_forward<T, P_REPLICATION>(ni, no, nd, m, i, o, zero_of<T>());                                                                      \
+    }                                                                                                                                          \
+    extern "C" void pad_with_constant_backward_##SUF(size_t ni, size_t no, size_t nd, const size_t* m, const T* g, T* gi) {                     \
+        pad_backward<T, P_CONSTANT>(ni, no, nd, m, g, gi);                                                                                     \
+    }                                                                                                                                          \
+    extern "C" void pad_with_reflection_backward_##SUF(size_t ni, size_t no, size_t nd, const size_t* m, const T* g, T* gi) {                   \
+        pad_backward<T, P_REFLECTION>(ni, no, nd, m, g, gi);                                                                                   \
+    }                                                                                                                                          \
+    extern "C" void pad_with_replication_backward_##SUF(size_t ni, size_t no, size_t nd, const size_t* m, const T* g, T* gi) {                  \
+        pad_backward<T, P_REPLICATION>(ni, no, nd, m, g, gi);                                                                                  \
+    }
+FOR_ARITH12(DEF_PAD)
+
+// ---------------------------------------------------------------------------------
+// softmax: crates/maidenx_cpu/src/nn/activation/softmax.rs:63-217
+// metadata: [dims(n) | strides(n) | offset]; every step (x - max, exp, the running sum, the quotient) is
+// carried out in the element type, as the reference's generic code does for bf16 / f16.
+// ---------------------------------------------------------------------------------
+template <class T>
+static inline T sm_exp(T v) {
+    if constexpr (is_half_v<T>) return T::from_f32(std::exp(v.to_f32()));
+    else return std::exp(v);
+}
+template <class T>
+static inline T sm_neg_inf() {
+    if constexpr (is_half_v<T>) return T::from_f32(-INFINITY);
+    else return (T)-INFINITY;
+}
+// wide mode: f32 (f64 for f32 inputs) arithmetic with one final rounding
+template <class T, class A>
+static void softmax_impl(size_t num_els, size_t nd, size_t dim_in, const size_t* meta, const T* input, T* output) {
+    (void)num_els;
+    if (!meta || !input || !output || nd == 0) return;
+    const size_t dim = dim_in >= nd ? nd - 1 : dim_in;  // :70
+    const size_t* dims = meta;
+    const size_t* strides = meta + nd;
+    const size_t offset = meta[2 * nd];
+    size_t pre = 1, post = 1;
+    for (size_t d = 0; d < dim; d++) pre *= dims[d];
+    for (size_t d = dim + 1; d < nd; d++) post *= dims[d];
+    const size_t n = dims[dim];
+    bool cont = true;  // :86-98: unlike utils.rs this test does not skip size-1 dims
+    {
+        size_t acc = 1;
+        for (size_t d = nd; d-- > 0;) {
+            if (strides[d] != acc) {
+                cont = false;
+                break;
+            }
+            acc *= dims[d];
+        }
+    }
+    auto index = [&](size_t pre_idx, size_t i, size_t post_idx) -> size_t {
+        if (cont) return offset + pre_idx * (n * post) + i * post + post_idx;
+        size_t idx = offset, rem = pre_idx;
+        for (size_t d = 0; d < dim; d++) {  // :123-128: ascending dims take the remainders (dim 0 varies fastest)
+            idx += (rem % dims[d]) * strides[d];
+            rem /= dims[d];
+        }
+        idx += i * strides[dim];
+        rem = post_idx;
+        for (size_t d = nd; d-- > dim + 1;) {
+            idx += (rem % dims[d]) * strides[d];
+            rem /= dims[d];
+        }
+        return idx;
+    };
+#pragma omp parallel for schedule(static)
+    for (long long s = 0; s < (long long)(pre * post); s++) {
+        const size_t pre_idx = (size_t)s / post, post_idx = (size_t)s % post;
+        if constexpr (std::is_same<A, T>::value) {
+            T mx = sm_neg_inf<T>();
+            for (size_t i = 0; i < n; i++) {
+                T v = input[index(pre_idx, i, post_idx)];
+                if (v > mx) mx = v;
+            }
+            T sum = sm_exp<T>(sm_neg_inf<T>() - mx);  // :144
+            for (size_t i = 0; i < n; i++) sum = sum + sm_exp<T>(input[index(pre_idx, i, post_idx)] - mx);
+            for (size_t i = 0; i < n; i++) output[pre_idx * (n * post) + i * post + post_idx] = sm_exp<T>(input[index(pre_idx, i, post_idx)] - mx) / sum;
+        } else {
+            A mx = (A)-INFINITY;
+            for (size_t i = 0; i < n; i++) {
+                A v = to_acc<A, T>(input[index(pre_idx, i, post_idx)]);
+                if (v > mx) mx = v;
+            }
+            A sum = std::exp((A)-INFINITY - mx);
+            for (size_t i = 0; i < n; i++) sum += std::exp(to_acc<A, T>(input[index(pre_idx, i, post_idx)]) - mx);
+            for (size_t i = 0; i < n; i++)
+                output[pre_idx * (n * post) + i * post + post_idx] = from_acc<T, A>(std::exp(to_acc<A, T>(input[index(pre_idx, i, post_idx)]) - mx) / sum);
+        }
+    }
+}
+template <class T>
+static void softmax_op(size_t n, size_t nd, size_t dim, const size_t* meta, const T* in, T* out) {
+    if (g_wide) softmax_impl<T, typename WideAcc<T>::type>(n, nd, dim, meta, in, out);
+    else softmax_impl<T, T>(n, nd, dim, meta, in, out);
+}
+#define DEF_SOFTMAX(SUF, T) \
+    extern "C" void softmax_##SUF(size_t n, size_t nd, size_t dim, const size_t* m, const T* i, T* o) { softmax_op<T>(n, nd, dim, m, i, o); }
+FOR_FLOAT4(DEF_SOFTMAX)

@@ -5,7 +5,7 @@ The reference is a Rust workspace that cannot be compiled where this repository 
 so its known-answer tests are read as TEXT: this script parses
 `crates/maidenx_tensor/tests/ops_binary.rs` and `ops_unary.rs` (one `pub fn <op>_test`
 per op, one `match` arm per dtype class) and lifts inputs, scalar arguments, expected
-outputs and tolerances out of each arm.  The reduction, matmul and MSE vectors are listed
+outputs and tolerances out of each arm.  The reduction, matmul, padding, fold and MSE vectors are listed
 below by hand with the line they come from; every literal listed is checked to be present
 in the cited source range before it is written out.
 
@@ -215,6 +215,42 @@ MSE_CASE = {"pred": [2.0, 3.0, 4.0], "target": [1.0, 2.0, 3.0], "loss": 1.0, "gr
             "cite": (MSE, 45, 79), "needles": ["vec![2.0f32, 3.0, 4.0]", "vec![1.0f32, 2.0, 3.0]", "vec![1.0]", "2.0 / 3.0"]}
 
 
+PAD = "crates/maidenx_tensor/tests/ops_padding.rs"
+X1 = [1.0, 2.0, 3.0, 4.0]                 # TEST_DATA_F32_1D (ops_padding.rs:9)
+X2 = [1.0, 2.0, 3.0, 4.0, 5.0, 6.0]       # TEST_DATA_F32_2D flattened (ops_padding.rs:10)
+# (mode, input, shape, pads, pad value, expected output, expected grad of the input under backward of sum | None, cite, needles)
+PADDINGS = [
+    ("constant", X1, [4], [(1, 2)], 0.0, [0.0, 1.0, 2.0, 3.0, 4.0, 0.0, 0.0], [1.0] * 4, (PAD, 116, 131),
+     ["x.pad(&[(1, 2)], 0.0)", "vec![0.0, 1.0, 2.0, 3.0, 4.0, 0.0, 0.0]", "vec![1.0, 1.0, 1.0, 1.0]"]),
+    ("constant", X2, [2, 3], [(1, 1), (2, 1)], 3.0,
+     [3.0] * 8 + [1.0, 2.0, 3.0] + [3.0] * 3 + [4.0, 5.0, 6.0] + [3.0] * 7, [1.0] * 6, (PAD, 133, 151),
+     ["x.pad(&[(1, 1), (2, 1)], 3.0)", "3.0, 3.0, 3.0, 3.0, 3.0, 3.0, 3.0, 3.0, 1.0, 2.0, 3.0, 3.0, 3.0, 3.0, 4.0, 5.0, 6.0, 3.0, 3.0, 3.0,",
+      "vec![1.0, 1.0, 1.0, 1.0, 1.0, 1.0]"]),
+    ("constant", X1, [4], [(0, 2)], 9.9, [1.0, 2.0, 3.0, 4.0, 9.9, 9.9], None, (PAD, 153, 160),
+     ["x.pad(&[(0, 2)], 9.9)", "vec![1.0, 2.0, 3.0, 4.0, 9.9, 9.9]"]),
+    ("reflection", X1, [4], [(2, 2)], None, [3.0, 2.0, 1.0, 2.0, 3.0, 4.0, 3.0, 2.0], [1.0, 3.0, 3.0, 1.0], (PAD, 237, 254),
+     ["x.pad_with_reflection(&[(2, 2)])", "vec![3.0, 2.0, 1.0, 2.0, 3.0, 4.0, 3.0, 2.0]", "vec![1.0, 3.0, 3.0, 1.0]"]),
+    ("reflection", X2, [2, 3], [(1, 1), (2, 2)], None,
+     [6.0, 5.0, 4.0, 5.0, 6.0, 5.0, 4.0, 3.0, 2.0, 1.0, 2.0, 3.0, 2.0, 1.0, 6.0, 5.0, 4.0, 5.0, 6.0, 5.0, 4.0, 3.0, 2.0, 1.0, 2.0, 3.0, 2.0, 1.0],
+     None, (PAD, 256, 267),
+     ["x.pad_with_reflection(&[(1, 1), (2, 2)])", "6.0, 5.0, 4.0, 5.0, 6.0, 5.0, 4.0, 3.0, 2.0, 1.0, 2.0, 3.0, 2.0, 1.0, 6.0, 5.0, 4.0, 5.0, 6.0, 5.0,"]),
+    ("replication", X1, [4], [(2, 2)], None, [1.0, 1.0, 1.0, 2.0, 3.0, 4.0, 4.0, 4.0], [3.0, 1.0, 1.0, 3.0], (PAD, 370, 386),
+     ["x.pad_with_replication(&[(2, 2)])", "vec![1.0, 1.0, 1.0, 2.0, 3.0, 4.0, 4.0, 4.0]", "vec![3.0, 1.0, 1.0, 3.0]"]),
+    ("replication", X2, [2, 3], [(1, 1), (2, 2)], None,
+     [1.0, 1.0, 1.0, 2.0, 3.0, 3.0, 3.0, 1.0, 1.0, 1.0, 2.0, 3.0, 3.0, 3.0, 4.0, 4.0, 4.0, 5.0, 6.0, 6.0, 6.0, 4.0, 4.0, 4.0, 5.0, 6.0, 6.0, 6.0],
+     None, (PAD, 388, 399),
+     ["x.pad_with_replication(&[(1, 1), (2, 2)])", "1.0, 1.0, 1.0, 2.0, 3.0, 3.0, 3.0, 1.0, 1.0, 1.0, 2.0, 3.0, 3.0, 3.0, 4.0, 4.0, 4.0, 5.0, 6.0, 6.0,"]),
+]
+# fold of an unfolded view: (input, shape, unfold dim, window size, step, expected, cite, needles); the unfolded view has
+# the window count at `dim` (stride step * stride[dim]) and the window as the next dim (crates/maidenx_core/src/layout.rs:193-250)
+FOLDS = [
+    ([1.0, 2.0, 3.0, 4.0, 5.0], [5], 0, 2, 1, [1.0, 4.0, 6.0, 8.0, 5.0], (RED, 484, 497),
+     ["vec![1.0, 2.0, 3.0, 4.0, 5.0]", "x.unfold(0, 2, 1)", "unfolded.fold(0, 2, 1)", "vec![1.0, 4.0, 6.0, 8.0, 5.0]"]),
+    (X2, [2, 3], 1, 2, 1, [1.0, 4.0, 3.0, 4.0, 10.0, 6.0], (RED, 520, 531),
+     ["x_2d.unfold(1, 2, 1)", "unfolded_2d.fold(1, 2, 1)", "vec![1.0, 4.0, 3.0, 4.0, 10.0, 6.0]"]),
+]
+
+
 def check_needles(ref: Path, cite, needles):
     file, lo, hi = cite
     lines = (ref / file).read_text().split("\n")[lo - 1:hi]
@@ -242,6 +278,10 @@ def main():
     for a, ash, b, bsh, c, ga, gb, cite, needles in MATMULS:
         data["matmul"].append({"a": a, "a_shape": ash, "b": b, "b_shape": bsh, "c": c, "grad_a": ga, "grad_b": gb,
                                "cite": check_needles(ref, cite, needles)})
+    data["padding"] = [{"mode": mode, "input": x, "shape": shape, "pads": [list(p) for p in pads], "value": value, "expected": exp, "grad": grad,
+                        "cite": check_needles(ref, cite, needles)} for mode, x, shape, pads, value, exp, grad, cite, needles in PADDINGS]
+    data["fold"] = [{"input": x, "shape": shape, "dim": dim, "size": size, "step": step, "expected": exp, "cite": check_needles(ref, cite, needles)}
+                    for x, shape, dim, size, step, exp, cite, needles in FOLDS]
     m = dict(MSE_CASE)
     m["cite"] = check_needles(ref, m["cite"], m.pop("needles"))
     data["mse"] = m

@@ -178,6 +178,76 @@ def run_sum_to_shape(be, dt, dims, strides, out_dims, off, in_store):
     return be.call("sum_to_shape", dt, meta, build)["out"]
 
 
+def pad_metadata(in_dims, in_strides, off, pads):
+    """crates/maidenx_tensor/src/ops/padding.rs:272-294."""
+    out_dims = [d + a + b for d, (a, b) in zip(in_dims, pads)]
+    flat = [v for ab in pads for v in ab]
+    return list(in_dims) + list(in_strides) + [off] + out_dims + flat, out_dims
+
+
+def run_pad(be, mode, dt, in_dims, in_strides, off, pads, in_store, value=None):
+    """mode: constant | reflection | replication.  Returns the padded tensor (dense)."""
+    meta, out_dims = pad_metadata(in_dims, in_strides, off, pads)
+    n_in, n_out = numel(in_dims), numel(out_dims)
+    out0 = np.full(max(n_out, 1), 7).astype(dt.np_storage)  # dirty: the op must overwrite
+
+    def build(put, META):
+        ip, _ = put(in_store)
+        op_, oh = put(out0)
+        args = [_sz(n_in), _sz(n_out), _sz(len(in_dims)), META, ip, op_]
+        if mode == "constant":
+            args.append(D.scalar_arg(value, dt))
+        return args, {"out": (oh, dt.np_storage, n_out)}
+
+    return be.call(f"pad_with_{mode}", dt, meta, build)["out"]
+
+
+def run_pad_backward(be, mode, dt, in_dims, in_strides, off, pads, grad_out_store, grad_in_len):
+    """Returns the whole grad_in buffer (grad_in_len elements; the op writes [off, off + numel(in_dims)))."""
+    meta, out_dims = pad_metadata(in_dims, in_strides, off, pads)
+    n_in, n_out = numel(in_dims), numel(out_dims)
+    gi0 = np.full(max(grad_in_len, 1), 7).astype(dt.np_storage)
+
+    def build(put, META):
+        gp, _ = put(grad_out_store)
+        ip, ih = put(gi0)
+        return [_sz(n_in), _sz(n_out), _sz(len(in_dims)), META, gp, ip], {"grad_in": (ih, dt.np_storage, grad_in_len)}
+
+    return be.call(f"pad_with_{mode}_backward", dt, meta, build)["grad_in"]
+
+
+def run_fold(be, dt, dims, strides, fold_dim, window_dim, fold_size, step, off, in_store):
+    """crates/maidenx_tensor/src/ops/reduction.rs:745-769: [dims | strides | fold_dim, window_dim, fold_size, step, window_size, offset]."""
+    n = numel(dims)
+    meta = list(dims) + list(strides) + [fold_dim, window_dim, fold_size, step, dims[window_dim], off]
+    out_n = 1
+    for d, ext in enumerate(dims):
+        if d == window_dim:
+            continue
+        out_n *= fold_size if d == fold_dim else ext
+    out0 = np.full(max(out_n, 1), 7).astype(dt.np_storage)
+
+    def build(put, META):
+        ip, _ = put(in_store)
+        op_, oh = put(out0)
+        return [_sz(n), _sz(len(dims)), META, ip, op_], {"out": (oh, dt.np_storage, out_n)}
+
+    return be.call("fold", dt, meta, build)["out"]
+
+
+def run_softmax(be, dt, dims, strides, off, dim, in_store):
+    n = numel(dims)
+    meta = list(dims) + list(strides) + [off]
+    out0 = np.full(max(n, 1), 7).astype(dt.np_storage)
+
+    def build(put, META):
+        ip, _ = put(in_store)
+        op_, oh = put(out0)
+        return [_sz(n), _sz(len(dims)), _sz(dim), META, ip, op_], {"out": (oh, dt.np_storage, n)}
+
+    return be.call("softmax", dt, meta, build)["out"]
+
+
 def matmul_metadata(out_shape, a_shape, b_shape, a_strides, b_strides, a_off, b_off):
     """crates/maidenx_tensor/src/ops/matmul.rs:227-264."""
     return [len(out_shape), len(a_shape), len(b_shape)] + list(out_shape) + list(a_shape) + list(b_shape) + \

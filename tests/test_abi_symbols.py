@@ -42,15 +42,19 @@ def test_every_declared_symbol_is_exported():
 
 
 def test_op_symbol_set_matches_reference_dispatch():
-    """237 binary + 295 unary + 52 reduction (sum, max, min, sum_to_shape x12, mean x4) + 24 matmul
-    + 8 conv entry points, as dispatched by crates/maidenx_core/src/be/ops/*.rs and be/nn/conv.rs."""
+    """237 binary + 295 unary + 64 reduction (sum, max, min, sum_to_shape, fold x12, mean x4) + 24 matmul
+    + 8 conv + 72 padding + 4 softmax = the 704 entry points dispatched by crates/maidenx_core/src/be/ops/*.rs,
+    be/nn/conv.rs and be/nn/activation.rs."""
     table = list(sig.op_table())
     fam = {}
     for op, d, f in table:
         fam[f] = fam.get(f, 0) + 1
     assert fam["binary"] + fam["binary_bool"] + fam["binary_inplace"] == 237
     assert fam["unary"] + fam["unary_bool"] + fam["unary_const"] + fam["unary_const_bool"] == 295
-    assert fam["reduce"] + fam["sum_to_shape"] == 52
+    assert fam["reduce"] + fam["sum_to_shape"] == 64
+    assert fam["pad"] + fam["pad_const"] == 72
+    assert fam["softmax"] == 4
+    assert len(table) == 704
     assert fam["matmul"] + fam["matmul_backward"] == 24
     assert fam["conv"] == 8
     exported = _exported()

@@ -166,3 +166,35 @@ def test_mse_golden(oracle):
     p2 = H.run_unary(oracle, "mul_scalar", dt, [n], [1], 0, p1, scalar=2.0)
     grad = H.run_binary(oracle, "mul", dt, [n], [1], [1], 0, 0, gb, p2)
     assert np.allclose(grad, np.array(rec["grad"], np.float32), rtol=1e-6)
+
+
+@pytest.mark.parametrize("rec", GOLD["padding"], ids=lambda r: f"{r['mode']}-{r['shape']}-{r['pads']}")
+def test_padding_golden(oracle, rec):
+    """Values from crates/maidenx_tensor/tests/ops_padding.rs; the gradient is the backward of sum(padded),
+    i.e. the padding's backward applied to ones."""
+    for dt in D.ARITH:
+        if rec["value"] is not None and rec["value"] != int(rec["value"]) and dt.kind != "float":
+            continue  # 9.9 truncates to 9 for integer dtypes in the reference's test; the float arm is the golden one
+        shape, pads = rec["shape"], [tuple(p) for p in rec["pads"]]
+        store = _padded(rec["input"], dt)
+        got = H.run_pad(oracle, rec["mode"], dt, shape, H.contiguous_strides(shape), 1, pads, store, rec["value"])
+        tol = 0.1 if dt.name in ("bf16", "f16") else (1e-6 if dt.name == "f32" else 0)
+        assert np.allclose(D.decode(got, dt).astype(np.float64), np.array(rec["expected"]), atol=tol), (dt.name, got)
+        if rec["grad"] is not None:
+            n_out = len(rec["expected"])
+            gi = H.run_pad_backward(oracle, rec["mode"], dt, shape, H.contiguous_strides(shape), 0, pads, D.encode(np.ones(n_out), dt), len(rec["input"]))
+            assert np.allclose(D.decode(gi, dt).astype(np.float64), np.array(rec["grad"]), atol=tol), (dt.name, gi)
+
+
+@pytest.mark.parametrize("rec", GOLD["fold"], ids=lambda r: f"{r['shape']}-dim{r['dim']}")
+def test_fold_golden(oracle, rec):
+    """crates/maidenx_tensor/tests/ops_reduction.rs:484-531: x.unfold(dim, size, step).fold(dim, size, step)."""
+    for dt in D.ARITH:
+        shape, dim, size, step = rec["shape"], rec["dim"], rec["size"], rec["step"]
+        st = H.contiguous_strides(shape)
+        nwin = (shape[dim] - size) // step + 1
+        dims = shape[:dim] + [nwin, size] + shape[dim + 1:]      # the unfolded view (crates/maidenx_core/src/layout.rs:193-250):
+        strides = st[:dim] + [step * st[dim], st[dim]] + st[dim + 1:]  # window count, then the window right behind it
+        got = H.run_fold(oracle, dt, dims, strides, dim, dim + 1, shape[dim], step, 1, _padded(rec["input"], dt))
+        tol = 0.1 if dt.name in ("bf16", "f16") else 0
+        assert np.allclose(D.decode(got, dt).astype(np.float64), np.array(rec["expected"]), atol=tol), (dt.name, got)
