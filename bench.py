@@ -190,6 +190,31 @@ def run_sweep_group(torch, lib_mod, cases, iters, warm, seeds, dist):
 # ---------------------------------------------------------------------------------------
 # CPU arm: the oracle port of the reference's CPU backend on the host cores
 # ---------------------------------------------------------------------------------------
+def dispatch_overhead(torch, lib, iters=300):
+    """Host-side cost of one op call made the reference's way (crates/maidenx_core/src/be/ops/binary.rs:112-163):
+    cuda_malloc + cuda_memcpy_h2d of the metadata block, the op, cuda_free - on a 64-element add, so the kernel
+    itself is negligible.  With the small-block pool the free no longer synchronises the device."""
+    from maidenx_b200 import device
+    a = torch.ones(64, device="cuda")
+    b = torch.ones(64, device="cuda")
+    o = torch.empty(64, device="cuda")
+    meta = [64, 1, 1, 0, 0]
+    out = {}
+    for label, on in (("pooled_us_per_op", 1), ("cuda_malloc_free_us_per_op", 0)):
+        lib.mx_set_small_pool(on)
+        for _ in range(20):
+            device.dispatch("add", "f32", meta, SZ(64), SZ(1), "META", a.data_ptr(), b.data_ptr(), o.data_ptr())
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            device.dispatch("add", "f32", meta, SZ(64), SZ(1), "META", a.data_ptr(), b.data_ptr(), o.data_ptr())
+        torch.cuda.synchronize()
+        out[label] = round((time.perf_counter() - t0) / iters * 1e6, 2)
+    lib.mx_set_small_pool(1)
+    out["what"] = "cuda_malloc + cuda_memcpy_h2d(metadata) + cuda_add_f32(64 elements) + cuda_free through ctypes, host wall clock"
+    return out
+
+
 def cpu_sweep(cases_fn, R, C, passes):
     """Times the oracle on a bounded sample: the same sweep at [R, C] instead of [16384, 16384]."""
     from oracle import binding
@@ -482,6 +507,7 @@ def main():
             "elementwise_aggregate_gbs": round(sum(r["bytes"] for r in ew) / sum(r["ms"] for r in ew) / 1e6, 1),
             "cases_at_or_above_80pct_of_measured": sum(1 for g in ("elementwise", "reduction", "conv") for r in sweeps_out[g] if r["frac"] >= 0.8),
             "cases": sum(len(sweeps_out[g]) for g in ("elementwise", "reduction", "conv"))}
+        sweeps_out["dispatch"] = dispatch_overhead(torch, lib)
         if lib.mx_last_error():
             raise RuntimeError(f"op library reported status {lib.mx_last_error()} at {lib.mx_last_error_where().decode()}")
     if rank == 0 and world == 1 and not args.no_cpu:

@@ -245,6 +245,20 @@ MX_DTYPES_FLOAT(MX_DECL_SOFTMAX_T, _)
 #define MX_DECL_CONTIGUOUS_T(T, ...) void mx_contiguous_##T(size_t num_els, size_t num_dims, const size_t* metadata, const mx_##T* inp, mx_##T* out);
 MX_DTYPES_ALL(MX_DECL_CONTIGUOUS_T, _)
 
+/* Dtype casts on the device, dense buffers: out[i] = cast(in[i]) with the element rules of the reference's host-side
+ * conversion (crates/maidenx_core/src/buffer/mod.rs:132-575; listed in maidenx_b200/csrc/cast.cu).  One symbol per
+ * ordered pair of the 13 dtypes: mx_cast_<from>_<to>(num_els, in, out). */
+#define MX_CAST_TARGETS(X, FROM)                                                                                     \
+    X(bf16, FROM) X(f16, FROM) X(f32, FROM) X(f64, FROM) X(bool, FROM) X(u8, FROM) X(u16, FROM) X(u32, FROM) X(u64, FROM) \
+    X(i8, FROM) X(i16, FROM) X(i32, FROM) X(i64, FROM)
+#define MX_DECL_CAST(TO, FROM) void mx_cast_##FROM##_##TO(size_t num_els, const mx_##FROM* in, mx_##TO* out);
+#define MX_DECL_CAST_FROM(FROM, ...) MX_CAST_TARGETS(MX_DECL_CAST, FROM)
+MX_DTYPES_ALL(MX_DECL_CAST_FROM, _)
+
+/* cuda_malloc serves requests of up to 2 KB (the per-call metadata blocks of the dispatch layer) from a pool of
+ * fixed-size slots and cuda_free hands them back without a device synchronisation; 0 turns the pool off. */
+void mx_set_small_pool(int enabled);
+
 /* Stream used by this thread's subsequent op launches (NULL = legacy default stream). */
 void mx_set_stream(void* stream);
 void* mx_get_stream(void);

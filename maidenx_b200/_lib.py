@@ -60,6 +60,7 @@ RUNTIME_SIGNATURES = {
     "mx_mlp_dp_join": ([ctypes.c_void_p], None),
     "mx_mlp_dp_set_exchange": ([ctypes.c_void_p, ctypes.c_int, ctypes.c_int], ctypes.c_int),
     "mx_set_gemm_sm_limit": ([ctypes.c_int], None),
+    "mx_set_small_pool": ([ctypes.c_int], None),
 }
 
 
@@ -90,6 +91,14 @@ def load() -> ctypes.CDLL:
     _ops = sig.bind(lib, "cuda_")
     _lib = lib
     return lib
+
+
+def cast(from_name: str, to_name: str):
+    """`mx_cast_<from>_<to>(num_els, in, out)`: dense dtype conversion on the device."""
+    fn = getattr(load(), f"mx_cast_{from_name}_{to_name}")
+    fn.argtypes = [ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
+    fn.restype = None
+    return fn
 
 
 def contiguous(dtype_name: str):

@@ -10,6 +10,7 @@
 // address; the op entry points find the block there without touching the GPU.  Blocks
 // uploaded some other way are read back with a synchronous cudaMemcpy, and a metadata
 // pointer that is ordinary host memory is used directly.
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -161,14 +162,78 @@ static void side_table_forget(const void* p) {
 
 using namespace mx;
 
+namespace mx {
+namespace {
+constexpr size_t kPoolSlotBytes = 2048;
+constexpr size_t kPoolSlabSlots = 256;
+std::atomic<bool> g_pool_enabled{true};
+
+struct Slab {
+    char* base;
+    int device;
+};
+std::mutex g_pool_mutex;
+std::vector<Slab> g_slabs;
+std::vector<void*> g_free_slots[64];  // per device
+
+void* pool_take() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(g_pool_mutex);
+    std::vector<void*>& fl = g_free_slots[dev];
+    if (fl.empty()) {
+        void* slab = nullptr;
+        if (cudaMalloc(&slab, kPoolSlotBytes * kPoolSlabSlots) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;  // the caller falls back to a plain allocation
+        }
+        g_slabs.push_back({static_cast<char*>(slab), dev});
+        for (size_t i = kPoolSlabSlots; i-- > 0;) fl.push_back(static_cast<char*>(slab) + i * kPoolSlotBytes);
+    }
+    void* p = fl.back();
+    fl.pop_back();
+    return p;
+}
+
+bool pool_give_back(void* ptr) {
+    if (!ptr) return false;
+    std::lock_guard<std::mutex> lk(g_pool_mutex);
+    for (const Slab& sl : g_slabs) {
+        if (ptr >= sl.base && ptr < sl.base + kPoolSlotBytes * kPoolSlabSlots) {
+            g_free_slots[sl.device].push_back(ptr);
+            return true;
+        }
+    }
+    return false;
+}
+}  // namespace
+}  // namespace mx
+using namespace mx;
+
 extern "C" {
 
-int cuda_malloc(void** ptr, size_t size) { return (int)cudaMalloc(ptr, size); }
+// Small blocks come from a pool.  The reference's dispatch layer allocates and frees a metadata block
+// around EVERY op call (crates/maidenx_core/src/be/ops/binary.rs:112-133,161-163), and cudaFree
+// synchronises the device each time; requests of up to kPoolSlotBytes are served from slabs of
+// fixed-size slots that are handed back to a free list instead.  Reuse is safe in stream order: a
+// slot is only rewritten by work queued after its previous user.  mx_set_small_pool(0) turns it off.
+int cuda_malloc(void** ptr, size_t size) {
+    if (ptr && size <= kPoolSlotBytes && g_pool_enabled.load(std::memory_order_relaxed)) {
+        if (void* p = pool_take()) {
+            *ptr = p;
+            return (int)cudaSuccess;
+        }
+    }
+    return (int)cudaMalloc(ptr, size);
+}
 
 int cuda_free(void* ptr) {
     side_table_forget(ptr);
+    if (pool_give_back(ptr)) return (int)cudaSuccess;
     return (int)cudaFree(ptr);
 }
+
+void mx_set_small_pool(int enabled) { g_pool_enabled.store(enabled != 0, std::memory_order_relaxed); }
 
 int cuda_memcpy_h2d(void* dst, const void* src, size_t size) {
     cudaError_t e = cudaMemcpy(dst, src, size, cudaMemcpyHostToDevice);

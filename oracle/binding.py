@@ -46,6 +46,14 @@ def op(name: str, dtype_name: str):
     return _ops[(name, dtype_name)]
 
 
+def cast(from_name: str, to_name: str):
+    """cast_<from>_<to>(num_els, in, out): the reference's host-side dtype conversion, element by element."""
+    fn = getattr(load(), f"cast_{from_name}_{to_name}")
+    fn.argtypes = [ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
+    fn.restype = None
+    return fn
+
+
 def set_wide(wide: bool):
     load().oracle_set_wide(1 if wide else 0)
 

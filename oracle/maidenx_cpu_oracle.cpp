@@ -1319,3 +1319,55 @@ static void softmax_op(size_t n, size_t nd, size_t dim, const size_t* meta, cons
 #define DEF_SOFTMAX(SUF, T) \
     extern "C" void softmax_##SUF(size_t n, size_t nd, size_t dim, const size_t* m, const T* i, T* o) { softmax_op<T>(n, nd, dim, m, i, o); }
 FOR_FLOAT4(DEF_SOFTMAX)
+
+// ---------------------------------------------------------------------------------
+// dtype casts: crates/maidenx_core/src/buffer/mod.rs:132-575 (copy_from_with_dtype_cast).  Element rules:
+//   16-bit float -> X        to_f32(x) `as` X (float -> int saturates, NaN -> 0); -> bool: to_f32(x) != 0   (:330-378)
+//   f32 / f64 -> 16-bit      from_f32(x as f32): an f64 is rounded to f32 first                              (:281-302)
+//   f32 / f64 -> int, float  Rust `as`                                                                       (:152-196)
+//   anything -> bool         x != 0 (a NaN is true)                                                          (:260-280)
+//   bool -> X                through u8 (0 / 1)
+//   u8 / i8 -> 16-bit float  exact (`From`);  wider integers -> 16-bit float go through `as u8` / `as i8` FIRST, i.e. only
+//                            their low byte survives (:93-94, :107-108, :121-122, :149-150, :163-164, :177-178)
+//   int -> int               Rust `as`: truncate or sign-/zero-extend
+// ---------------------------------------------------------------------------------
+template <class From, class To>
+static inline To cast_one(From x) {
+    if constexpr (std::is_same<From, To>::value) {
+        return x;
+    } else if constexpr (std::is_same<To, bool>::value) {
+        if constexpr (is_half_v<From>) return x.to_f32() != 0.0f;
+        else return x != (From)0;
+    } else if constexpr (is_half_v<From>) {
+        const f32 v = x.to_f32();
+        if constexpr (is_half_v<To>) return To::from_f32(v);
+        else if constexpr (std::is_floating_point<To>::value) return (To)v;
+        else return sat_cast<To, f32>(v);
+    } else if constexpr (is_half_v<To>) {
+        if constexpr (std::is_floating_point<From>::value) return To::from_f32((f32)x);
+        else if constexpr (std::is_same<From, bool>::value) return To::from_f32(x ? 1.0f : 0.0f);
+        else if constexpr (std::is_signed<From>::value) return To::from_f32((f32)(int8_t)x);   // `as i8`, then From<i8>
+        else return To::from_f32((f32)(uint8_t)x);                                             // `as u8`, then From<u8>
+    } else if constexpr (std::is_floating_point<From>::value) {
+        if constexpr (std::is_floating_point<To>::value) return (To)x;
+        else return sat_cast<To, From>(x);
+    } else if constexpr (std::is_same<From, bool>::value) {
+        return (To)(uint8_t)(x ? 1 : 0);
+    } else {
+        return (To)x;  // integer source: value-preserving to floats (round to nearest), modular to integers
+    }
+}
+template <class From, class To>
+static void cast_op(size_t n, const From* in, To* out) {
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < (long long)n; i++) out[i] = cast_one<From, To>(in[i]);
+}
+#define DEF_CAST_TO(TSUF, TO, FSUF, FROM) \
+    extern "C" void cast_##FSUF##_##TSUF(size_t n, const FROM* i, TO* o) { cast_op<FROM, TO>(n, i, o); }
+// (a second copy of the dtype list: a macro cannot expand inside its own expansion)
+#define CAST_TARGETS(X, ...)                                                                                                                 \
+    X(bf16, bf16, ##__VA_ARGS__) X(f16, f16, ##__VA_ARGS__) X(f32, f32, ##__VA_ARGS__) X(f64, f64, ##__VA_ARGS__) X(bool, bool, ##__VA_ARGS__) \
+    X(u8, u8, ##__VA_ARGS__) X(u16, u16, ##__VA_ARGS__) X(u32, u32, ##__VA_ARGS__) X(u64, u64, ##__VA_ARGS__)                                \
+    X(i8, i8, ##__VA_ARGS__) X(i16, i16, ##__VA_ARGS__) X(i32, i32, ##__VA_ARGS__) X(i64, i64, ##__VA_ARGS__)
+#define DEF_CAST_FROM(FSUF, FROM) CAST_TARGETS(DEF_CAST_TO, FSUF, FROM)
+FOR_ALL13(DEF_CAST_FROM)

@@ -269,3 +269,37 @@ def test_16bit_float_arithmetic_is_bit_exact_on_random_bit_patterns(oracle, cuda
         ref = H.run_binary(oracle, op, dt, [r, c], [1, r], [c, 1], 0, 0, a, b)
         got = H.run_binary(cuda, op, dt, [r, c], [1, r], [c, 1], 0, 0, a, b)
         H.assert_same(op, dt, got, ref, what="bit-patterns-transposed")
+
+
+def test_small_block_pool_reuses_slots_and_can_be_switched_off(cuda):
+    """cuda_malloc of a metadata-sized block comes from the pool: freeing and allocating again returns the same
+    slot, slots of one slab are 2 KB apart, and a large request bypasses the pool."""
+    import ctypes
+
+    from maidenx_b200 import _lib
+    lib = _lib.load()
+
+    def alloc(n):
+        p = ctypes.c_void_p()
+        assert lib.cuda_malloc(ctypes.byref(p), n) == 0
+        return p.value
+
+    lib.mx_set_small_pool(1)
+    a, b = alloc(40), alloc(2048)
+    assert abs(a - b) % 2048 == 0
+    assert lib.cuda_free(a) == 0
+    c = alloc(16)
+    assert c == a                      # the freed slot is handed out again
+    big = alloc(1 << 20)
+    assert lib.cuda_free(big) == 0 and lib.cuda_free(b) == 0 and lib.cuda_free(c) == 0
+    # ops keep working on pooled metadata blocks (the whole suite runs that way); with the pool off as well
+    lib.mx_set_small_pool(0)
+    try:
+        d = alloc(40)
+        assert lib.cuda_free(d) == 0
+        rng = np.random.default_rng(0)
+        x, y = H.random_store(rng, D.F32, 100), H.random_store(rng, D.F32, 100)
+        got = H.run_binary(cuda, "add", D.F32, [100], [1], [1], 0, 0, x, y)
+        assert np.array_equal(got, x + y)
+    finally:
+        lib.mx_set_small_pool(1)
