@@ -280,9 +280,10 @@ def reference_arm(args):
 MLP_LAYERS, MLP_DIM, MLP_GLOBAL_BATCH, MLP_LR = 4, 8192, 16384, 1e-3
 MLP_GEMMS_PER_STEP = 3 * MLP_LAYERS - 1       # dX of the first layer is not needed and not computed
 # kernels launched per step: 11 GEMMs + 4 bias(/gelu) passes + 2 (mse, mse finish) + 3 gelu backward
-# + 8 (bias-gradient sums, two passes each) + 8 SGD updates (weights and bias per layer)
+# + 4 bias-gradient sums (partials folded inside the same launch) + 8 SGD updates (weights and bias per layer);
+# with the NVLink exchange the 8 SGD launches become 4 x (barrier, fused reduce + update, barrier)
 GEMM_DRAM_BYTES_PER_FLOP = 655.2e6 / 5.4976e11
-MLP_KERNELS_PER_STEP = MLP_GEMMS_PER_STEP + MLP_LAYERS + 2 + (MLP_LAYERS - 1) + 2 * MLP_LAYERS + 2 * MLP_LAYERS
+MLP_KERNELS_PER_STEP = MLP_GEMMS_PER_STEP + MLP_LAYERS + 2 + (MLP_LAYERS - 1) + MLP_LAYERS + 2 * MLP_LAYERS
 
 
 EXCHANGE_TEXT = {
@@ -334,25 +335,31 @@ def time_gemm(torch, lib_mod, local_batch, iters=10):
 
 
 def e2e_mlp(torch, lib, mlp, x, y, dist, world, steps, warm):
-    """The same step fed from pinned host memory: H2D of the shard's inputs, the step, D2H of the loss."""
+    """The same step fed from pinned host memory: every step copies its shard's inputs host -> device and reads the
+    loss back.  The copies of step i + 1 run on a copy stream into the second of two device buffers while step i
+    computes (an input pipeline: the user-facing loop of maidenx_b200.mlp.InputPipeline)."""
+    from maidenx_b200.mlp import InputPipeline
     hx, hy = x.cpu().pin_memory(), y.cpu().pin_memory()
     nbytes = x.numel() * x.element_size()
     loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
+    pipe = InputPipeline(torch, x, y)
 
-    def step():
-        lib.cuda_memcpy_h2d(x.data_ptr(), hx.data_ptr(), nbytes)
-        lib.cuda_memcpy_h2d(y.data_ptr(), hy.data_ptr(), nbytes)
-        mlp.train_step(x.data_ptr(), y.data_ptr(), MLP_LR, torch, dist, world)
-        lib.cuda_memcpy_d2h(loss_host.data_ptr(), mlp.ptr("loss_ptr"), 4)
+    def run(n):
+        pipe.prefetch(hx, hy)
+        for i in range(n):
+            xb, yb = pipe.next_batch()          # the compute stream now waits for this batch's copies
+            if i + 1 < n:
+                pipe.prefetch(hx, hy)           # next batch: copies overlap this step
+            mlp.train_step(xb.data_ptr(), yb.data_ptr(), MLP_LR, torch, dist, world)
+            pipe.release()                      # the buffers may be overwritten once this step's kernels are done
+            lib.cuda_memcpy_d2h(loss_host.data_ptr(), mlp.ptr("loss_ptr"), 4)
 
-    for _ in range(warm):
-        step()
+    run(warm)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     t0 = time.perf_counter()
-    for _ in range(steps):
-        step()
+    run(steps)
     torch.cuda.synchronize()
     dt_s = (time.perf_counter() - t0) / steps
     if world > 1:
@@ -360,7 +367,8 @@ def e2e_mlp(torch, lib, mlp, x, y, dist, world, steps, warm):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dt_s = float(t.item())
     return {"value": round(MLP_GLOBAL_BATCH / dt_s, 1), "unit": "samples/s", "h2d_bytes_per_step": 2 * nbytes * world, "d2h_bytes_per_step": 4 * world,
-            "steps": steps, "ms_per_step": round(dt_s * 1e3, 3), "loss": float(loss_host[0])}
+            "steps": steps, "ms_per_step": round(dt_s * 1e3, 3), "loss": float(loss_host[0]),
+            "pipeline": "double-buffered: host->device copies of step i+1 on a copy stream while step i computes"}
 
 
 def cpu_mlp(sample_batch, steps=1):
@@ -369,6 +377,7 @@ def cpu_mlp(sample_batch, steps=1):
     from oracle import binding, mlp_reference
     from maidenx_b200 import dtypes as D
     binding.load()
+    binding.set_num_threads(os.cpu_count() or 1)  # all host cores, also under torchrun (which exports OMP_NUM_THREADS=1)
     binding.set_reduce_parallel(True)
     rng = np.random.default_rng(6)
     bound = 1.0 / np.sqrt(MLP_DIM)
@@ -474,7 +483,7 @@ def main():
 
     # the dominant kernel alone, live, on this rank's shapes
     gemm_ms, gemm_flops = time_gemm(torch, lib_mod, local_batch)
-    e2e = None if args.no_e2e else e2e_mlp(torch, lib, mlp, x, y, dist, world, steps=3, warm=1)
+    e2e = None if args.no_e2e else e2e_mlp(torch, lib, mlp, x, y, dist, world, steps=6, warm=2)
     clocks = sampler.stop()
 
     sweeps_out, roofline, cpu = {}, None, None

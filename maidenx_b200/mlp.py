@@ -184,6 +184,50 @@ def make_mlp(layers: int, dim: int, batch: int, dtype: str, seed: int, torch=Non
     return m
 
 
+class InputPipeline:
+    """Double-buffered host -> device input feed for a training loop.
+
+        pipe = InputPipeline(torch, x_like, y_like)
+        pipe.prefetch(host_x, host_y)
+        for ...:
+            xb, yb = pipe.next_batch()       # compute stream waits (on the device) for the copies of this batch
+            pipe.prefetch(next_host_x, next_host_y)   # overlaps the step below
+            mlp.train_step(xb.data_ptr(), yb.data_ptr(), lr, ...)
+            pipe.release()                   # this batch's buffers may be refilled after the step's kernels
+
+    Host tensors must be pinned for the copies to be asynchronous.  The compute stream is the stream the op library
+    launches on (torch's current stream unless mx_set_stream chose another: pass it as `compute_stream`)."""
+
+    def __init__(self, torch, x_like, y_like, compute_stream=None):
+        self.torch = torch
+        self.compute = compute_stream or torch.cuda.current_stream()
+        self.copy = torch.cuda.Stream()
+        self.bufs = [(x_like, y_like), (torch.empty_like(x_like), torch.empty_like(y_like))]
+        self.copied = [torch.cuda.Event(), torch.cuda.Event()]
+        self.consumed = [torch.cuda.Event(), torch.cuda.Event()]
+        for e in self.consumed:
+            e.record(self.compute)
+        self.filled, self.taken = 0, 0
+
+    def prefetch(self, host_x, host_y):
+        slot = self.filled % 2
+        with self.torch.cuda.stream(self.copy):
+            self.copy.wait_event(self.consumed[slot])
+            self.bufs[slot][0].copy_(host_x, non_blocking=True)
+            self.bufs[slot][1].copy_(host_y, non_blocking=True)
+            self.copied[slot].record(self.copy)
+        self.filled += 1
+
+    def next_batch(self):
+        slot = self.taken % 2
+        self.compute.wait_event(self.copied[slot])
+        return self.bufs[slot]
+
+    def release(self):
+        self.consumed[self.taken % 2].record(self.compute)
+        self.taken += 1
+
+
 class _CudaArray:
     """Minimal __cuda_array_interface__ holder so torch can alias memory owned by the library."""
 
