@@ -154,3 +154,32 @@ def device_read(ptr, np_dtype, count):
     out = np.empty(count, dtype=np_dtype)
     assert _lib.load().cuda_memcpy_d2h(out.ctypes.data, ptr, out.nbytes) == 0
     return out
+
+
+def test_input_pipeline_delivers_batches_in_order(cuda):
+    """maidenx_b200.mlp.InputPipeline: the batch handed out by next_batch() is the one prefetched for it, also when
+    the next prefetch is queued before the consumer ran (the consumer here is mx_contiguous_f32 on the op stream)."""
+    import torch
+
+    from maidenx_b200.mlp import InputPipeline
+    n = 1 << 20
+    like_x = torch.empty(n, dtype=torch.float32, device="cuda")
+    like_y = torch.empty(n, dtype=torch.float32, device="cuda")
+    out = torch.empty(n, dtype=torch.float32, device="cuda")
+    host = [(torch.full((n,), float(i)).pin_memory(), torch.full((n,), float(-i)).pin_memory()) for i in range(5)]
+    pipe = InputPipeline(torch, like_x, like_y)
+    fn = _lib.contiguous("f32")
+    meta = np.array([n, 1, 0], dtype=np.uint64)
+    seen = []
+    pipe.prefetch(*host[0])
+    for i in range(5):
+        xb, yb = pipe.next_batch()
+        if i + 1 < 5:
+            pipe.prefetch(*host[i + 1])
+        fn(SZ(n), SZ(1), meta.ctypes.data, xb.data_ptr(), out.data_ptr())   # consumer on the library's stream
+        fn(SZ(n), SZ(1), meta.ctypes.data, yb.data_ptr(), xb.data_ptr())    # and a second one that overwrites the x buffer
+        pipe.release()
+        device.synchronize()
+        seen.append((float(out[0]), float(out[-1]), float(xb[n // 2])))
+    assert seen == [(float(i), float(i), float(-i)) for i in range(5)]
+    assert device.last_error() is None
