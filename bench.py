@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
-"""Benchmark of the sm_100a op library (see DESIGN.md for what each number means).
+"""Benchmark of the sm_100a op library.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload auto|elementwise|mlp]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--exchange auto|multimem-exclusive|multimem|peer|copy|nccl]
     python bench.py --impl reference ...      # the CPU arm: the oracle port on the host cores
 
 One JSON line is printed by rank 0.  `value` is whole-job throughput with inputs resident

@@ -9,7 +9,7 @@ outputs and tolerances out of each arm.  The reduction, matmul, padding, fold an
 below by hand with the line they come from; every literal listed is checked to be present
 in the cited source range before it is written out.
 
-Usage:  python tests/golden/extract_reference_vectors.py [/path/to/reference]
+Usage:  python tests/golden/extract_reference_vectors.py /path/to/reference
 """
 from __future__ import annotations
 
@@ -262,7 +262,9 @@ def check_needles(ref: Path, cite, needles):
 
 
 def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: extract_reference_vectors.py <path to a checkout of the reference (miniex/maidenx)>")
+    ref = Path(sys.argv[1])
     data = {
         "_comment": "Known-answer vectors of the reference's own tests, lifted from its test sources as text by "
                     "tests/golden/extract_reference_vectors.py. Every fixture in those tests is a padded buffer "
