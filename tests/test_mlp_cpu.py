@@ -114,3 +114,77 @@ def test_two_rank_data_parallel_step_equals_single_process_step():
     m.step(x, y, 0.1)
     for l in range(L):
         assert np.allclose(got[l], m.W[l], rtol=1e-5, atol=1e-7)
+
+
+def _sharded_worker(rank, world, port, L, Dm, B, q):
+    """The exchange the CUDA data-parallel engine performs (csrc/dp_sync.cu), restated over gloo: every rank sums,
+    in rank order, only ITS 1/world shard of each layer's gradients, updates that shard of the weights, and the
+    shards are gathered back so that all ranks hold the full new weights."""
+    import torch
+    import torch.distributed as dist
+    from oracle.mlp_reference import CpuMlp
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    W, b = _model(L, Dm, 1)
+    rng = np.random.default_rng(2)
+    x, y = rng.standard_normal(B * Dm).astype(np.float32), rng.standard_normal(B * Dm).astype(np.float32)
+    local = B // world
+    xs, ys = x[rank * local * Dm:(rank + 1) * local * Dm].copy(), y[rank * local * Dm:(rank + 1) * local * Dm].copy()
+    m = CpuMlp(L, Dm, local, "f32", W, b)
+    _, gW, gb = m.gradients(xs, ys)
+    lr, scale = np.float32(0.1), np.float32(1.0 / world)
+    n = Dm * Dm
+    shard = n // world
+    lo, hi = rank * shard, (rank + 1) * shard
+    for l in reversed(range(L)):
+        # "peer loads": my shard of every rank's gradient, summed in rank order
+        pieces = [torch.empty(shard, dtype=torch.float32) for _ in range(world)]
+        for owner in range(world):                       # rank `owner` collects shard `owner` from everyone
+            mine = torch.from_numpy(gW[l][owner * shard:(owner + 1) * shard].copy())
+            dist.gather(mine, pieces if rank == owner else None, dst=owner)
+        acc = np.zeros(shard, dtype=np.float32)
+        for p in range(world):
+            acc = acc + pieces[p].numpy()
+        new_shard = m.W[l][lo:hi] - (lr * scale) * acc   # the update touches 1/world of the weights
+        # "peer stores": every rank receives every shard
+        out = [torch.empty(shard, dtype=torch.float32) for _ in range(world)]
+        dist.all_gather(out, torch.from_numpy(new_shard.astype(np.float32)))
+        m.W[l] = np.concatenate([t.numpy() for t in out])
+        # the scalar bias: every rank adds all ranks' gradients in rank order
+        gbs = [torch.empty(1, dtype=torch.float32) for _ in range(world)]
+        dist.all_gather(gbs, torch.from_numpy(gb[l].copy()))
+        s = np.float32(0)
+        for t in gbs:
+            s = np.float32(s + t.numpy()[0])
+        m.b[l] = (m.b[l] - (lr * scale) * s).astype(np.float32)
+    q.put((rank, [w.copy() for w in m.W], [v.copy() for v in m.b]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_reduce_update_gather_equals_single_process_step():
+    import torch.multiprocessing as mp
+    from oracle.mlp_reference import CpuMlp
+    L, Dm, B, world = 2, 16, 16, 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_sharded_worker, args=(r, world, port, L, Dm, B, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict((r, (w, bb)) for r, w, bb in (q.get(timeout=120) for _ in range(world)))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    # every rank ends with bit-identical parameters ...
+    for l in range(L):
+        assert np.array_equal(results[0][0][l], results[1][0][l]) and np.array_equal(results[0][1][l], results[1][1][l])
+    # ... and they are those of one process training on the whole batch
+    W, b = _model(L, Dm, 1)
+    rng = np.random.default_rng(2)
+    x, y = rng.standard_normal(B * Dm).astype(np.float32), rng.standard_normal(B * Dm).astype(np.float32)
+    m = CpuMlp(L, Dm, B, "f32", W, b)
+    m.step(x, y, 0.1)
+    for l in range(L):
+        assert np.allclose(results[0][0][l], m.W[l], rtol=1e-5, atol=1e-7)
+        assert np.allclose(results[0][1][l], m.b[l], rtol=1e-5, atol=1e-7)
