@@ -43,3 +43,32 @@ def test_f64_to_16_bit_rounds_twice_and_bool_rules(oracle):
     assert D.decode(_cast(oracle, np.array([True, False]), D.BOOL, D.BF16), D.BF16).tolist() == [1.0, 0.0]
     assert _cast(oracle, np.array([-1, 256, 65536 + 7], dtype=np.int64), D.I64, D.U8).tolist() == [255, 0, 7]
     assert _cast(oracle, np.array([200], dtype=np.uint8), D.U8, D.I8).tolist() == [-56]
+
+
+def test_integer_and_plain_float_casts_agree_with_numpy(oracle):
+    """For integer sources (to integers: truncate / extend; to f32 / f64: round to nearest), bool sources and
+    f32 <-> f64, numpy's astype has the semantics of Rust's `as`: an independent check of about 100 of the pairs."""
+    rng = np.random.default_rng(5)
+    ints = [D.U8, D.U16, D.U32, D.U64, D.I8, D.I16, D.I32, D.I64]
+    for sdt in ints + [D.BOOL]:
+        if sdt is D.BOOL:
+            x = rng.integers(0, 2, 4096).astype(np.bool_)
+        else:
+            info = np.iinfo(sdt.np_storage)
+            x = rng.integers(info.min, info.max, 4096, dtype=sdt.np_storage, endpoint=True)
+            x[:4] = [info.min, info.max, 0, 1]
+        for ddt in ints + [D.F32, D.F64, D.BOOL]:
+            if ddt is sdt:
+                continue
+            got = _cast(oracle, x, sdt, ddt)
+            want = (x != 0) if ddt is D.BOOL else x.astype(ddt.np_storage)
+            assert np.array_equal(got, want), (sdt.name, ddt.name)
+    f = (rng.standard_normal(4096) * 10.0 ** rng.integers(-30, 30, 4096)).astype(np.float64)
+    assert np.array_equal(_cast(oracle, f, D.F64, D.F32), f.astype(np.float32))
+    f32 = f.astype(np.float32)
+    assert np.array_equal(_cast(oracle, f32, D.F32, D.F64), f32.astype(np.float64))
+    # f32 -> 16-bit floats: numpy's float16 is IEEE binary16 with round-to-nearest-even, like the half crate
+    h = (rng.standard_normal(4096) * 10.0 ** rng.integers(-6, 5, 4096)).astype(np.float32)
+    with np.errstate(over="ignore"):
+        assert np.array_equal(_cast(oracle, h, D.F32, D.F16).view(np.uint16), h.astype(np.float16).view(np.uint16))
+    assert np.array_equal(_cast(oracle, h, D.F32, D.BF16), D.f32_to_bf16_bits(h))
