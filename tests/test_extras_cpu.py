@@ -35,3 +35,65 @@ def test_oracle_softmax_rows_of_the_reference_example(oracle):
     # along dim 0: every column is softmax([a, a + 3])
     got0 = D.decode(H.run_softmax(oracle, D.F32, [2, 3], [3, 1], 0, 0, D.encode(x.ravel(), D.F32)), D.F32).reshape(2, 3)
     assert np.allclose(got0[0], 1.0 / (1.0 + np.exp(3.0)), rtol=1e-6) and np.all(got0[0] < got0[1])
+
+
+NP_MODE = {"constant": "constant", "reflection": "reflect", "replication": "edge"}
+
+
+@pytest.mark.parametrize("mode", ["constant", "reflection", "replication"])
+def test_oracle_padding_agrees_with_numpy_pad(oracle, mode):
+    """np.pad's constant / reflect / edge modes are the three paddings; the backward pass is the transpose of the
+    forward gather, built here by padding an index array and scatter-adding."""
+    rng = np.random.default_rng(len(mode))
+    cases = [([11], [(3, 5)]), ([6, 9], [(2, 1), (4, 3)]), ([3, 5, 7], [(0, 2), (1, 0), (3, 3)])]
+    for dt in (D.F64, D.F32, D.I32, D.U8):
+        for shape, pads in cases:
+            n = int(np.prod(shape))
+            x = rng.integers(0, 50, n).astype(np.float64)
+            store = D.encode(x, dt)
+            kw = {"constant_values": 7} if mode == "constant" else {}
+            want = np.pad(x.reshape(shape), pads, mode=NP_MODE[mode], **kw).ravel()
+            got = H.run_pad(oracle, mode, dt, shape, H.contiguous_strides(shape), 0, pads, store, 7)
+            assert np.array_equal(D.decode(got, dt).astype(np.float64), want), (mode, dt.name, shape)
+            # a transposed view of the same data gives the padded transpose
+            if len(shape) == 2:
+                xt = np.ascontiguousarray(x.reshape(shape).T)       # stored transposed, viewed back as `shape`
+                got_t = H.run_pad(oracle, mode, dt, shape, [1, shape[0]], 0, pads, D.encode(xt.ravel(), dt), 7)
+                assert np.array_equal(D.decode(got_t, dt).astype(np.float64), want), (mode, dt.name, "transposed")
+            # backward: where each output element was read from
+            idx = np.arange(n, dtype=np.int64).reshape(shape)
+            if mode == "constant":
+                src = np.pad(idx, pads, mode="constant", constant_values=-1).ravel()
+            else:
+                src = np.pad(idx, pads, mode=NP_MODE[mode]).ravel()
+            g = rng.integers(-20, 20, src.size).astype(np.float64) if dt is not D.U8 else rng.integers(0, 5, src.size).astype(np.float64)
+            want_g = np.zeros(n)
+            np.add.at(want_g, src[src >= 0], g[src >= 0])
+            got_g = H.run_pad_backward(oracle, mode, dt, shape, H.contiguous_strides(shape), 0, pads, D.encode(g, dt), n)
+            ref = want_g if dt is not D.U8 else np.mod(want_g, 256)
+            assert np.array_equal(D.decode(got_g, dt).astype(np.float64), ref), (mode, dt.name, shape, "backward")
+
+
+def test_oracle_fold_is_the_transpose_of_unfold(oracle):
+    """fold(unfold view of x) multiplies every element by the number of windows that cover it, and fold of a dense
+    gradient equals numpy's scatter-add over the window positions."""
+    rng = np.random.default_rng(3)
+    for shape, dim, size, step in (([23], 0, 5, 2), ([4, 17], 1, 4, 3), ([9, 6], 0, 3, 1)):
+        st = H.contiguous_strides(shape)
+        nwin = (shape[dim] - size) // step + 1
+        dims = shape[:dim] + [nwin, size] + shape[dim + 1:]
+        g = rng.integers(-9, 9, int(np.prod(dims))).astype(np.float64)
+        fold_size = (nwin - 1) * step + size
+        out_shape = shape[:dim] + [fold_size] + shape[dim + 1:]
+        want = np.zeros(out_shape)
+        gv = g.reshape(dims)
+        for w in range(nwin):
+            for p in range(size):
+                sl = [slice(None)] * len(out_shape)
+                sl[dim] = w * step + p
+                src = [slice(None)] * len(dims)
+                src[dim], src[dim + 1] = w, p
+                want[tuple(sl)] += gv[tuple(src)]
+        for dt in (D.F64, D.F32, D.I64):
+            got = H.run_fold(oracle, dt, dims, H.contiguous_strides(dims), dim, dim + 1, fold_size, step, 0, D.encode(g, dt))
+            assert np.array_equal(D.decode(got, dt).astype(np.float64), want.ravel()), (shape, dim, dt.name)
