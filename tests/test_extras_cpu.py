@@ -97,3 +97,38 @@ def test_oracle_fold_is_the_transpose_of_unfold(oracle):
         for dt in (D.F64, D.F32, D.I64):
             got = H.run_fold(oracle, dt, dims, H.contiguous_strides(dims), dim, dim + 1, fold_size, step, 0, D.encode(g, dt))
             assert np.array_equal(D.decode(got, dt).astype(np.float64), want.ravel()), (shape, dim, dt.name)
+
+
+def _np_im2col(x, kh, kw, ph, pw, sh, sw):
+    B, C, Hh, W = x.shape
+    oh, ow = (Hh + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+    xp = np.pad(x, ((0, 0), (0, 0), (ph, ph), (pw, pw)))
+    col = np.zeros((B, C, kh, kw, oh, ow))
+    for i in range(kh):
+        for j in range(kw):
+            col[:, :, i, j] = xp[:, :, i:i + sh * oh:sh, j:j + sw * ow:sw]
+    return col, oh, ow
+
+
+@pytest.mark.parametrize("geom", [(3, 3, 1, 1, 1, 1), (3, 3, 0, 0, 2, 2), (2, 5, 1, 2, 1, 3), (1, 1, 0, 0, 1, 1)], ids=str)
+def test_oracle_im2col_col2im_agree_with_numpy(oracle, geom):
+    """The reference pins conv only by shapes; this checks the restatement against an independent numpy
+    formulation: col[b][c,kh,kw][oh,ow] = padded x at (oh*s - p + kh, ow*s - p + kw), and col2im as its transpose."""
+    kh, kw, ph, pw, sh, sw = geom
+    rng = np.random.default_rng(sum(geom))
+    B, C, Hh, W = 2, 3, 9, 11
+    x = rng.integers(-9, 9, (B, C, Hh, W)).astype(np.float64)
+    col, oh, ow = _np_im2col(x, kh, kw, ph, pw, sh, sw)
+    meta = H.conv_metadata(B, C, Hh, W, kh, kw, oh, ow, ph, pw, sh, sw)
+    for dt in (D.F32, D.F64):
+        got = H.run_im2col(oracle, dt, meta, col.size, D.encode(x.ravel(), dt))
+        assert np.array_equal(D.decode(got, dt).astype(np.float64), col.ravel()), (geom, dt.name)
+        # col2im of an arbitrary col = the transpose of the gather: scatter-add every col entry to its pixel
+        g = rng.integers(-9, 9, col.shape).astype(np.float64)
+        want = np.zeros((B, C, Hh + 2 * ph, W + 2 * pw))
+        for i in range(kh):
+            for j in range(kw):
+                want[:, :, i:i + sh * oh:sh, j:j + sw * ow:sw] += g[:, :, i, j]
+        want = want[:, :, ph:ph + Hh, pw:pw + W]
+        got = H.run_col2im(oracle, dt, meta, g.size, D.encode(g.ravel(), dt), x.size)
+        assert np.array_equal(D.decode(got, dt).astype(np.float64), want.ravel()), (geom, dt.name, "col2im")
