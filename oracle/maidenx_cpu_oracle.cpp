@@ -20,11 +20,15 @@
 // Exported symbols carry the reference backend's own names (`add_f32`, `sum_bf16`, …)
 // and argument order, with the metadata pointer in host memory.
 //
+// Later sections add the rest of the backend with their own citations: fold, the three paddings with
+// their backward passes, softmax, and the dtype casts of crates/maidenx_core/src/buffer/mod.rs.
+//
 // Pinning: checked against the known-answer vectors of the reference's own tests
-// (crates/maidenx_tensor/tests/ops_{binary,unary,reduction,matmul}.rs), stored under
-// tests/golden/.  Nothing in the reference pins im2col / col2im values or the exact
-// 16-bit rounding of the `half` crate; for those this restatement is the definition
-// ("parity unpinned").
+// (crates/maidenx_tensor/tests/ops_{binary,unary,reduction,matmul,padding}.rs, the fold test in
+// ops_reduction.rs, crates/maidenx_nn/src/losses/mse.rs), stored under tests/golden/.  The reference
+// pins no values for im2col / col2im, softmax or the dtype casts, and the 16-bit rounding of the
+// `half` crate only loosely ("parity unpinned" by the reference); those parts are checked against
+// independent numpy formulations in tests/test_extras_cpu.py and tests/test_cast_cpu.py.
 //
 // Accumulation modes (oracle_set_wide):
 //   0 = faithful: sums and dot products accumulate in the element type, ascending
