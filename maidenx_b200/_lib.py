@@ -61,6 +61,11 @@ RUNTIME_SIGNATURES = {
     "mx_mlp_dp_set_exchange": ([ctypes.c_void_p, ctypes.c_int, ctypes.c_int], ctypes.c_int),
     "mx_set_gemm_sm_limit": ([ctypes.c_int], None),
     "mx_set_small_pool": ([ctypes.c_int], None),
+    "mx_debug_elementwise_plan": ([ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t,
+                                   ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
+                                   ctypes.POINTER(ctypes.c_int)], ctypes.c_int),
+    "mx_debug_reduce_plan": ([ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_size_t),
+                              ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)], ctypes.c_int),
 }
 
 

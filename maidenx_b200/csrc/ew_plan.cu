@@ -311,3 +311,18 @@ void ew_fill_gen_params(const EwPlan& pl, EwGenParams& P) {
 }
 
 }  // namespace mx
+
+// Host-only view of the planner for tests that run without a GPU: which kernel class a call would take.
+// metadata is HOST memory in the layout of the op family (binary: [dims | lhs strides | rhs strides | offsets],
+// unary: [dims | strides | offset]); returns the EwKind (0 empty, 1 flat, 2 row, 3 tile, 4 generic,
+// 5 serial, 6 error) and writes the merged rank, the vector flag and the tile's transposed-operand mask.
+extern "C" int mx_debug_elementwise_plan(size_t num_els, size_t num_dims, const size_t* host_metadata, int num_inputs, int inplace,
+                                         size_t elem_size, size_t out_elem_size, const void* out, const void* a, const void* b, int* merged_rank,
+                                         int* vector_ok, int* transposed_mask) {
+    mx::EwPlan pl;
+    mx::ew_make_plan(pl, num_els, num_dims, host_metadata, num_inputs, inplace != 0, elem_size, out_elem_size, out, a, b);
+    if (merged_rank) *merged_rank = pl.nd;
+    if (vector_ok) *vector_ok = pl.vec ? 1 : 0;
+    if (transposed_mask) *transposed_mask = pl.kind == mx::EW_TILE ? ((pl.transposed[1] ? 1 : 0) | (pl.transposed[2] ? 2 : 0)) : 0;
+    return pl.kind;
+}

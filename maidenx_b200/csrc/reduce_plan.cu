@@ -199,3 +199,17 @@ void red_plan_shape(RedPlan& pl, size_t n, size_t nd, const size_t* hm) {
 }
 
 }  // namespace mx
+
+// Host-only view of the reduction planner (see mx_debug_elementwise_plan): returns the RedPlanKind
+// (0 empty, 1 rows, 2 cols, 3 generic scatter, 4 error) and the recognised [O, R, I] structure.
+// sum_to_shape != 0 reads metadata as [in_dims | in_strides | out_dims | offset] and ignores num_red_dims.
+extern "C" int mx_debug_reduce_plan(size_t num_els, size_t num_dims, size_t num_red_dims, const size_t* host_metadata, int sum_to_shape,
+                                    size_t* outer, size_t* reduced, size_t* inner) {
+    mx::RedPlan pl;
+    if (sum_to_shape) mx::red_plan_shape(pl, num_els, num_dims, host_metadata);
+    else mx::red_plan_dims(pl, num_els, num_dims, num_red_dims, host_metadata);
+    if (outer) *outer = pl.O;
+    if (reduced) *reduced = pl.R;
+    if (inner) *inner = pl.I;
+    return pl.kind;
+}

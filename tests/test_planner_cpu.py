@@ -1,0 +1,77 @@
+"""The host-side launch planners, without a GPU: layouts of the benchmark and of the parity tests must be
+recognised as the kernel class that was written for them (a silent fall to the generic gather kernel would keep
+every parity test green and lose an order of magnitude of bandwidth)."""
+import ctypes
+
+import numpy as np
+
+from maidenx_b200 import _lib
+
+FLAT, ROW, TILE, GENERIC, SERIAL = 1, 2, 3, 4, 5
+ROWS, COLS, SCATTER = 1, 2, 3
+BASE = 0x7F0000000000  # a 256-byte aligned pretend device address: the planner only looks at alignment
+
+
+def ew_plan(meta, nd, n, nin=2, inplace=False, esz=4, osz=4, out=BASE, a=BASE + (1 << 32), b=BASE + (2 << 32)):
+    lib = _lib.load()
+    m = np.asarray(meta, dtype=np.uint64)
+    rank, vec, tmask = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    kind = lib.mx_debug_elementwise_plan(n, nd, m.ctypes.data, nin, int(inplace), esz, osz, out, a, b, ctypes.byref(rank), ctypes.byref(vec),
+                                         ctypes.byref(tmask))
+    return kind, rank.value, vec.value, tmask.value
+
+
+def test_benchmark_layouts_take_their_kernels():
+    R = C = 16384
+    n = R * C
+    assert ew_plan([R, C, C, 1, C, 1, 0, 0], 2, n)[:3] == (FLAT, 1, 1)                 # contiguous: merged to one dim
+    kind, rank, vec, tmask = ew_plan([R, C, 1, R, C, 1, 0, 0], 2, n)                    # transposed lhs
+    assert (kind, vec, tmask) == (TILE, 1, 1)
+    assert ew_plan([R, C, C, 1, 0, 1, 0, 0], 2, n)[:3] == (ROW, 2, 1)                  # rhs broadcast from [1, C]
+    assert ew_plan([R, C, 1, R, 0], 2, n, nin=1)[0] == TILE                            # unary on a transposed view
+    assert ew_plan([R, C, 0, 1, 0], 2, n, nin=1)[0] == ROW                             # unary on a broadcast row
+    for esz in (2, 4, 8):
+        assert ew_plan([R, C, 1, R, C, 1, 0, 0], 2, n, esz=esz, osz=esz)[0] == TILE
+
+
+def test_odd_layouts_degrade_gracefully():
+    # offset 1 (the layout of the reference's test fixtures) breaks 16-byte alignment: the vector kernels are
+    # not legal and the call takes the per-element gather kernel - correct, but not a bandwidth path
+    assert ew_plan([1000, 1, 1, 1, 1], 1, 1000)[:3] == (GENERIC, 1, 0)
+    # the same view at an aligned offset is flat again
+    assert ew_plan([1000, 1, 1, 4, 8], 1, 1000)[:3] == (FLAT, 1, 1)
+    # a permuted 3-d view has no unit-stride pairing the tile kernel handles
+    assert ew_plan([5, 6, 7, 1, 35, 5, 42, 7, 1, 0, 0], 3, 210)[0] == GENERIC
+    # size-1 dims are dropped before anything else
+    assert ew_plan([1, 9, 1, 11, 99, 11, 11, 1, 99, 11, 11, 1, 0, 0], 4, 99)[:2] == (FLAT, 1)
+    # both operands transposed the same way: the output is the only direct operand
+    kind, _, _, tmask = ew_plan([96, 80, 1, 96, 1, 96, 0, 0], 2, 96 * 80)
+    assert (kind, tmask) == (TILE, 3)
+    # in-place with an lhs that overlaps itself (stride 0) must run serially
+    assert ew_plan([8, 4, 0, 1, 4, 1, 0, 0], 2, 32, inplace=True, out=BASE, a=BASE)[0] == SERIAL
+    # scalars
+    assert ew_plan([2, 1], 0, 1)[0] in (FLAT, GENERIC)
+
+
+def red_plan(meta, nd, nr, n, shape=False):
+    lib = _lib.load()
+    m = np.asarray(meta, dtype=np.uint64)
+    o, r, i = ctypes.c_size_t(), ctypes.c_size_t(), ctypes.c_size_t()
+    kind = lib.mx_debug_reduce_plan(n, nd, nr, m.ctypes.data, int(shape), ctypes.byref(o), ctypes.byref(r), ctypes.byref(i))
+    return kind, o.value, r.value, i.value
+
+
+def test_reduction_layouts_take_their_kernels():
+    R, C = 8192, 16384
+    n = R * C
+    assert red_plan([R, C, C, 1, R, C, 0], 2, 1, n) == (COLS, 1, R, C)                  # dim 0: fold 8192 rows of 16384 columns
+    assert red_plan([R, C, C, 1, C, 1, 0], 2, 1, n)[:3] == (ROWS, R, C)                 # dim 1: 8192 rows of 16384
+    # sum_to_shape [64, 512, 4096] -> [1, 1, 4096]: the two leading dims fold into one reduced extent
+    assert red_plan([64, 512, 4096, 512 * 4096, 4096, 1, 1, 1, 4096, 0], 3, 0, 64 * 512 * 4096, shape=True) == (COLS, 1, 64 * 512, 4096)
+    # the middle dim of a 3-d tensor
+    assert red_plan([7, 129, 5, 645, 5, 1, 129, 5, 0], 3, 1, 7 * 129 * 5) == (COLS, 7, 129, 5)
+    # a full reduction as the MLP's bias gradient issues it
+    assert red_plan([1 << 20, 1, 1 << 20, 1, 0], 1, 1, 1 << 20)[:3] == (ROWS, 1, 1 << 20)
+    # two reduced dims at once, or a transposed input, follow the reference's index formulas literally
+    assert red_plan([4, 6, 8, 48, 8, 1, 4, 8, 48, 1, 0], 3, 2, 192)[0] == SCATTER
+    assert red_plan([64, 32, 1, 64, 64, 1, 0], 2, 1, 2048)[0] == SCATTER
