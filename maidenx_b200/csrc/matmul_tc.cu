@@ -508,34 +508,50 @@ extern "C" int mx_tc_gemm_status(void) {
     return v;
 }
 
+// Forward product C[m, n] = sum_k A[m, k] * B[k, n]: can it run on the tensor-core kernel, and with which operand
+// majors?  Unbatched, every operand either dense row-major or the transposed view of a dense matrix.
+struct ForwardClass {
+    const char* A;
+    const char* B;
+    bool a_mn, b_mn;
+    uint64_t m, n, k;
+};
+static bool classify_forward(const MmDesc& d, size_t num_els, const void* x, const void* y, const void* out, ForwardClass& c) {
+    const size_t es = 2;
+    if (d.out_nd < 2 || d.a_nd < 2 || d.b_nd < 2) return false;
+    const uint64_t m = d.m, n = d.n, k = d.k_fwd;
+    if (num_els != m * n) return false;  // batched products stay on the SIMT path
+    c.A = static_cast<const char*>(x) + d.a_off * es;
+    c.B = static_cast<const char*>(y) + d.b_off * es;
+    bool a_kmajor, a_mnmajor, b_kmajor, b_mnmajor;
+    if (d.a_cont && d.b_cont) {
+        // the reference's contiguous branch: A is [m, k], B is [k, n], both dense
+        a_kmajor = true;
+        a_mnmajor = false;
+        b_kmajor = false;
+        b_mnmajor = true;
+    } else {
+        // strided branch: A[m * as1 + k * as2], B[k * bs1 + n * bs2]
+        a_kmajor = d.a_strides[2] == 1 && d.a_strides[1] == (int64_t)k;
+        a_mnmajor = d.a_strides[1] == 1 && d.a_strides[2] == (int64_t)m;  // transposed view of a dense [k, m] matrix
+        b_kmajor = d.b_strides[1] == 1 && d.b_strides[2] == (int64_t)k;   // transposed view of a dense [n, k] matrix
+        b_mnmajor = d.b_strides[2] == 1 && d.b_strides[1] == (int64_t)n;  // dense [k, n]
+    }
+    if (!(a_kmajor || a_mnmajor) || !(b_kmajor || b_mnmajor)) return false;
+    c.a_mn = !a_kmajor;
+    c.b_mn = !b_kmajor;
+    c.m = m;
+    c.n = n;
+    c.k = k;
+    return eligible(m, n, k, c.a_mn, c.b_mn, c.A, c.B, out);
+}
+
 bool tc_gemm_bf16_f16(bool is_bf16, const MmDesc& d, int which, size_t num_els, size_t nea, size_t neb, const void* x, const void* y, void* out,
                       const char* where) {
-    const size_t es = 2;
     if (which == 0) {
-        // forward: C[m, n] = sum_k A[m, k] * B[k, n], unbatched, dense operands
-        if (d.out_nd < 2 || d.a_nd < 2 || d.b_nd < 2) return false;
-        const uint64_t m = d.m, n = d.n, k = d.k_fwd;
-        if (num_els != m * n) return false;  // batched products stay on the SIMT path
-        const char* A = static_cast<const char*>(x) + d.a_off * es;
-        const char* B = static_cast<const char*>(y) + d.b_off * es;
-        bool a_kmajor, a_mnmajor, b_kmajor, b_mnmajor;
-        if (d.a_cont && d.b_cont) {
-            // the reference's contiguous branch: A is [m, k], B is [k, n], both dense
-            a_kmajor = true;
-            a_mnmajor = false;
-            b_kmajor = false;
-            b_mnmajor = true;
-        } else {
-            // strided branch: A[m * as1 + k * as2], B[k * bs1 + n * bs2]
-            a_kmajor = d.a_strides[2] == 1 && d.a_strides[1] == (int64_t)k;
-            a_mnmajor = d.a_strides[1] == 1 && d.a_strides[2] == (int64_t)m;  // transposed view of a dense [k, m] matrix
-            b_kmajor = d.b_strides[1] == 1 && d.b_strides[2] == (int64_t)k;   // transposed view of a dense [n, k] matrix
-            b_mnmajor = d.b_strides[2] == 1 && d.b_strides[1] == (int64_t)n;  // dense [k, n]
-        }
-        if (!(a_kmajor || a_mnmajor) || !(b_kmajor || b_mnmajor)) return false;
-        const bool a_mn = !a_kmajor, b_mn = !b_kmajor;
-        if (!eligible(m, n, k, a_mn, b_mn, A, B, out)) return false;
-        return launch_gemm(is_bf16, A, a_mn, B, b_mn, out, m, n, k, where);
+        ForwardClass c;
+        if (!classify_forward(d, num_els, x, y, out, c)) return false;
+        return launch_gemm(is_bf16, c.A, c.a_mn, c.B, c.b_mn, out, c.m, c.n, c.k, where);
     }
     // backward products read g, A and B as dense row-major matrices (strides ignored)
     if (d.out_nd != 2) return false;
@@ -552,3 +568,20 @@ bool tc_gemm_bf16_f16(bool is_bf16, const MmDesc& d, int which, size_t num_els, 
 }
 
 }  // namespace mx
+
+// Host-only view for tests without a GPU: would cuda_matmul_<bf16|f16> with this HOST metadata and these base
+// addresses run on the tensor-core kernel?  Returns 0 (SIMT kernel) or 1, and the operand majors (0 = K-major,
+// 1 = MN-major) and extents it would be launched with.
+extern "C" int mx_debug_matmul_forward_path(size_t num_els, const size_t* host_metadata, const void* a, const void* b, const void* out, int* a_mn_major,
+                                            int* b_mn_major, size_t* m, size_t* n, size_t* k) {
+    mx::MmDesc d;
+    if (!host_metadata || !mx::mm_parse(host_metadata, d)) return 0;
+    mx::ForwardClass c;
+    if (!mx::classify_forward(d, num_els, a, b, out, c)) return 0;
+    if (a_mn_major) *a_mn_major = c.a_mn ? 1 : 0;
+    if (b_mn_major) *b_mn_major = c.b_mn ? 1 : 0;
+    if (m) *m = c.m;
+    if (n) *n = c.n;
+    if (k) *k = c.k;
+    return 1;
+}

@@ -75,3 +75,31 @@ def test_reduction_layouts_take_their_kernels():
     # two reduced dims at once, or a transposed input, follow the reference's index formulas literally
     assert red_plan([4, 6, 8, 48, 8, 1, 4, 8, 48, 1, 0], 3, 2, 192)[0] == SCATTER
     assert red_plan([64, 32, 1, 64, 64, 1, 0], 2, 1, 2048)[0] == SCATTER
+
+
+def mm_path(meta, num_els, a=BASE, b=BASE + (1 << 32), out=BASE + (2 << 32)):
+    lib = _lib.load()
+    m_ = np.asarray(meta, dtype=np.uint64)
+    amn, bmn = ctypes.c_int(-1), ctypes.c_int(-1)
+    M, N, K = ctypes.c_size_t(), ctypes.c_size_t(), ctypes.c_size_t()
+    tc = lib.mx_debug_matmul_forward_path(num_els, m_.ctypes.data, a, b, out, ctypes.byref(amn), ctypes.byref(bmn), ctypes.byref(M),
+                                          ctypes.byref(N), ctypes.byref(K))
+    return tc, amn.value, bmn.value, M.value, N.value, K.value
+
+
+def test_the_three_products_of_a_linear_layer_run_on_the_tensor_core_kernel():
+    """Forward x . W^T (B read through a transposed view), dW = du^T . a (A through a transposed view) and
+    dX = du . W (both dense), at the benchmark's per-rank shapes for 1 and 8 ranks: none needs a transposed copy."""
+    D = 8192
+    for B in (16384, 2048):
+        assert mm_path([2, 2, 2, B, D, B, D, D, D, D, 1, 1, D, 0, 0], B * D) == (1, 0, 0, B, D, D)       # NT: both K-major
+        assert mm_path([2, 2, 2, D, D, D, B, B, D, 1, D, D, 1, 0, 0], D * D) == (1, 1, 1, D, D, B)       # TN: both MN-major
+        assert mm_path([2, 2, 2, B, D, B, D, D, D, D, 1, D, 1, 0, 0], B * D) == (1, 0, 1, B, D, D)       # NN
+
+
+def test_products_the_tensor_core_kernel_does_not_take():
+    assert mm_path([2, 2, 2, 64, 64, 64, 64, 64, 64, 64, 1, 64, 1, 0, 0], 64 * 64)[0] == 0               # too small for a persistent launch
+    assert mm_path([2, 2, 2, 512, 516, 512, 512, 512, 516, 512, 1, 516, 1, 0, 0], 512 * 516)[0] == 0     # N not a multiple of 8 elements
+    assert mm_path([2, 2, 2, 512, 512, 512, 512, 512, 512, 512, 1, 512, 1, 1, 0], 512 * 512)[0] == 0     # offset 1: base not 16-byte aligned
+    assert mm_path([2, 2, 2, 512, 512, 512, 512, 512, 512, 1024, 2, 512, 1, 0, 0], 512 * 512)[0] == 0    # A with a stride of 2 along k
+    assert mm_path([3, 3, 3, 4, 512, 512, 4, 512, 512, 4, 512, 512, 262144, 512, 1, 262144, 512, 1, 0, 0], 4 * 512 * 512)[0] == 0  # batched
