@@ -544,14 +544,18 @@ def run_only_case(torch, lib_mod, args):
         groups = sweeps.elementwise_cases(8192, 8192) + sweeps.reduction_cases(4096, 16384, (16, 512, 4096)) + sweeps.conv_cases(N=16)
     else:
         groups = sweeps.elementwise_cases() + sweeps.reduction_cases() + sweeps.conv_cases()
-    if args.only_case.startswith("gemm_bf16"):
-        # the forward product of one MLP layer; --small: 8192 x 4096 x 8192 (256 MB of operands, above L2)
+    if args.only_case.startswith("gemm_"):
+        # gemm_<bf16|f16|f32>[_<MxNxK>]: the forward product x . W^T of one MLP layer; --small: 8192 x 4096 x 8192 (above L2)
+        parts = args.only_case.split("_")
+        dt = parts[1]
         M, N, K = (8192, 4096, 8192) if args.small else (MLP_GLOBAL_BATCH, MLP_DIM, MLP_DIM)
-        x = torch.randn(M, K, device="cuda").bfloat16()
-        w = (torch.randn(N, K, device="cuda") / K ** 0.5).bfloat16()
-        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        if len(parts) > 2:
+            M, N, K = (int(v) for v in parts[2].split("x"))
+        x = torch.randn(M, K, device="cuda").to(torch_dtype(dt))
+        w = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch_dtype(dt))
+        c = torch.empty(M, N, device="cuda", dtype=torch_dtype(dt))
         meta = np.array([2, 2, 2, M, N, M, K, K, N, K, 1, 1, K, 0, 0], dtype=np.uint64)
-        f = lib_mod.op("matmul", "bf16")
+        f = lib_mod.op("matmul", dt)
         ms = time_launches(torch, lambda: f(SZ(M * N), meta.ctypes.data, x.data_ptr(), w.data_ptr(), c.data_ptr()), max(1, args.steps), max(0, args.warmup))
         lib_mod.load().mx_device_synchronize()
         print(json.dumps({"case": args.only_case, "shape": [M, N, K], "ms": round(ms, 4), "tflops": round(2.0 * M * N * K / ms / 1e9, 1),

@@ -259,20 +259,6 @@ MX_DTYPES_ALL(MX_DECL_CAST_FROM, _)
  * fixed-size slots and cuda_free hands them back without a device synchronisation; 0 turns the pool off. */
 void mx_set_small_pool(int enabled);
 
-/* Host-only views of the launch planners, for tests that run without a GPU: which kernel class a call with this
- * HOST metadata and these base addresses would take.  Elementwise: 0 empty, 1 flat, 2 row, 3 tile, 4 generic,
- * 5 serial (an in-place lhs that overlaps itself), 6 error.  Reduction: 0 empty, 1 rows, 2 columns, 3 generic
- * scatter, 4 error, with the recognised [outer, reduced, inner] extents. */
-int mx_debug_elementwise_plan(size_t num_els, size_t num_dims, const size_t* host_metadata, int num_inputs, int inplace, size_t elem_size,
-                              size_t out_elem_size, const void* out, const void* a, const void* b, int* merged_rank, int* vector_ok,
-                              int* transposed_mask);
-/* Would cuda_matmul_<bf16|f16> with this HOST metadata run on the tcgen05 kernel (1) or on the SIMT kernel (0)?
- * Also returns the operand layouts (0 = K-major, 1 = MN-major) and the extents of the launch. */
-int mx_debug_matmul_forward_path(size_t num_els, const size_t* host_metadata, const void* a, const void* b, const void* out, int* a_mn_major,
-                                 int* b_mn_major, size_t* m, size_t* n, size_t* k);
-int mx_debug_reduce_plan(size_t num_els, size_t num_dims, size_t num_red_dims, const size_t* host_metadata, int sum_to_shape, size_t* outer,
-                         size_t* reduced, size_t* inner);
-
 /* Stream used by this thread's subsequent op launches (NULL = legacy default stream). */
 void mx_set_stream(void* stream);
 void* mx_get_stream(void);

@@ -32,6 +32,7 @@
 // still reads the old weights) and one after it (every shard of the new weights has landed).
 // The waiting kernels run on different GPUs, one per GPU, so they are always co-resident.
 #include <cstdlib>
+#include <mutex>
 
 #include "abi_common.cuh"
 #include "ops.cuh"
@@ -243,10 +244,23 @@ static void dp_reduce_sgd_launch(const DpPeers& peers, void* mc_base, const DpLa
     const size_t nvec = L.shard_elems / 8;
     if (exclusive_sms > 0 && !staged && mc_base) {
         // k CTAs of 1024 threads, one per SM, kept apart from the GEMM by their shared-memory request
-        static bool opted_in = false;
-        if (!opted_in) {
-            cudaFuncSetAttribute(dp_reduce_sgd_kernel<T, kMulticast>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDpExclusiveSmem);
-            opted_in = true;
+        // the opt-in to large dynamic shared memory is a per-device function attribute
+        static std::mutex mu;
+        static bool opted_in[64] = {false};
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+            set_error(kErrNoDevice, 0, where);
+            return;
+        }
+        {
+            std::lock_guard<std::mutex> lock(mu);
+            if (!opted_in[dev]) {
+                if (cudaFuncSetAttribute(dp_reduce_sgd_kernel<T, kMulticast>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDpExclusiveSmem) != cudaSuccess) {
+                    set_error(kErrCuda, (int)cudaGetLastError(), where);
+                    return;
+                }
+                opted_in[dev] = true;
+            }
         }
         dp_reduce_sgd_kernel<T, kMulticast><<<exclusive_sms, kDpMaxThreads, kDpExclusiveSmem, s>>>(peers, static_cast<char*>(mc_base), L, rank, world, step, 0);
         check_launch(where);

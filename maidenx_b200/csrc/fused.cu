@@ -151,13 +151,23 @@ __global__ void __launch_bounds__(kFusedThreads) sgd_kernel(float* __restrict__ 
     const uint64_t stride = (uint64_t)gridDim.x * kFusedThreads;
     for (uint64_t v = (uint64_t)blockIdx.x * kFusedThreads + threadIdx.x; v < nvec; v += stride) {
         Vec<T, VEC> gi = *reinterpret_cast<const Vec<T, VEC>*>(g + v * VEC), wo;
-        Vec<float, VEC> w = *reinterpret_cast<const Vec<float, VEC>*>(w32 + v * VEC);
+        // the master weights are promised 16-byte aligned only: move them as float4 quads, never as one 32-byte access
+        float4 w[VEC / 4];
 #pragma unroll
-        for (int j = 0; j < VEC; j++) {
-            w.v[j] = w.v[j] - step * up(gi.v[j]);
-            wo.v[j] = st_from_f32<T>(w.v[j]);
+        for (int q = 0; q < VEC / 4; q++) w[q] = *reinterpret_cast<const float4*>(w32 + v * VEC + 4 * q);
+#pragma unroll
+        for (int q = 0; q < VEC / 4; q++) {
+            w[q].x = w[q].x - step * up(gi.v[4 * q + 0]);
+            w[q].y = w[q].y - step * up(gi.v[4 * q + 1]);
+            w[q].z = w[q].z - step * up(gi.v[4 * q + 2]);
+            w[q].w = w[q].w - step * up(gi.v[4 * q + 3]);
+            wo.v[4 * q + 0] = st_from_f32<T>(w[q].x);
+            wo.v[4 * q + 1] = st_from_f32<T>(w[q].y);
+            wo.v[4 * q + 2] = st_from_f32<T>(w[q].z);
+            wo.v[4 * q + 3] = st_from_f32<T>(w[q].w);
         }
-        *reinterpret_cast<Vec<float, VEC>*>(w32 + v * VEC) = w;
+#pragma unroll
+        for (int q = 0; q < VEC / 4; q++) *reinterpret_cast<float4*>(w32 + v * VEC + 4 * q) = w[q];
         *reinterpret_cast<Vec<T, VEC>*>(w16 + v * VEC) = wo;
     }
     if (blockIdx.x == 0)

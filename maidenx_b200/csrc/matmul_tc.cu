@@ -30,8 +30,11 @@
 #include <unordered_map>
 
 #include "matmul_tc.cuh"
+#include "tc_ptx.cuh"
 
 namespace mx {
+
+using namespace tc;
 
 namespace {
 
@@ -46,7 +49,6 @@ constexpr int EPI_STAGE_BYTES = 32 * EPI_CHUNK_COLS * 2;  // 4 KB per warp per b
 constexpr int TC_THREADS = 32 * (2 + EPI_WARPS);
 constexpr int TMEM_COLS = 512;                // two 256-column f32 accumulators
 constexpr int GROUP_M = 16;                   // row-tiles per column sweep (L2 re-use)
-constexpr long long WAIT_BUDGET_CYCLES = 4000000000ll;  // about two seconds
 
 struct SmemLayout {
     // offsets inside the dynamic shared memory block (base aligned to 1024 bytes)
@@ -58,118 +60,6 @@ struct SmemLayout {
 };
 constexpr int TC_SMEM_BYTES = SmemLayout::total + 1024;  // slack for the 1024-byte alignment
 
-// ---------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: returns false (and records `code` in *err) when the budget runs out or when
-// another thread has already reported an error.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (true) {
-        for (int i = 0; i < 64; i++)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (*reinterpret_cast<volatile int*>(err) != 0) return false;
-        if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
-            atomicCAS(err, 0, code);
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-                 "l"(map), "r"(x), "r"(y), "r"(bar)
-                 : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
-          "=r"(r[31])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptors, 128-byte swizzle.  Fields: start address >> 4 in bits
-// [0,14), leading byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), descriptor
-// version 1 (sm_100) at bit 46, layout type 2 (128-byte swizzle) in [61,64).
-//  * K-major tile (rows of 64 K-elements = 128 bytes): groups of 8 rows are 1024 bytes apart
-//    (stride byte offset); the leading byte offset is not used.  Advancing 16 elements along K
-//    stays inside the swizzled row: +32 bytes on the start address.
-//  * MN-major tile, stored as chunks of [64 K-rows x 64 MN-elements] (one TMA box each, 8 KB):
-//    groups of 8 K-rows are 1024 bytes apart (stride byte offset) and the next 64 MN-elements
-//    start 8192 bytes later (leading byte offset).  Advancing 16 elements along K = two groups
-//    of 8 K-rows: +2048 bytes on the start address.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)(lbo_bytes >> 4) << 16;
-    d |= (uint64_t)(sbo_bytes >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
 constexpr int MN_CHUNK_BYTES = 64 * BK * 2;  // one [64 K-rows x 64 MN] box
 
 // Instruction descriptor of tcgen05.mma kind::f16 with f32 accumulation.
@@ -214,7 +104,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_d,
-               TcParams p, int* err) {
+               TcParams p, int* err, int tag) {
     extern __shared__ unsigned char tc_smem_raw[];
     // 128-byte swizzled TMA tiles and UMMA descriptors want 1024-byte aligned bases
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -259,7 +149,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 int tm, tn;
                 tile_coords(tile, p, tm, tn);
                 for (int kb = 0; kb < p.num_kb; kb++) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1, err, 1)) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1, err, tag, 1)) {
                         ok = false;
                         break;
                     }
@@ -296,11 +186,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, err, 2)) break;
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, err, tag, 2)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
                 for (int kb = 0; kb < p.num_kb; kb++) {
-                    if (!mbar_wait(full_bar(stage), phase, err, 3)) {
+                    if (!mbar_wait(full_bar(stage), phase, err, tag, 3)) {
                         ok = false;
                         break;
                     }
@@ -334,7 +224,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int tm, tn;
             tile_coords(tile, p, tm, tn);
             // the TMEM loads below are warp-collective: leave the loop only as a whole warp
-            const bool ready = mbar_wait(tfull_bar(acc), acc_phase, err, 4);
+            const bool ready = mbar_wait(tfull_bar(acc), acc_phase, err, tag, 4);
             if (!__all_sync(0xFFFFFFFFu, ready)) break;
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
@@ -383,7 +273,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // common exit: TMEM is released by the warp that allocated it, after everyone is done with it
     tc_fence_before();
     __syncthreads();
-    if (*reinterpret_cast<volatile int*>(err) != 0) {
+    if (tc_err_mine(err, tag)) {
         // a wait gave up: give bulk copies still in flight towards this CTA's shared memory time to land
         const long long t0 = clock64();
         while (clock64() - t0 < 4000000ll) {
@@ -400,64 +290,34 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ---------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
 // [rows, cols] row-major 16-bit matrix, box = box_rows x 64 columns, 128-byte swizzle
 bool make_map(CUtensorMap* map, bool is_bf16, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-    EncodeTiledFn enc = encode_fn();
-    if (!enc) return false;
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols * 2};
-    cuuint32_t box[2] = {64, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
+    return make_map_2d(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, rows, cols, box_rows);
 }
 
-struct DeviceState {
-    int* err = nullptr;       // device error word
-    bool attr_set = false;
-};
-thread_local DeviceState t_state[64];
-
-DeviceState* device_state() {
+bool opt_in_shared_memory() {
+    static std::mutex mu;
+    static bool done[64] = {false};
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    DeviceState& s = t_state[dev];
-    if (!s.err) {
-        if (cudaMalloc(&s.err, sizeof(int)) != cudaSuccess) return nullptr;
-        cudaMemset(s.err, 0, sizeof(int));
-    }
-    if (!s.attr_set) {
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done[dev]) {
         if (cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES) != cudaSuccess) {
             cudaGetLastError();
-            return nullptr;
+            return false;
         }
-        s.attr_set = true;
+        done[dev] = true;
     }
-    return &s;
+    return true;
 }
 
 // D[M,N] = sum_k Aop[m,k] * Bop[n,k].  A K-major operand is a dense row-major [MN, K] matrix, an
 // MN-major operand a dense row-major [K, MN] matrix; D is dense row-major [M, N].
 bool launch_gemm(bool is_bf16, const void* A, bool a_mn, const void* B, bool b_mn, void* D, uint64_t M, uint64_t N, uint64_t K, const char* where) {
-    DeviceState* st = device_state();
-    if (!st) return false;
+    if (!opt_in_shared_memory()) return false;
+    int tag = 0;
+    int* err = next_launch_error_word(&tag);
+    if (!err) return false;
     CUtensorMap ma, mb, md;
     const bool oka = a_mn ? make_map(&ma, is_bf16, A, K, M, 64) : make_map(&ma, is_bf16, A, M, K, BM);
     const bool okb = b_mn ? make_map(&mb, is_bf16, B, K, N, 64) : make_map(&mb, is_bf16, B, N, K, BN);
@@ -476,48 +336,132 @@ bool launch_gemm(bool is_bf16, const void* A, bool a_mn, const void* B, bool b_m
     int grid = sm_count();
     if (ctx().gemm_sm_limit > 0 && ctx().gemm_sm_limit < grid) grid = ctx().gemm_sm_limit;
     if (grid > p.num_tiles) grid = p.num_tiles;
-    tc_gemm_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx().stream>>>(ma, mb, md, p, st->err);
+    tc_gemm_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx().stream>>>(ma, mb, md, p, err, tag);
     check_launch(where);
     return true;
 }
 
-// TMA wants 16-byte aligned bases and row pitches: the contiguous extent of every matrix
-// (K for K-major operands, MN for MN-major ones, N for D) must be a multiple of 8 elements.
-bool eligible(uint64_t M, uint64_t N, uint64_t K, bool a_mn, bool b_mn, const void* a, const void* b, const void* d) {
+}  // namespace
+
+// ---------------------------------------------------------------------------------
+// shared host helpers (declared in tc_ptx.cuh)
+// ---------------------------------------------------------------------------------
+namespace tc {
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+bool make_map_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+namespace {
+struct DeviceState {
+    int* err = nullptr;     // device error word
+    int seq = 0;            // launches made so far (the tag of a launch is seq & 0x7FFFFF, never 0)
+    bool unchecked = false; // a launch was made since the host last read the word
+};
+thread_local DeviceState t_state[64];
+
+DeviceState* current_state() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    return &t_state[dev];
+}
+}  // namespace
+
+int* next_launch_error_word(int* tag) {
+    DeviceState* s = current_state();
+    if (!s) return nullptr;
+    if (!s->err) {
+        if (cudaMalloc(&s->err, sizeof(int)) != cudaSuccess) {
+            cudaGetLastError();
+            s->err = nullptr;
+            return nullptr;
+        }
+        cudaMemset(s->err, 0, sizeof(int));
+    }
+    s->seq = (s->seq + 1) & 0x7FFFFF;
+    if (s->seq == 0) s->seq = 1;
+    s->unchecked = true;
+    *tag = s->seq;
+    return s->err;
+}
+
+}  // namespace tc
+
+// Reads the error word of the calling thread's device.  The copy runs on the legacy stream, i.e. after the work the
+// thread has queued there; call it after a synchronisation point.  A non-zero word sets the sticky status
+// kErrDeviceWait (its detail = the code of the wait that gave up) and is cleared.
+static int collect_tc_status(bool only_if_unchecked) {
+    tc::DeviceState* s = tc::current_state();
+    if (!s || !s->err) return 0;
+    if (only_if_unchecked && !s->unchecked) return 0;
+    int v = 0;
+    if (cudaMemcpy(&v, s->err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    s->unchecked = false;
+    if (v != 0) {
+        set_error(kErrDeviceWait, v & 0xFF, "tc_gemm_kernel");
+        cudaMemset(s->err, 0, sizeof(int));
+    }
+    return v & 0xFF;
+}
+
+// Called by the ABI's own synchronisation points (cuda_memcpy_d2h, cuda_stream_synchronize): costs one 4-byte
+// read-back, and only when a tensor-core launch was made since the last check.
+int tc_status_after_sync() { return collect_tc_status(true); }
+
+}  // namespace mx
+
+// Checks the error word of the calling thread's device after a synchronisation point: 0 = fine, else the code of
+// the bounded wait that ran out (also recorded as the sticky status kErrDeviceWait).
+extern "C" int mx_tc_gemm_status(void) { return mx::collect_tc_status(false); }
+
+// Test hook: writes `value` into the error word the way a kernel of an EARLIER launch would have left it
+// (tag 0 is never handed to a launch), so the surfacing of a stale report can be tested without making a wait run out.
+extern "C" int mx_debug_tc_gemm_poke_status(int value) {
+    int tag = 0;
+    int* err = mx::tc::next_launch_error_word(&tag);
+    if (!err) return -1;
+    const int word = value ? (value & 0xFF) | (0x7FFFFF << 8) : 0;
+    return cudaMemcpy(err, &word, sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess ? 0 : -1;
+}
+
+namespace mx {
+
+// TMA wants 16-byte aligned bases and row pitches: the contiguous extent of every matrix (K for K-major
+// operands, MN for MN-major ones, N for D) must be a multiple of 16 / elem_size elements.
+static bool eligible(size_t es, uint64_t M, uint64_t N, uint64_t K, bool a_mn, bool b_mn, const void* a, const void* b, const void* d) {
+    const uint64_t q = 16 / es;
     if (M == 0 || N == 0 || K == 0) return false;
-    if (N % 8 != 0) return false;
-    if ((a_mn ? M : K) % 8 != 0 || (b_mn ? N : K) % 8 != 0) return false;
+    if (N % q != 0) return false;
+    if ((a_mn ? M : K) % q != 0 || (b_mn ? N : K) % q != 0) return false;
     if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)d) % 16 != 0) return false;
     if (M > 0x7FFFFFFFull || N > 0x7FFFFFFFull || K > 0x7FFFFFFFull) return false;
     if (M * N * K < (1ull << 24)) return false;  // small problems are not worth a persistent launch
     return true;
 }
 
-}  // namespace
-
-// Checks the error word of the calling thread's device after a synchronisation point.
-extern "C" int mx_tc_gemm_status(void) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !t_state[dev].err) return 0;
-    int v = 0;
-    if (cudaMemcpy(&v, t_state[dev].err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (v != 0) {
-        set_error(kErrDeviceWait, v, "tc_gemm_kernel");
-        cudaMemset(t_state[dev].err, 0, sizeof(int));
-    }
-    return v;
-}
-
-// Forward product C[m, n] = sum_k A[m, k] * B[k, n]: can it run on the tensor-core kernel, and with which operand
+// Forward product C[m, n] = sum_k A[m, k] * B[k, n]: can it run on a tensor-core kernel, and with which operand
 // majors?  Unbatched, every operand either dense row-major or the transposed view of a dense matrix.
-struct ForwardClass {
-    const char* A;
-    const char* B;
-    bool a_mn, b_mn;
-    uint64_t m, n, k;
-};
-static bool classify_forward(const MmDesc& d, size_t num_els, const void* x, const void* y, const void* out, ForwardClass& c) {
-    const size_t es = 2;
+static bool classify_forward(const MmDesc& d, size_t es, size_t num_els, const void* x, const void* y, const void* out, TcProduct& c) {
     if (d.out_nd < 2 || d.a_nd < 2 || d.b_nd < 2) return false;
     const uint64_t m = d.m, n = d.n, k = d.k_fwd;
     if (num_els != m * n) return false;  // batched products stay on the SIMT path
@@ -543,28 +487,42 @@ static bool classify_forward(const MmDesc& d, size_t num_els, const void* x, con
     c.m = m;
     c.n = n;
     c.k = k;
-    return eligible(m, n, k, c.a_mn, c.b_mn, c.A, c.B, out);
+    return eligible(es, m, n, k, c.a_mn, c.b_mn, c.A, c.B, out);
 }
 
-bool tc_gemm_bf16_f16(bool is_bf16, const MmDesc& d, int which, size_t num_els, size_t nea, size_t neb, const void* x, const void* y, void* out,
-                      const char* where) {
-    if (which == 0) {
-        ForwardClass c;
-        if (!classify_forward(d, num_els, x, y, out, c)) return false;
-        return launch_gemm(is_bf16, c.A, c.a_mn, c.B, c.b_mn, out, c.m, c.n, c.k, where);
-    }
-    // backward products read g, A and B as dense row-major matrices (strides ignored)
+// which = 0: forward (x = A base, y = B base).  1: grad_a[m, k] = sum_n g[m, n] * B[k, n] (x = g, y = B + offset),
+// reduction over n, both operands K-major.  2: grad_b[k, n] = sum_m A[m, k] * g[m, n] (x = g, y = A + offset),
+// reduction over m, both operands MN-major.  The backward products read g, A and B as dense row-major matrices
+// (strides ignored, crates/maidenx_cpu/src/ops/matmul.rs:196-261).
+bool tc_classify(const MmDesc& d, int which, size_t es, size_t num_els, size_t nea, size_t neb, const void* x, const void* y, const void* out,
+                 TcProduct& c) {
+    if (which == 0) return classify_forward(d, es, num_els, x, y, out, c);
     if (d.out_nd != 2) return false;
     const uint64_t m = d.m, n = d.n, k = d.k_bwd;
     if (d.g_size != m * n || nea != m * k || neb != k * n) return false;
     if (which == 1) {
-        // grad_a[m, k] = sum_n g[m, n] * B[k, n]: reduction over n, both operands K-major
-        if (!eligible(m, k, n, false, false, x, y, out)) return false;
-        return launch_gemm(is_bf16, x, false, y, false, out, m, k, n, where);
+        c.A = static_cast<const char*>(x);
+        c.B = static_cast<const char*>(y);
+        c.a_mn = c.b_mn = false;
+        c.m = m;
+        c.n = k;
+        c.k = n;
+    } else {
+        c.A = static_cast<const char*>(y);
+        c.B = static_cast<const char*>(x);
+        c.a_mn = c.b_mn = true;
+        c.m = k;
+        c.n = n;
+        c.k = m;
     }
-    // grad_b[k, n] = sum_m A[m, k] * g[m, n]: reduction over m, both operands MN-major
-    if (!eligible(k, n, m, true, true, y, x, out)) return false;
-    return launch_gemm(is_bf16, y, true, x, true, out, k, n, m, where);
+    return eligible(es, c.m, c.n, c.k, c.a_mn, c.b_mn, c.A, c.B, out);
+}
+
+bool tc_gemm_bf16_f16(bool is_bf16, const MmDesc& d, int which, size_t num_els, size_t nea, size_t neb, const void* x, const void* y, void* out,
+                      const char* where) {
+    TcProduct c;
+    if (!tc_classify(d, which, 2, num_els, nea, neb, x, y, out, c)) return false;
+    return launch_gemm(is_bf16, c.A, c.a_mn, c.B, c.b_mn, out, c.m, c.n, c.k, where);
 }
 
 }  // namespace mx
@@ -572,16 +530,24 @@ bool tc_gemm_bf16_f16(bool is_bf16, const MmDesc& d, int which, size_t num_els, 
 // Host-only view for tests without a GPU: would cuda_matmul_<bf16|f16> with this HOST metadata and these base
 // addresses run on the tensor-core kernel?  Returns 0 (SIMT kernel) or 1, and the operand majors (0 = K-major,
 // 1 = MN-major) and extents it would be launched with.
-extern "C" int mx_debug_matmul_forward_path(size_t num_els, const size_t* host_metadata, const void* a, const void* b, const void* out, int* a_mn_major,
-                                            int* b_mn_major, size_t* m, size_t* n, size_t* k) {
+static int debug_forward_path(size_t es, size_t num_els, const size_t* host_metadata, const void* a, const void* b, const void* out, int* a_mn_major,
+                              int* b_mn_major, size_t* m, size_t* n, size_t* k) {
     mx::MmDesc d;
     if (!host_metadata || !mx::mm_parse(host_metadata, d)) return 0;
-    mx::ForwardClass c;
-    if (!mx::classify_forward(d, num_els, a, b, out, c)) return 0;
+    mx::TcProduct c;
+    if (!mx::tc_classify(d, 0, es, num_els, 0, 0, a, b, out, c)) return 0;
     if (a_mn_major) *a_mn_major = c.a_mn ? 1 : 0;
     if (b_mn_major) *b_mn_major = c.b_mn ? 1 : 0;
     if (m) *m = c.m;
     if (n) *n = c.n;
     if (k) *k = c.k;
     return 1;
+}
+extern "C" int mx_debug_matmul_forward_path(size_t num_els, const size_t* host_metadata, const void* a, const void* b, const void* out, int* a_mn_major,
+                                            int* b_mn_major, size_t* m, size_t* n, size_t* k) {
+    return debug_forward_path(2, num_els, host_metadata, a, b, out, a_mn_major, b_mn_major, m, n, k);
+}
+extern "C" int mx_debug_matmul_forward_path_f32(size_t num_els, const size_t* host_metadata, const void* a, const void* b, const void* out,
+                                                int* a_mn_major, int* b_mn_major, size_t* m, size_t* n, size_t* k) {
+    return debug_forward_path(4, num_els, host_metadata, a, b, out, a_mn_major, b_mn_major, m, n, k);
 }

@@ -1,0 +1,364 @@
+// Tensor-core path for f32 matmul on sm_100a: tcgen05.mma kind::tf32 with split operands, so the
+// product keeps f32-level accuracy although the tensor core multiplies 11-bit significands.
+//
+// Every f32 operand element x is used as two tf32 values
+//     big   = x with the low 13 significand bits dropped (what the tensor core reads from the raw f32 bits),
+//     small = x - big   (exact in f32; its own low bits are again dropped by the tensor core),
+// and each k-step issues three MMAs into the same TMEM accumulator:
+//     a_small * b_big  +  a_big * b_small  +  a_big * b_big.
+// The dropped term a_small * b_small and the truncation of `small` are each below 2^-21 of |a * b|, so a dot
+// product agrees with f32 arithmetic to a few 1e-7 relative to sum |a_k * b_k| (the stated f32 matmul tolerance is
+// 1e-4); accumulation is in f32 inside the tensor core.
+//
+// One persistent CTA per SM, 320 threads in four roles:
+//   warp 0      TMA producer: raw f32 A [128 x 32] and B [BN x 32] k-blocks (128-byte swizzle rows of 32 floats)
+//               into a ring of STAGES stages;
+//   warps 6-9   splitter: when a stage has landed, read the raw tiles and write the `small` tiles beside them
+//               (element-wise, so the swizzled placement carries over unchanged), then hand the stage to
+//   warp 1      the MMA issuer: 4 k-steps x 3 tcgen05.mma (M128, N = BN, K8) per k-block into one of two TMEM
+//               accumulators; commits the stage back to the producer and a finished accumulator to
+//   warps 2-5   the epilogue: tcgen05.ld 32 columns at a time, swizzled 4 KB staging tile, TMA store of f32.
+// Operands may be K-major ([MN, K] row-major) or MN-major ([K, MN] row-major, loaded as [32 K-rows x 32 MN] boxes),
+// which covers x . W^T, g . W and x^T . g without transposed copies.  No cluster launch, no multicast.
+// Every mbarrier wait is bounded (see tc_ptx.cuh); on expiry all roles fall through to the common exit.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "matmul_tc.cuh"
+#include "tc_ptx.cuh"
+
+namespace mx {
+
+using namespace tc;
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 32;     // CTA tile; BK * 4 bytes = one 128-byte swizzle row
+constexpr int UMMA_K = 8;                      // tf32: 32 bytes of K per instruction
+constexpr int STAGES = 3;
+constexpr int A_TILE = BM * BK * 4;            // 16 KB
+constexpr int B_TILE = BN * BK * 4;
+constexpr int RAW_BYTES = A_TILE + B_TILE;     // what TMA delivers per stage
+constexpr int STAGE_BYTES = 2 * RAW_BYTES;     // [A raw | B raw | A small | B small]
+constexpr int EPI_WARPS = 4, SPLIT_WARPS = 4;
+constexpr int EPI_CHUNK_COLS = 32;             // 32 f32 = 128 bytes per staged row
+constexpr int EPI_STAGE_BYTES = 32 * EPI_CHUNK_COLS * 4;  // 4 KB per warp per buffer
+constexpr int THREADS = 32 * (2 + EPI_WARPS + SPLIT_WARPS);
+constexpr int TMEM_COLS = 2 * BN;              // two f32 accumulators
+constexpr int GROUP_M = 16;
+constexpr int MN_CHUNK_BYTES = BK * 128;       // one [32 K-rows x 32 MN-elements] box
+
+static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM allocations are powers of two");
+static_assert(RAW_BYTES % (16 * 32 * SPLIT_WARPS) == 0, "the splitter moves 16 bytes per thread and step");
+
+struct Smem {
+    static constexpr int stages = 0;
+    static constexpr int epi = stages + STAGES * STAGE_BYTES;
+    static constexpr int bars = epi + EPI_WARPS * 2 * EPI_STAGE_BYTES;
+    static constexpr int total = bars + 256;
+};
+constexpr int SMEM_BYTES = Smem::total + 1024;  // slack for the 1024-byte alignment
+static_assert(SMEM_BYTES <= 232448, "shared memory per CTA");
+
+__host__ __device__ constexpr uint32_t make_idesc_tf32(bool a_mn_major, bool b_mn_major) {
+    uint32_t d = 0;
+    d |= 1u << 4;                               // D format: f32
+    d |= 2u << 7;                               // A format: tf32
+    d |= 2u << 10;                              // B format: tf32
+    d |= (a_mn_major ? 1u : 0u) << 15;
+    d |= (b_mn_major ? 1u : 0u) << 16;
+    d |= (uint32_t)(BN >> 3) << 17;
+    d |= (uint32_t)(BM >> 4) << 24;
+    return d;
+}
+
+struct Params {
+    int tiles_m, tiles_n, num_tiles, num_kb;
+    int a_mn, b_mn;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, const Params& p, int& tm, int& tn) {
+    const int group_size = GROUP_M * p.tiles_n;
+    const int group = tile / group_size;
+    const int first_m = group * GROUP_M;
+    const int rows = min(GROUP_M, p.tiles_m - first_m);
+    const int in_group = tile - group * group_size;
+    tm = first_m + in_group % rows;
+    tn = in_group / rows;
+}
+
+// small = x - (x with its low 13 bits cleared); infinities and NaNs keep all their weight in `big`.
+__device__ __forceinline__ uint32_t small_part(uint32_t bits) {
+    const float x = __uint_as_float(bits);
+    const float big = __uint_as_float(bits & 0xFFFFE000u);
+    const float s = x - big;
+    return (bits & 0x7F800000u) == 0x7F800000u ? 0u : __float_as_uint(s);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+tc_gemm_f32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_d,
+                   Params p, int* err, int tag) {
+    extern __shared__ unsigned char tcf_smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)tcf_smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_base + Smem::bars;
+    // barrier slots (8 bytes each): full[STAGES], split[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then the TMEM base word
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto split_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (3 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (3 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + Smem::bars + 8 * (3 * STAGES + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(split_bar(s), SPLIT_WARPS);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), EPI_WARPS);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                int tm, tn;
+                tile_coords(tile, p, tm, tn);
+                for (int kb = 0; kb < p.num_kb; kb++) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1, err, tag, 1)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(full_bar(stage), RAW_BYTES);
+                    const uint32_t sa = smem_base + Smem::stages + stage * STAGE_BYTES;
+                    const uint32_t sb = sa + A_TILE;
+                    if (!p.a_mn) {
+                        tma_load_2d(sa, &map_a, kb * BK, tm * BM, full_bar(stage));
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < BM / 32; h++) tma_load_2d(sa + h * MN_CHUNK_BYTES, &map_a, tm * BM + h * 32, kb * BK, full_bar(stage));
+                    }
+                    if (!p.b_mn) {
+                        tma_load_2d(sb, &map_b, kb * BK, tn * BN, full_bar(stage));
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < BN / 32; h++) tma_load_2d(sb + h * MN_CHUNK_BYTES, &map_b, tn * BN + h * 32, kb * BK, full_bar(stage));
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_tf32(p.a_mn != 0, p.b_mn != 0);
+            const uint32_t a_lbo = p.a_mn ? MN_CHUNK_BYTES : 16, b_lbo = p.b_mn ? MN_CHUNK_BYTES : 16;
+            // K-major: 8 floats further along the 128-byte row; MN-major: the next group of eight K-rows
+            const uint64_t a_kstep = p.a_mn ? (1024 >> 4) : (32 >> 4), b_kstep = p.b_mn ? (1024 >> 4) : (32 >> 4);
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, err, tag, 2)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+                for (int kb = 0; kb < p.num_kb; kb++) {
+                    // the raw tiles (TMA) and the small tiles (splitter) are both operands
+                    if (!mbar_wait(full_bar(stage), phase, err, tag, 3) || !mbar_wait(split_bar(stage), phase, err, tag, 6)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t s0 = smem_base + Smem::stages + stage * STAGE_BYTES;
+                    const uint64_t a_big = smem_desc_sw128(s0, a_lbo, 1024);
+                    const uint64_t b_big = smem_desc_sw128(s0 + A_TILE, b_lbo, 1024);
+                    const uint64_t a_small = smem_desc_sw128(s0 + RAW_BYTES, a_lbo, 1024);
+                    const uint64_t b_small = smem_desc_sw128(s0 + RAW_BYTES + A_TILE, b_lbo, 1024);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        umma_tf32(d_tmem, a_small + a_kstep * k, b_big + b_kstep * k, idesc, (kb | k) != 0);
+                        umma_tf32(d_tmem, a_big + a_kstep * k, b_small + b_kstep * k, idesc, 1);
+                        umma_tf32(d_tmem, a_big + a_kstep * k, b_big + b_kstep * k, idesc, 1);
+                    }
+                    umma_commit(empty_bar(stage));
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(tfull_bar(acc));
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+            }
+        }
+    } else if (warp < 2 + EPI_WARPS) {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;  // TMEM lanes [32 * quarter, 32 * quarter + 32)
+        const int ew = warp - 2;
+        unsigned char* stage_buf = smem + Smem::epi + ew * 2 * EPI_STAGE_BYTES;
+        int acc = 0, buf = 0;
+        uint32_t acc_phase = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+            int tm, tn;
+            tile_coords(tile, p, tm, tn);
+            const bool ready = mbar_wait(tfull_bar(acc), acc_phase, err, tag, 4);
+            if (!__all_sync(0xFFFFFFFFu, ready)) break;
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / EPI_CHUNK_COLS; c++) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(t_row + c * EPI_CHUNK_COLS, v);
+                tmem_ld_wait();
+                if (c == BN / EPI_CHUNK_COLS - 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(acc));
+                }
+                if (lane == 0) tma_store_wait_read<1>();
+                __syncwarp();
+                unsigned char* dst = stage_buf + buf * EPI_STAGE_BYTES + lane * 128;  // row `lane` of the 32 x 32 tile
+#pragma unroll
+                for (int j = 0; j < 8; j++)  // eight 16-byte chunks per row, XOR-swizzled by the row index
+                    *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&map_d, smem_u32(stage_buf + buf * EPI_STAGE_BYTES), tn * BN + c * EPI_CHUNK_COLS, tm * BM + quarter * 32);
+                    tma_store_commit();
+                }
+                buf ^= 1;
+            }
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1;
+            }
+        }
+        if (lane == 0) tma_store_wait_all();
+    } else {
+        // ------------------------------------------------------------ splitter (warps 6..9)
+        const int t = threadIdx.x - 32 * (2 + EPI_WARPS);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < p.num_kb; kb++) {
+                const bool landed = mbar_wait(full_bar(stage), phase, err, tag, 5);
+                if (!__all_sync(0xFFFFFFFFu, landed)) {
+                    ok = false;
+                    break;
+                }
+                const uint4* raw = reinterpret_cast<const uint4*>(smem + Smem::stages + stage * STAGE_BYTES);
+                uint4* small = reinterpret_cast<uint4*>(smem + Smem::stages + stage * STAGE_BYTES + RAW_BYTES);
+                constexpr int STEPS = RAW_BYTES / 16 / (32 * SPLIT_WARPS);
+#pragma unroll 8
+                for (int i = 0; i < STEPS; i++) {
+                    const uint4 q = raw[t + i * 32 * SPLIT_WARPS];
+                    small[t + i * 32 * SPLIT_WARPS] = make_uint4(small_part(q.x), small_part(q.y), small_part(q.z), small_part(q.w));
+                }
+                fence_proxy_async_smem();  // the tensor core reads these through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(split_bar(stage));
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+        }
+    }
+
+    // common exit: TMEM is released by the warp that allocated it, after everyone is done with it
+    tc_fence_before();
+    __syncthreads();
+    if (tc_err_mine(err, tag)) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 4000000ll) {
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+bool opt_in_shared_memory() {
+    static std::mutex mu;
+    static bool done[64] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done[dev]) {
+        if (cudaFuncSetAttribute(tc_gemm_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        done[dev] = true;
+    }
+    return true;
+}
+
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    return make_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, rows, cols, box_rows);
+}
+
+// D[M,N] = sum_k Aop[m,k] * Bop[n,k]; K-major operand = dense row-major [MN, K], MN-major = dense row-major [K, MN].
+bool launch(const void* A, bool a_mn, const void* B, bool b_mn, void* D, uint64_t M, uint64_t N, uint64_t K, const char* where) {
+    if (!opt_in_shared_memory()) return false;
+    int tag = 0;
+    int* err = next_launch_error_word(&tag);
+    if (!err) return false;
+    CUtensorMap ma, mb, md;
+    const bool oka = a_mn ? make_map(&ma, A, K, M, BK) : make_map(&ma, A, M, K, BM);
+    const bool okb = b_mn ? make_map(&mb, B, K, N, BK) : make_map(&mb, B, N, K, BN);
+    if (!oka || !okb || !make_map(&md, D, M, N, 32)) return false;
+    Params p;
+    p.tiles_m = (int)((M + BM - 1) / BM);
+    p.tiles_n = (int)((N + BN - 1) / BN);
+    p.num_tiles = p.tiles_m * p.tiles_n;
+    p.num_kb = (int)((K + BK - 1) / BK);
+    p.a_mn = a_mn ? 1 : 0;
+    p.b_mn = b_mn ? 1 : 0;
+    int grid = sm_count();
+    if (ctx().gemm_sm_limit > 0 && ctx().gemm_sm_limit < grid) grid = ctx().gemm_sm_limit;
+    if (grid > p.num_tiles) grid = p.num_tiles;
+    tc_gemm_f32_kernel<<<grid, THREADS, SMEM_BYTES, ctx().stream>>>(ma, mb, md, p, err, tag);
+    check_launch(where);
+    return true;
+}
+
+}  // namespace
+
+bool tc_gemm_f32(const MmDesc& d, int which, size_t num_els, size_t nea, size_t neb, const void* x, const void* y, void* out, const char* where) {
+    TcProduct c;
+    if (!tc_classify(d, which, 4, num_els, nea, neb, x, y, out, c)) return false;
+    return launch(c.A, c.a_mn, c.B, c.b_mn, out, c.m, c.n, c.k, where);
+}
+
+}  // namespace mx

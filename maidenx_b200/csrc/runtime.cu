@@ -22,6 +22,8 @@
 
 namespace mx {
 
+int tc_status_after_sync();  // matmul_tc.cu
+
 namespace {
 constexpr size_t kSideTableMaxBytes = 2048;
 
@@ -248,7 +250,15 @@ int cuda_memcpy_h2d(void* dst, const void* src, size_t size) {
     return (int)e;
 }
 
-int cuda_memcpy_d2h(void* dst, const void* src, size_t size) { return (int)cudaMemcpy(dst, src, size, cudaMemcpyDeviceToHost); }
+// The reference's callers learn of device-side trouble only through the return codes of the copies and
+// synchronisations that follow an op (the ops return void).  A tensor-core kernel whose bounded waits ran out is
+// therefore reported here: sticky status kErrDeviceWait and a non-zero return (cudaErrorLaunchTimeout).
+static int surface_device_waits(int e) {
+    if (e == (int)cudaSuccess && mx::tc_status_after_sync() > 0) return (int)cudaErrorLaunchTimeout;
+    return e;
+}
+
+int cuda_memcpy_d2h(void* dst, const void* src, size_t size) { return surface_device_waits((int)cudaMemcpy(dst, src, size, cudaMemcpyDeviceToHost)); }
 
 int cuda_memcpy_d2d(void* dst, const void* src, size_t size) {
     side_table_forget(dst);
@@ -259,7 +269,7 @@ int cuda_set_device(int device_id) { return (int)cudaSetDevice(device_id); }
 int cuda_get_device(int* device_id) { return (int)cudaGetDevice(device_id); }
 int cuda_stream_create(void** stream) { return (int)cudaStreamCreate(reinterpret_cast<cudaStream_t*>(stream)); }
 int cuda_stream_destroy(void* stream) { return (int)cudaStreamDestroy(reinterpret_cast<cudaStream_t>(stream)); }
-int cuda_stream_synchronize(void* stream) { return (int)cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)); }
+int cuda_stream_synchronize(void* stream) { return surface_device_waits((int)cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream))); }
 
 int cuda_pointer_get_attributes(MxCudaPointerAttributes* attributes, const void* ptr) {
     cudaPointerAttributes a;

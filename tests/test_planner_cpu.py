@@ -77,12 +77,13 @@ def test_reduction_layouts_take_their_kernels():
     assert red_plan([64, 32, 1, 64, 64, 1, 0], 2, 1, 2048)[0] == SCATTER
 
 
-def mm_path(meta, num_els, a=BASE, b=BASE + (1 << 32), out=BASE + (2 << 32)):
+def mm_path(meta, num_els, a=BASE, b=BASE + (1 << 32), out=BASE + (2 << 32), f32=False):
     lib = _lib.load()
     m_ = np.asarray(meta, dtype=np.uint64)
     amn, bmn = ctypes.c_int(-1), ctypes.c_int(-1)
     M, N, K = ctypes.c_size_t(), ctypes.c_size_t(), ctypes.c_size_t()
-    tc = lib.mx_debug_matmul_forward_path(num_els, m_.ctypes.data, a, b, out, ctypes.byref(amn), ctypes.byref(bmn), ctypes.byref(M),
+    fn = lib.mx_debug_matmul_forward_path_f32 if f32 else lib.mx_debug_matmul_forward_path
+    tc = fn(num_els, m_.ctypes.data, a, b, out, ctypes.byref(amn), ctypes.byref(bmn), ctypes.byref(M),
                                           ctypes.byref(N), ctypes.byref(K))
     return tc, amn.value, bmn.value, M.value, N.value, K.value
 
@@ -103,3 +104,14 @@ def test_products_the_tensor_core_kernel_does_not_take():
     assert mm_path([2, 2, 2, 512, 512, 512, 512, 512, 512, 512, 1, 512, 1, 1, 0], 512 * 512)[0] == 0     # offset 1: base not 16-byte aligned
     assert mm_path([2, 2, 2, 512, 512, 512, 512, 512, 512, 1024, 2, 512, 1, 0, 0], 512 * 512)[0] == 0    # A with a stride of 2 along k
     assert mm_path([3, 3, 3, 4, 512, 512, 4, 512, 512, 4, 512, 512, 262144, 512, 1, 262144, 512, 1, 0, 0], 4 * 512 * 512)[0] == 0  # batched
+
+
+def test_f32_products_take_the_split_tf32_kernel_when_rows_are_16_byte_multiples():
+    """f32: the contiguous extent of each matrix must be a multiple of 4 elements (16 bytes for TMA), not 8."""
+    D = 8192
+    assert mm_path([2, 2, 2, 2048, D, 2048, D, D, D, D, 1, 1, D, 0, 0], 2048 * D, f32=True) == (1, 0, 0, 2048, D, D)
+    # conv forward at the benchmark shape: cols [200704, 2304] . weight^T view of [256, 2304]
+    assert mm_path([2, 2, 2, 200704, 256, 200704, 2304, 2304, 256, 2304, 1, 1, 2304, 0, 0], 200704 * 256, f32=True) == (1, 0, 0, 200704, 256, 2304)
+    assert mm_path([2, 2, 2, 512, 516, 512, 512, 512, 516, 512, 1, 516, 1, 0, 0], 512 * 516, f32=True)[0] == 1   # 516 = 4 * 129
+    assert mm_path([2, 2, 2, 512, 514, 512, 512, 512, 514, 512, 1, 514, 1, 0, 0], 512 * 514, f32=True)[0] == 0
+    assert mm_path([2, 2, 2, 64, 64, 64, 64, 64, 64, 64, 1, 64, 1, 0, 0], 64 * 64, f32=True)[0] == 0             # small: SIMT, bit-exact order
