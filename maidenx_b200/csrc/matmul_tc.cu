@@ -78,11 +78,15 @@ __host__ __device__ constexpr uint32_t make_idesc(bool is_bf16, bool a_mn_major,
 struct TcParams {
     int M, N, K;
     int tiles_m, tiles_n, num_tiles, num_kb;
+    int tiles_per_batch;   // tiles_m * tiles_n; num_tiles = batch * tiles_per_batch
+    int a_batched, b_batched;  // 0: the operand is one matrix shared by every batch (third TMA coordinate stays 0)
     int is_bf16;
     int a_mn, b_mn;  // operand is MN-major in global memory ([K, MN] row-major) instead of K-major ([MN, K])
 };
 
-__device__ __forceinline__ void tile_coords(int tile, const TcParams& p, int& tm, int& tn) {
+__device__ __forceinline__ void tile_coords(int tile, const TcParams& p, int& tm, int& tn, int& tb) {
+    tb = tile / p.tiles_per_batch;
+    tile -= tb * p.tiles_per_batch;
     // sweep GROUP_M row-tiles for each column tile before moving to the next column tile
     const int group_size = GROUP_M * p.tiles_n;
     const int group = tile / group_size;
@@ -146,8 +150,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-                int tm, tn;
-                tile_coords(tile, p, tm, tn);
+                int tm, tn, tb;
+                tile_coords(tile, p, tm, tn, tb);
+                const int za = p.a_batched ? tb : 0, zb = p.b_batched ? tb : 0;
                 for (int kb = 0; kb < p.num_kb; kb++) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1, err, tag, 1)) {
                         ok = false;
@@ -157,16 +162,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t sa = smem_base + SmemLayout::a + stage * A_STAGE_BYTES;
                     const uint32_t sb = smem_base + SmemLayout::b + stage * B_STAGE_BYTES;
                     if (!p.a_mn) {
-                        tma_load_2d(sa, &map_a, kb * BK, tm * BM, full_bar(stage));
+                        tma_load_3d(sa, &map_a, kb * BK, tm * BM, za, full_bar(stage));
                     } else {
 #pragma unroll
-                        for (int h = 0; h < BM / 64; h++) tma_load_2d(sa + h * MN_CHUNK_BYTES, &map_a, tm * BM + h * 64, kb * BK, full_bar(stage));
+                        for (int h = 0; h < BM / 64; h++) tma_load_3d(sa + h * MN_CHUNK_BYTES, &map_a, tm * BM + h * 64, kb * BK, za, full_bar(stage));
                     }
                     if (!p.b_mn) {
-                        tma_load_2d(sb, &map_b, kb * BK, tn * BN, full_bar(stage));
+                        tma_load_3d(sb, &map_b, kb * BK, tn * BN, zb, full_bar(stage));
                     } else {
 #pragma unroll
-                        for (int h = 0; h < BN / 64; h++) tma_load_2d(sb + h * MN_CHUNK_BYTES, &map_b, tn * BN + h * 64, kb * BK, full_bar(stage));
+                        for (int h = 0; h < BN / 64; h++) tma_load_3d(sb + h * MN_CHUNK_BYTES, &map_b, tn * BN + h * 64, kb * BK, zb, full_bar(stage));
                     }
                     if (++stage == STAGES) {
                         stage = 0;
@@ -221,8 +226,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int acc = 0, buf = 0;
         uint32_t acc_phase = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
-            int tm, tn;
-            tile_coords(tile, p, tm, tn);
+            int tm, tn, tb;
+            tile_coords(tile, p, tm, tn, tb);
             // the TMEM loads below are warp-collective: leave the loop only as a whole warp
             const bool ready = mbar_wait(tfull_bar(acc), acc_phase, err, tag, 4);
             if (!__all_sync(0xFFFFFFFFu, ready)) break;
@@ -257,7 +262,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    tma_store_2d(&map_d, smem_u32(stage_buf + buf * EPI_STAGE_BYTES), tn * BN + c * EPI_CHUNK_COLS, tm * BM + quarter * 32);
+                    tma_store_3d(&map_d, smem_u32(stage_buf + buf * EPI_STAGE_BYTES), tn * BN + c * EPI_CHUNK_COLS, tm * BM + quarter * 32, tb);
                     tma_store_commit();
                 }
                 buf ^= 1;
@@ -291,8 +296,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // host side
 // ---------------------------------------------------------------------------------
 // [rows, cols] row-major 16-bit matrix, box = box_rows x 64 columns, 128-byte swizzle
-bool make_map(CUtensorMap* map, bool is_bf16, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-    return make_map_2d(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, rows, cols, box_rows);
+bool make_map(CUtensorMap* map, bool is_bf16, const void* base, uint64_t rows, uint64_t cols, uint64_t batch, uint64_t batch_stride, uint32_t box_rows) {
+    return make_map_3d(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, rows, cols, batch, batch_stride, box_rows);
 }
 
 bool opt_in_shared_memory() {
@@ -313,22 +318,28 @@ bool opt_in_shared_memory() {
 
 // D[M,N] = sum_k Aop[m,k] * Bop[n,k].  A K-major operand is a dense row-major [MN, K] matrix, an
 // MN-major operand a dense row-major [K, MN] matrix; D is dense row-major [M, N].
-bool launch_gemm(bool is_bf16, const void* A, bool a_mn, const void* B, bool b_mn, void* D, uint64_t M, uint64_t N, uint64_t K, const char* where) {
+bool launch_gemm(bool is_bf16, const TcProduct& c, void* D, const char* where) {
+    const void *A = c.A, *B = c.B;
+    const bool a_mn = c.a_mn, b_mn = c.b_mn;
+    const uint64_t M = c.m, N = c.n, K = c.k, batch = c.batch;
     if (!opt_in_shared_memory()) return false;
     int tag = 0;
     int* err = next_launch_error_word(&tag);
     if (!err) return false;
     CUtensorMap ma, mb, md;
-    const bool oka = a_mn ? make_map(&ma, is_bf16, A, K, M, 64) : make_map(&ma, is_bf16, A, M, K, BM);
-    const bool okb = b_mn ? make_map(&mb, is_bf16, B, K, N, 64) : make_map(&mb, is_bf16, B, N, K, BN);
-    if (!oka || !okb || !make_map(&md, is_bf16, D, M, N, 32)) return false;
+    const bool oka = a_mn ? make_map(&ma, is_bf16, A, K, M, batch, c.a_bs, 64) : make_map(&ma, is_bf16, A, M, K, batch, c.a_bs, BM);
+    const bool okb = b_mn ? make_map(&mb, is_bf16, B, K, N, batch, c.b_bs, 64) : make_map(&mb, is_bf16, B, N, K, batch, c.b_bs, BN);
+    if (!oka || !okb || !make_map(&md, is_bf16, D, M, N, batch, M * N, 32)) return false;
     TcParams p;
     p.M = (int)M;
     p.N = (int)N;
     p.K = (int)K;
     p.tiles_m = (int)((M + BM - 1) / BM);
     p.tiles_n = (int)((N + BN - 1) / BN);
-    p.num_tiles = p.tiles_m * p.tiles_n;
+    p.tiles_per_batch = p.tiles_m * p.tiles_n;
+    p.num_tiles = (int)batch * p.tiles_per_batch;
+    p.a_batched = (batch > 1 && c.a_bs != 0) ? 1 : 0;
+    p.b_batched = (batch > 1 && c.b_bs != 0) ? 1 : 0;
     p.num_kb = (int)((K + BK - 1) / BK);
     p.is_bf16 = is_bf16 ? 1 : 0;
     p.a_mn = a_mn ? 1 : 0;
@@ -368,6 +379,20 @@ bool make_map_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, con
     cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+bool make_map_3d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t rows, uint64_t cols, uint64_t batch,
+                 uint64_t batch_stride, uint32_t box_rows) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return false;
+    const bool bcast = batch_stride == 0 || batch <= 1;
+    cuuint64_t dims[3] = {cols, rows, bcast ? 1 : batch};
+    cuuint64_t strides[2] = {cols * (uint64_t)elem_bytes, (bcast ? rows * cols : batch_stride) * (uint64_t)elem_bytes};
+    cuuint32_t box[3] = {(cuuint32_t)(128 / elem_bytes), box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, type, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
@@ -448,14 +473,16 @@ namespace mx {
 
 // TMA wants 16-byte aligned bases and row pitches: the contiguous extent of every matrix (K for K-major
 // operands, MN for MN-major ones, N for D) must be a multiple of 16 / elem_size elements.
-static bool eligible(size_t es, uint64_t M, uint64_t N, uint64_t K, bool a_mn, bool b_mn, const void* a, const void* b, const void* d) {
+static bool eligible(size_t es, uint64_t M, uint64_t N, uint64_t K, uint64_t batch, bool a_mn, bool b_mn, const void* a, const void* b, const void* d) {
     const uint64_t q = 16 / es;
     if (M == 0 || N == 0 || K == 0) return false;
     if (N % q != 0) return false;
     if ((a_mn ? M : K) % q != 0 || (b_mn ? N : K) % q != 0) return false;
     if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)d) % 16 != 0) return false;
     if (M > 0x7FFFFFFFull || N > 0x7FFFFFFFull || K > 0x7FFFFFFFull) return false;
-    if (M * N * K < (1ull << 24)) return false;  // small problems are not worth a persistent launch
+    if (batch > 1 && (M * N) % q != 0) return false;  // every batch's output starts on a 16-byte boundary
+    if (batch * M * N * K < (1ull << 24)) return false;  // small problems are not worth a persistent launch
+    if (batch * ((M + 127) / 128) * ((N + 127) / 128) > 0x3FFFFFFFull) return false;
     return true;
 }
 
@@ -464,30 +491,45 @@ static bool eligible(size_t es, uint64_t M, uint64_t N, uint64_t K, bool a_mn, b
 static bool classify_forward(const MmDesc& d, size_t es, size_t num_els, const void* x, const void* y, const void* out, TcProduct& c) {
     if (d.out_nd < 2 || d.a_nd < 2 || d.b_nd < 2) return false;
     const uint64_t m = d.m, n = d.n, k = d.k_fwd;
-    if (num_els != m * n) return false;  // batched products stay on the SIMT path
+    if (m == 0 || n == 0 || num_els % (m * n) != 0) return false;
+    const uint64_t batch = num_els / (m * n);
+    // batched: rank-3 operands only (for higher ranks the reference indexes the batch through strides[0] alone)
+    if (batch > 1 && !(d.out_nd == 3 && d.a_nd == 3 && d.b_nd == 3)) return false;
+    if (batch > 0x7FFFull) return false;
     c.A = static_cast<const char*>(x) + d.a_off * es;
     c.B = static_cast<const char*>(y) + d.b_off * es;
     bool a_kmajor, a_mnmajor, b_kmajor, b_mnmajor;
     if (d.a_cont && d.b_cont) {
-        // the reference's contiguous branch: A is [m, k], B is [k, n], both dense
+        // the reference's contiguous branch: A is [batch, m, k], B is [batch, k, n], both dense
         a_kmajor = true;
         a_mnmajor = false;
         b_kmajor = false;
         b_mnmajor = true;
+        c.a_bs = (int64_t)(m * k);
+        c.b_bs = (int64_t)(k * n);
     } else {
-        // strided branch: A[m * as1 + k * as2], B[k * bs1 + n * bs2]
+        // strided branch: A[b * as0 + m * as1 + k * as2], B[b * bs0 + k * bs1 + n * bs2]
         a_kmajor = d.a_strides[2] == 1 && d.a_strides[1] == (int64_t)k;
         a_mnmajor = d.a_strides[1] == 1 && d.a_strides[2] == (int64_t)m;  // transposed view of a dense [k, m] matrix
         b_kmajor = d.b_strides[1] == 1 && d.b_strides[2] == (int64_t)k;   // transposed view of a dense [n, k] matrix
         b_mnmajor = d.b_strides[2] == 1 && d.b_strides[1] == (int64_t)n;  // dense [k, n]
+        c.a_bs = batch > 1 ? d.a_strides[0] : 0;                          // 0: one matrix broadcast over the batch
+        c.b_bs = batch > 1 ? d.b_strides[0] : 0;
     }
     if (!(a_kmajor || a_mnmajor) || !(b_kmajor || b_mnmajor)) return false;
+    if (batch > 1) {
+        // a batch stride is a TMA stride: a multiple of 16 bytes, and whole matrices apart (no overlap tricks)
+        const int64_t q = (int64_t)(16 / es);
+        if (c.a_bs < 0 || c.b_bs < 0 || c.a_bs % q != 0 || c.b_bs % q != 0) return false;
+        if ((c.a_bs != 0 && c.a_bs < (int64_t)(m * k)) || (c.b_bs != 0 && c.b_bs < (int64_t)(k * n))) return false;
+    }
     c.a_mn = !a_kmajor;
     c.b_mn = !b_kmajor;
     c.m = m;
     c.n = n;
     c.k = k;
-    return eligible(es, m, n, k, c.a_mn, c.b_mn, c.A, c.B, out);
+    c.batch = batch;
+    return eligible(es, m, n, k, batch, c.a_mn, c.b_mn, c.A, c.B, out);
 }
 
 // which = 0: forward (x = A base, y = B base).  1: grad_a[m, k] = sum_n g[m, n] * B[k, n] (x = g, y = B + offset),
@@ -500,6 +542,8 @@ bool tc_classify(const MmDesc& d, int which, size_t es, size_t num_els, size_t n
     if (d.out_nd != 2) return false;
     const uint64_t m = d.m, n = d.n, k = d.k_bwd;
     if (d.g_size != m * n || nea != m * k || neb != k * n) return false;
+    c.batch = 1;
+    c.a_bs = c.b_bs = 0;
     if (which == 1) {
         c.A = static_cast<const char*>(x);
         c.B = static_cast<const char*>(y);
@@ -515,14 +559,14 @@ bool tc_classify(const MmDesc& d, int which, size_t es, size_t num_els, size_t n
         c.n = n;
         c.k = m;
     }
-    return eligible(es, c.m, c.n, c.k, c.a_mn, c.b_mn, c.A, c.B, out);
+    return eligible(es, c.m, c.n, c.k, 1, c.a_mn, c.b_mn, c.A, c.B, out);
 }
 
 bool tc_gemm_bf16_f16(bool is_bf16, const MmDesc& d, int which, size_t num_els, size_t nea, size_t neb, const void* x, const void* y, void* out,
                       const char* where) {
     TcProduct c;
     if (!tc_classify(d, which, 2, num_els, nea, neb, x, y, out, c)) return false;
-    return launch_gemm(is_bf16, c.A, c.a_mn, c.B, c.b_mn, out, c.m, c.n, c.k, where);
+    return launch_gemm(is_bf16, c, out, where);
 }
 
 }  // namespace mx
@@ -541,7 +585,7 @@ static int debug_forward_path(size_t es, size_t num_els, const size_t* host_meta
     if (m) *m = c.m;
     if (n) *n = c.n;
     if (k) *k = c.k;
-    return 1;
+    return (int)c.batch;
 }
 extern "C" int mx_debug_matmul_forward_path(size_t num_els, const size_t* host_metadata, const void* a, const void* b, const void* out, int* a_mn_major,
                                             int* b_mn_major, size_t* m, size_t* n, size_t* k) {

@@ -14,6 +14,8 @@ struct TcProduct {
     const char* B;
     bool a_mn, b_mn;
     uint64_t m, n, k;
+    uint64_t batch;      // independent products; D is dense [batch, m, n]
+    int64_t a_bs, b_bs;  // elements between consecutive batches of each operand; 0 = one matrix shared by all
 };
 // which: 0 forward, 1 grad_a, 2 grad_b (see matmul_tc.cu); elem_size in bytes.
 bool tc_classify(const MmDesc& d, int which, size_t elem_size, size_t num_els, size_t nea, size_t neb, const void* x, const void* y, const void* out,

@@ -8,7 +8,14 @@
 //     a_small * b_big  +  a_big * b_small  +  a_big * b_big.
 // The dropped term a_small * b_small and the truncation of `small` are each below 2^-21 of |a * b|, so a dot
 // product agrees with f32 arithmetic to a few 1e-7 relative to sum |a_k * b_k| (the stated f32 matmul tolerance is
-// 1e-4); accumulation is in f32 inside the tensor core.
+// 1e-4).
+//
+// Two-level accumulation.  The tensor core adds each instruction's products into the f32 accumulator with
+// truncation, which pulls a long running sum towards zero by about half an ulp per instruction (measured:
+// -6e-6 relative after 147 instructions); over K = 8192 that would eat the whole 1e-4 budget.  So the TMEM
+// accumulator only ever holds the sum of CHUNK_KB k-blocks (256 values of K): the epilogue warps drain it after
+// every chunk and keep the running total in registers, added with round-to-nearest, while the tensor core fills
+// the other accumulator.  The truncation then acts on short partial sums of random sign instead of on the total.
 //
 // One persistent CTA per SM, 320 threads in four roles:
 //   warp 0      TMA producer: raw f32 A [128 x 32] and B [BN x 32] k-blocks (128-byte swizzle rows of 32 floats)
@@ -16,8 +23,10 @@
 //   warps 6-9   splitter: when a stage has landed, read the raw tiles and write the `small` tiles beside them
 //               (element-wise, so the swizzled placement carries over unchanged), then hand the stage to
 //   warp 1      the MMA issuer: 4 k-steps x 3 tcgen05.mma (M128, N = BN, K8) per k-block into one of two TMEM
-//               accumulators; commits the stage back to the producer and a finished accumulator to
-//   warps 2-5   the epilogue: tcgen05.ld 32 columns at a time, swizzled 4 KB staging tile, TMA store of f32.
+//               accumulators, switching accumulator every CHUNK_KB k-blocks; commits the stage back to the
+//               producer and each finished chunk to
+//   warps 2-5   the epilogue: per chunk tcgen05.ld of the warp's 32 rows x BN columns, added into BN registers per
+//               thread; after the tile's last chunk the totals go through a swizzled 4 KB staging tile to TMA stores.
 // Operands may be K-major ([MN, K] row-major) or MN-major ([K, MN] row-major, loaded as [32 K-rows x 32 MN] boxes),
 // which covers x . W^T, g . W and x^T . g without transposed copies.  No cluster launch, no multicast.
 // Every mbarrier wait is bounded (see tc_ptx.cuh); on expiry all roles fall through to the common exit.
@@ -47,6 +56,7 @@ constexpr int EPI_STAGE_BYTES = 32 * EPI_CHUNK_COLS * 4;  // 4 KB per warp per b
 constexpr int THREADS = 32 * (2 + EPI_WARPS + SPLIT_WARPS);
 constexpr int TMEM_COLS = 2 * BN;              // two f32 accumulators
 constexpr int GROUP_M = 16;
+constexpr int CHUNK_KB = 8;                    // k-blocks summed inside TMEM before the registers take over
 constexpr int MN_CHUNK_BYTES = BK * 128;       // one [32 K-rows x 32 MN-elements] box
 
 static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM allocations are powers of two");
@@ -75,10 +85,14 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(bool a_mn_major, bool b_m
 
 struct Params {
     int tiles_m, tiles_n, num_tiles, num_kb;
+    int tiles_per_batch;       // tiles_m * tiles_n; num_tiles = batch * tiles_per_batch
+    int a_batched, b_batched;  // 0: the operand is one matrix shared by every batch (third TMA coordinate stays 0)
     int a_mn, b_mn;
 };
 
-__device__ __forceinline__ void tile_coords(int tile, const Params& p, int& tm, int& tn) {
+__device__ __forceinline__ void tile_coords(int tile, const Params& p, int& tm, int& tn, int& tb) {
+    tb = tile / p.tiles_per_batch;
+    tile -= tb * p.tiles_per_batch;
     const int group_size = GROUP_M * p.tiles_n;
     const int group = tile / group_size;
     const int first_m = group * GROUP_M;
@@ -88,12 +102,14 @@ __device__ __forceinline__ void tile_coords(int tile, const Params& p, int& tm, 
     tn = in_group / rows;
 }
 
-// small = x - (x with its low 13 bits cleared); infinities and NaNs keep all their weight in `big`.
+// small = x - (x with its low 13 bits cleared), itself rounded to the 11 significant bits the tensor core will read
+// (rounding here instead of letting the hardware truncate keeps the error of the split unbiased); infinities and
+// NaNs keep all their weight in `big`.
 __device__ __forceinline__ uint32_t small_part(uint32_t bits) {
     const float x = __uint_as_float(bits);
     const float big = __uint_as_float(bits & 0xFFFFE000u);
-    const float s = x - big;
-    return (bits & 0x7F800000u) == 0x7F800000u ? 0u : __float_as_uint(s);
+    const uint32_t s = (__float_as_uint(x - big) + 0x1000u) & 0xFFFFE000u;
+    return (bits & 0x7F800000u) == 0x7F800000u ? 0u : s;
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -141,8 +157,9 @@ tc_gemm_f32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-                int tm, tn;
-                tile_coords(tile, p, tm, tn);
+                int tm, tn, tb;
+                tile_coords(tile, p, tm, tn, tb);
+                const int za = p.a_batched ? tb : 0, zb = p.b_batched ? tb : 0;
                 for (int kb = 0; kb < p.num_kb; kb++) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1, err, tag, 1)) {
                         ok = false;
@@ -152,16 +169,16 @@ tc_gemm_f32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     const uint32_t sa = smem_base + Smem::stages + stage * STAGE_BYTES;
                     const uint32_t sb = sa + A_TILE;
                     if (!p.a_mn) {
-                        tma_load_2d(sa, &map_a, kb * BK, tm * BM, full_bar(stage));
+                        tma_load_3d(sa, &map_a, kb * BK, tm * BM, za, full_bar(stage));
                     } else {
 #pragma unroll
-                        for (int h = 0; h < BM / 32; h++) tma_load_2d(sa + h * MN_CHUNK_BYTES, &map_a, tm * BM + h * 32, kb * BK, full_bar(stage));
+                        for (int h = 0; h < BM / 32; h++) tma_load_3d(sa + h * MN_CHUNK_BYTES, &map_a, tm * BM + h * 32, kb * BK, za, full_bar(stage));
                     }
                     if (!p.b_mn) {
-                        tma_load_2d(sb, &map_b, kb * BK, tn * BN, full_bar(stage));
+                        tma_load_3d(sb, &map_b, kb * BK, tn * BN, zb, full_bar(stage));
                     } else {
 #pragma unroll
-                        for (int h = 0; h < BN / 32; h++) tma_load_2d(sb + h * MN_CHUNK_BYTES, &map_b, tn * BN + h * 32, kb * BK, full_bar(stage));
+                        for (int h = 0; h < BN / 32; h++) tma_load_3d(sb + h * MN_CHUNK_BYTES, &map_b, tn * BN + h * 32, kb * BK, zb, full_bar(stage));
                     }
                     if (++stage == STAGES) {
                         stage = 0;
@@ -181,38 +198,44 @@ tc_gemm_f32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, err, tag, 2)) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
-                for (int kb = 0; kb < p.num_kb; kb++) {
-                    // the raw tiles (TMA) and the small tiles (splitter) are both operands
-                    if (!mbar_wait(full_bar(stage), phase, err, tag, 3) || !mbar_wait(split_bar(stage), phase, err, tag, 6)) {
+                for (int kb0 = 0; kb0 < p.num_kb && ok; kb0 += CHUNK_KB) {
+                    if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, err, tag, 2)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t s0 = smem_base + Smem::stages + stage * STAGE_BYTES;
-                    const uint64_t a_big = smem_desc_sw128(s0, a_lbo, 1024);
-                    const uint64_t b_big = smem_desc_sw128(s0 + A_TILE, b_lbo, 1024);
-                    const uint64_t a_small = smem_desc_sw128(s0 + RAW_BYTES, a_lbo, 1024);
-                    const uint64_t b_small = smem_desc_sw128(s0 + RAW_BYTES + A_TILE, b_lbo, 1024);
+                    const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+                    const int kb1 = min(kb0 + CHUNK_KB, p.num_kb);
+                    for (int kb = kb0; kb < kb1; kb++) {
+                        // the raw tiles (TMA) and the small tiles (splitter) are both operands
+                        if (!mbar_wait(full_bar(stage), phase, err, tag, 3) || !mbar_wait(split_bar(stage), phase, err, tag, 6)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t s0 = smem_base + Smem::stages + stage * STAGE_BYTES;
+                        const uint64_t a_big = smem_desc_sw128(s0, a_lbo, 1024);
+                        const uint64_t b_big = smem_desc_sw128(s0 + A_TILE, b_lbo, 1024);
+                        const uint64_t a_small = smem_desc_sw128(s0 + RAW_BYTES, a_lbo, 1024);
+                        const uint64_t b_small = smem_desc_sw128(s0 + RAW_BYTES + A_TILE, b_lbo, 1024);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++) {
-                        umma_tf32(d_tmem, a_small + a_kstep * k, b_big + b_kstep * k, idesc, (kb | k) != 0);
-                        umma_tf32(d_tmem, a_big + a_kstep * k, b_small + b_kstep * k, idesc, 1);
-                        umma_tf32(d_tmem, a_big + a_kstep * k, b_big + b_kstep * k, idesc, 1);
+                        for (int k = 0; k < BK / UMMA_K; k++) {
+                            umma_tf32(d_tmem, a_small + a_kstep * k, b_big + b_kstep * k, idesc, (kb != kb0) || (k != 0));
+                            umma_tf32(d_tmem, a_big + a_kstep * k, b_small + b_kstep * k, idesc, 1);
+                            umma_tf32(d_tmem, a_big + a_kstep * k, b_big + b_kstep * k, idesc, 1);
+                        }
+                        umma_commit(empty_bar(stage));
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1;
+                        }
                     }
-                    umma_commit(empty_bar(stage));
-                    if (++stage == STAGES) {
-                        stage = 0;
-                        phase ^= 1;
+                    if (!ok) break;
+                    umma_commit(tfull_bar(acc));  // this chunk's partial sums are complete
+                    if (++acc == 2) {
+                        acc = 0;
+                        acc_phase ^= 1;
                     }
-                }
-                if (!ok) break;
-                umma_commit(tfull_bar(acc));
-                if (++acc == 2) {
-                    acc = 0;
-                    acc_phase ^= 1;
                 }
             }
         }
@@ -223,40 +246,57 @@ tc_gemm_f32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         unsigned char* stage_buf = smem + Smem::epi + ew * 2 * EPI_STAGE_BYTES;
         int acc = 0, buf = 0;
         uint32_t acc_phase = 0;
-        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
-            int tm, tn;
-            tile_coords(tile, p, tm, tn);
-            const bool ready = mbar_wait(tfull_bar(acc), acc_phase, err, tag, 4);
-            if (!__all_sync(0xFFFFFFFFu, ready)) break;
-            tc_fence_after();
-            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
-#pragma unroll 1
-            for (int c = 0; c < BN / EPI_CHUNK_COLS; c++) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(t_row + c * EPI_CHUNK_COLS, v);
-                tmem_ld_wait();
-                if (c == BN / EPI_CHUNK_COLS - 1) {
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty_bar(acc));
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+            int tm, tn, tb;
+            tile_coords(tile, p, tm, tn, tb);
+            float total[BN];  // this thread's row of the tile (registers: every index below is a compile-time constant)
+#pragma unroll
+            for (int j = 0; j < BN; j++) total[j] = 0.0f;
+            for (int kb0 = 0; kb0 < p.num_kb; kb0 += CHUNK_KB) {
+                // the TMEM loads below are warp-collective: leave the loops only as a whole warp
+                const bool ready = mbar_wait(tfull_bar(acc), acc_phase, err, tag, 4);
+                if (!__all_sync(0xFFFFFFFFu, ready)) {
+                    ok = false;
+                    break;
                 }
+                tc_fence_after();
+                const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
+#pragma unroll
+                for (int c = 0; c < BN / 32; c++) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(t_row + c * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) total[c * 32 + j] += __uint_as_float(v[j]);
+                }
+                // every TMEM read of this accumulator is done: hand it back to the MMA warp
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(acc));
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+            }
+            if (!ok) break;
+#pragma unroll
+            for (int c = 0; c < BN / EPI_CHUNK_COLS; c++) {
+                // the staging buffer must have been read by its previous TMA store
                 if (lane == 0) tma_store_wait_read<1>();
                 __syncwarp();
                 unsigned char* dst = stage_buf + buf * EPI_STAGE_BYTES + lane * 128;  // row `lane` of the 32 x 32 tile
 #pragma unroll
                 for (int j = 0; j < 8; j++)  // eight 16-byte chunks per row, XOR-swizzled by the row index
-                    *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) =
+                        make_float4(total[c * 32 + 4 * j], total[c * 32 + 4 * j + 1], total[c * 32 + 4 * j + 2], total[c * 32 + 4 * j + 3]);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    tma_store_2d(&map_d, smem_u32(stage_buf + buf * EPI_STAGE_BYTES), tn * BN + c * EPI_CHUNK_COLS, tm * BM + quarter * 32);
+                    tma_store_3d(&map_d, smem_u32(stage_buf + buf * EPI_STAGE_BYTES), tn * BN + c * EPI_CHUNK_COLS, tm * BM + quarter * 32, tb);
                     tma_store_commit();
                 }
                 buf ^= 1;
-            }
-            if (++acc == 2) {
-                acc = 0;
-                acc_phase ^= 1;
             }
         }
         if (lane == 0) tma_store_wait_all();
@@ -324,24 +364,30 @@ bool opt_in_shared_memory() {
     return true;
 }
 
-bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-    return make_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, rows, cols, box_rows);
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t batch, uint64_t batch_stride, uint32_t box_rows) {
+    return make_map_3d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, rows, cols, batch, batch_stride, box_rows);
 }
 
 // D[M,N] = sum_k Aop[m,k] * Bop[n,k]; K-major operand = dense row-major [MN, K], MN-major = dense row-major [K, MN].
-bool launch(const void* A, bool a_mn, const void* B, bool b_mn, void* D, uint64_t M, uint64_t N, uint64_t K, const char* where) {
+bool launch(const TcProduct& c, void* D, const char* where) {
+    const void *A = c.A, *B = c.B;
+    const bool a_mn = c.a_mn, b_mn = c.b_mn;
+    const uint64_t M = c.m, N = c.n, K = c.k, batch = c.batch;
     if (!opt_in_shared_memory()) return false;
     int tag = 0;
     int* err = next_launch_error_word(&tag);
     if (!err) return false;
     CUtensorMap ma, mb, md;
-    const bool oka = a_mn ? make_map(&ma, A, K, M, BK) : make_map(&ma, A, M, K, BM);
-    const bool okb = b_mn ? make_map(&mb, B, K, N, BK) : make_map(&mb, B, N, K, BN);
-    if (!oka || !okb || !make_map(&md, D, M, N, 32)) return false;
+    const bool oka = a_mn ? make_map(&ma, A, K, M, batch, c.a_bs, BK) : make_map(&ma, A, M, K, batch, c.a_bs, BM);
+    const bool okb = b_mn ? make_map(&mb, B, K, N, batch, c.b_bs, BK) : make_map(&mb, B, N, K, batch, c.b_bs, BN);
+    if (!oka || !okb || !make_map(&md, D, M, N, batch, M * N, 32)) return false;
     Params p;
     p.tiles_m = (int)((M + BM - 1) / BM);
     p.tiles_n = (int)((N + BN - 1) / BN);
-    p.num_tiles = p.tiles_m * p.tiles_n;
+    p.tiles_per_batch = p.tiles_m * p.tiles_n;
+    p.num_tiles = (int)batch * p.tiles_per_batch;
+    p.a_batched = (batch > 1 && c.a_bs != 0) ? 1 : 0;
+    p.b_batched = (batch > 1 && c.b_bs != 0) ? 1 : 0;
     p.num_kb = (int)((K + BK - 1) / BK);
     p.a_mn = a_mn ? 1 : 0;
     p.b_mn = b_mn ? 1 : 0;
@@ -358,7 +404,7 @@ bool launch(const void* A, bool a_mn, const void* B, bool b_mn, void* D, uint64_
 bool tc_gemm_f32(const MmDesc& d, int which, size_t num_els, size_t nea, size_t neb, const void* x, const void* y, void* out, const char* where) {
     TcProduct c;
     if (!tc_classify(d, which, 4, num_els, nea, neb, x, y, out, c)) return false;
-    return launch(c.A, c.a_mn, c.B, c.b_mn, out, c.m, c.n, c.k, where);
+    return launch(c, out, where);
 }
 
 }  // namespace mx

@@ -73,6 +73,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
 }
+// 3-d forms: the third coordinate is the batch index (extent 1 for unbatched products and broadcast operands)
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {
@@ -154,6 +164,12 @@ EncodeTiledFn encode_fn();
 
 // [rows, cols] row-major matrix of `elem_bytes`-wide elements; box = box_rows x (128 / elem_bytes) columns, 128-byte swizzle.
 bool make_map_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+
+// `batch` row-major [rows, cols] matrices `batch_stride` elements apart (0 = one matrix read by every batch:
+// the map then has extent 1 along the third dimension and the kernel passes coordinate 0); box = box_rows x
+// (128 / elem_bytes) columns x 1, 128-byte swizzle.
+bool make_map_3d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t rows, uint64_t cols, uint64_t batch,
+                 uint64_t batch_stride, uint32_t box_rows);
 
 // The error word of the calling thread's current device (allocated on first use) and the tag of the launch about
 // to be made.  Returns nullptr when there is no usable device.

@@ -59,6 +59,12 @@ def fwd_cases():
     add("tc-nn", [136, 520], [136, 320], [320, 520])
     add("tc-tn", [264, 256], [264, 392], [392, 256], ast=[1, 264])          # A is the transposed view of a [392, 264] matrix
     add("tc-tt", [256, 264], [256, 384], [384, 264], ast=[1, 256], bst=[1, 384])
+    # batched products on the tensor cores: dense batches, and one operand shared by every batch (stride 0), which is
+    # how a [Cout, K] weight meets a [B, K, P] column buffer (crates/maidenx_tensor/src/ops/matmul.rs:161-225)
+    add("tc-batched", [3, 136, 264], [3, 136, 200], [3, 200, 264])
+    add("tc-batch-bcast-a", [4, 72, 264], [4, 72, 392], [4, 392, 264], ast=[0, 392, 1], alen=72 * 392)
+    add("tc-batch-bcast-b-nt", [3, 200, 264], [3, 200, 392], [3, 392, 264], bst=[0, 1, 392], blen=392 * 264)
+    add("tc-batched-tn", [2, 264, 256], [2, 264, 392], [2, 392, 256], ast=[392 * 264, 1, 264])
     return out
 
 

@@ -103,7 +103,8 @@ def test_products_the_tensor_core_kernel_does_not_take():
     assert mm_path([2, 2, 2, 512, 516, 512, 512, 512, 516, 512, 1, 516, 1, 0, 0], 512 * 516)[0] == 0     # N not a multiple of 8 elements
     assert mm_path([2, 2, 2, 512, 512, 512, 512, 512, 512, 512, 1, 512, 1, 1, 0], 512 * 512)[0] == 0     # offset 1: base not 16-byte aligned
     assert mm_path([2, 2, 2, 512, 512, 512, 512, 512, 512, 1024, 2, 512, 1, 0, 0], 512 * 512)[0] == 0    # A with a stride of 2 along k
-    assert mm_path([3, 3, 3, 4, 512, 512, 4, 512, 512, 4, 512, 512, 262144, 512, 1, 262144, 512, 1, 0, 0], 4 * 512 * 512)[0] == 0  # batched
+    assert mm_path([3, 3, 3, 4, 512, 512, 4, 512, 512, 4, 512, 512, 262144, 512, 1, 262144, 512, 1, 0, 0], 4 * 512 * 512)[0] == 4  # batched rank-3: one launch, four batches
+    assert mm_path([4, 4, 4, 2, 2, 512, 512, 2, 2, 512, 512, 2, 2, 512, 512, 524288, 262144, 512, 1, 524288, 262144, 512, 1, 0, 0], 4 * 512 * 512)[0] == 0  # rank 4
 
 
 def test_f32_products_take_the_split_tf32_kernel_when_rows_are_16_byte_multiples():
