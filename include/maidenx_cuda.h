@@ -297,6 +297,29 @@ MX_DECL_FUSED_T(bf16, _)
 MX_DECL_FUSED_T(f16, _)
 MX_DECL_FUSED_T(f32, _)
 
+/* ---- Conv2d forward / backward composed from the ops above (maidenx_b200/csrc/conv2d_layer.cu) ---------------
+ * The call sequence of the reference's layer (crates/maidenx_nn/src/layers/conv.rs:185-307,333-420): im2col,
+ * matmul, bias add; backward: matmul + col2im (input gradient), matmul (weight gradient), three sums (bias
+ * gradient).  mode 0 issues exactly the calls the reference's layer issues (column buffer declared [B*oh*ow, K],
+ * stride/padding slot order, col2im with num_els = B*C*H*W); mode 1 uses the same ops consistently (batched
+ * product with the weight shared by every batch) and is a true convolution.  x [B, C, H, W], weight
+ * [Cout, C, kh, kw], bias [Cout] or NULL, out / grad_out [B, Cout, oh, ow], all dense; `cols` has
+ * mx_conv2d_cols_elems elements and carries im2col's result from forward to backward; `workspace` has
+ * mx_conv2d_workspace_elems(conv, mode, backward) elements.  Any of grad_x / grad_weight / grad_bias may be NULL.
+ * In mode 0 grad_weight is the [C*kh*kw, Cout] product the reference re-labels as [Cout, C, kh, kw]. */
+typedef struct MxConv2d {
+    size_t batch, in_channels, height, width, out_channels, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w;
+} MxConv2d;
+size_t mx_conv2d_cols_elems(const MxConv2d* conv);
+size_t mx_conv2d_output_elems(const MxConv2d* conv);
+size_t mx_conv2d_workspace_elems(const MxConv2d* conv, int mode, int backward);
+#define MX_DECL_CONV2D_T(T, ...)                                                                                                        \
+    void mx_conv2d_forward_##T(const MxConv2d* conv, int mode, const mx_##T* x, const mx_##T* weight, const mx_##T* bias, mx_##T* cols, \
+                               mx_##T* workspace, mx_##T* out);                                                                         \
+    void mx_conv2d_backward_##T(const MxConv2d* conv, int mode, const mx_##T* grad_out, const mx_##T* weight, const mx_##T* cols,       \
+                                mx_##T* workspace, mx_##T* grad_x, mx_##T* grad_weight, mx_##T* grad_bias);
+MX_DTYPES_FLOAT(MX_DECL_CONV2D_T, _)
+
 /* ---- MLP training step (the data-parallel workload; maidenx_b200/csrc/mlp.cu) ------------------
  * L x [Linear(dim -> dim) + scalar bias, GELU between layers], MSE, SGD with f32 master weights.
  * dtype: 0 = bf16, 1 = f16.  x, y: [batch, dim] device buffers.  The step is forward,

@@ -76,6 +76,12 @@ RUNTIME_SIGNATURES = {
 }
 
 
+class MxConv2d(ctypes.Structure):
+    """MxConv2d of include/maidenx_cuda.h."""
+    _fields_ = [(n, ctypes.c_size_t) for n in ("batch", "in_channels", "height", "width", "out_channels", "kernel_h", "kernel_w", "stride_h",
+                                              "stride_w", "pad_h", "pad_w")]
+
+
 class LibraryMissing(RuntimeError):
     pass
 
@@ -111,6 +117,19 @@ def cast(from_name: str, to_name: str):
     fn.argtypes = [ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
     fn.restype = None
     return fn
+
+
+def conv2d(dtype_name: str):
+    """(mx_conv2d_forward_<dtype>, mx_conv2d_backward_<dtype>): the Conv2d layer composed from the op entry points."""
+    lib = load()
+    P, C = ctypes.c_void_p, ctypes.POINTER(MxConv2d)
+    fwd, bwd = getattr(lib, f"mx_conv2d_forward_{dtype_name}"), getattr(lib, f"mx_conv2d_backward_{dtype_name}")
+    fwd.argtypes, fwd.restype = [C, ctypes.c_int, P, P, P, P, P, P], None
+    bwd.argtypes, bwd.restype = [C, ctypes.c_int, P, P, P, P, P, P, P], None
+    for name in ("mx_conv2d_cols_elems", "mx_conv2d_output_elems"):
+        getattr(lib, name).argtypes, getattr(lib, name).restype = [C], ctypes.c_size_t
+    lib.mx_conv2d_workspace_elems.argtypes, lib.mx_conv2d_workspace_elems.restype = [C, ctypes.c_int, ctypes.c_int], ctypes.c_size_t
+    return fwd, bwd
 
 
 def contiguous(dtype_name: str):
