@@ -384,7 +384,7 @@ bool make_map_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, con
 }
 
 bool make_map_3d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t rows, uint64_t cols, uint64_t batch,
-                 uint64_t batch_stride, uint32_t box_rows) {
+                 uint64_t batch_stride, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return false;
     const bool bcast = batch_stride == 0 || batch <= 1;
@@ -392,7 +392,7 @@ bool make_map_3d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, con
     cuuint64_t strides[2] = {cols * (uint64_t)elem_bytes, (bcast ? rows * cols : batch_stride) * (uint64_t)elem_bytes};
     cuuint32_t box[3] = {(cuuint32_t)(128 / elem_bytes), box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = enc(map, type, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+    CUresult r = enc(map, type, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }

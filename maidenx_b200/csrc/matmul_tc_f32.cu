@@ -13,9 +13,10 @@
 // Two-level accumulation.  The tensor core adds each instruction's products into the f32 accumulator with
 // truncation, which pulls a long running sum towards zero by about half an ulp per instruction (measured:
 // -6e-6 relative after 147 instructions); over K = 8192 that would eat the whole 1e-4 budget.  So the TMEM
-// accumulator only ever holds the sum of CHUNK_KB k-blocks (256 values of K): the epilogue warps drain it after
-// every chunk and keep the running total in registers, added with round-to-nearest, while the tensor core fills
-// the other accumulator.  The truncation then acts on short partial sums of random sign instead of on the total.
+// accumulator only ever holds the sum of CHUNK_KB k-blocks (128 values of K, 48 instructions): the epilogue warps
+// drain it after every chunk and keep the running total in registers, added with round-to-nearest, while the tensor
+// core fills the other accumulator.  The pull towards zero is then bounded by the chunk length (about -2e-6 of the
+// result) whatever K is.
 //
 // One persistent CTA per SM, 320 threads in four roles:
 //   warp 0      TMA producer: raw f32 A [128 x 32] and B [BN x 32] k-blocks (128-byte swizzle rows of 32 floats)
@@ -56,7 +57,7 @@ constexpr int EPI_STAGE_BYTES = 32 * EPI_CHUNK_COLS * 4;  // 4 KB per warp per b
 constexpr int THREADS = 32 * (2 + EPI_WARPS + SPLIT_WARPS);
 constexpr int TMEM_COLS = 2 * BN;              // two f32 accumulators
 constexpr int GROUP_M = 16;
-constexpr int CHUNK_KB = 8;                    // k-blocks summed inside TMEM before the registers take over
+constexpr int CHUNK_KB = 4;                    // k-blocks summed inside TMEM before the registers take over
 constexpr int MN_CHUNK_BYTES = BK * 128;       // one [32 K-rows x 32 MN-elements] box
 
 static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM allocations are powers of two");
@@ -191,7 +192,6 @@ tc_gemm_f32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = make_idesc_tf32(p.a_mn != 0, p.b_mn != 0);
-            const uint32_t a_lbo = p.a_mn ? MN_CHUNK_BYTES : 16, b_lbo = p.b_mn ? MN_CHUNK_BYTES : 16;
             // K-major: 8 floats further along the 128-byte row; MN-major: the next group of eight K-rows
             const uint64_t a_kstep = p.a_mn ? (1024 >> 4) : (32 >> 4), b_kstep = p.b_mn ? (1024 >> 4) : (32 >> 4);
             int stage = 0, acc = 0;
@@ -214,10 +214,14 @@ tc_gemm_f32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         }
                         tc_fence_after();
                         const uint32_t s0 = smem_base + Smem::stages + stage * STAGE_BYTES;
-                        const uint64_t a_big = smem_desc_sw128(s0, a_lbo, 1024);
-                        const uint64_t b_big = smem_desc_sw128(s0 + A_TILE, b_lbo, 1024);
-                        const uint64_t a_small = smem_desc_sw128(s0 + RAW_BYTES, a_lbo, 1024);
-                        const uint64_t b_small = smem_desc_sw128(s0 + RAW_BYTES + A_TILE, b_lbo, 1024);
+                        // K-major: rows of 32 floats, groups of eight rows 1024 bytes apart.  MN-major: 32-byte-atom swizzle,
+                        // groups of four K-rows 512 bytes apart, 128-byte-wide MN chunks one box (4 KB) apart.
+                        const uint64_t a_big = p.a_mn ? smem_desc_sw128_atom32(s0, MN_CHUNK_BYTES, 512) : smem_desc_sw128(s0, 16, 1024);
+                        const uint64_t b_big = p.b_mn ? smem_desc_sw128_atom32(s0 + A_TILE, MN_CHUNK_BYTES, 512) : smem_desc_sw128(s0 + A_TILE, 16, 1024);
+                        const uint64_t a_small =
+                            p.a_mn ? smem_desc_sw128_atom32(s0 + RAW_BYTES, MN_CHUNK_BYTES, 512) : smem_desc_sw128(s0 + RAW_BYTES, 16, 1024);
+                        const uint64_t b_small = p.b_mn ? smem_desc_sw128_atom32(s0 + RAW_BYTES + A_TILE, MN_CHUNK_BYTES, 512)
+                                                        : smem_desc_sw128(s0 + RAW_BYTES + A_TILE, 16, 1024);
 #pragma unroll
                         for (int k = 0; k < BK / UMMA_K; k++) {
                             umma_tf32(d_tmem, a_small + a_kstep * k, b_big + b_kstep * k, idesc, (kb != kb0) || (k != 0));
@@ -364,8 +368,11 @@ bool opt_in_shared_memory() {
     return true;
 }
 
-bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t batch, uint64_t batch_stride, uint32_t box_rows) {
-    return make_map_3d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, rows, cols, batch, batch_stride, box_rows);
+// mn_major: the operand is loaded as [32 K-rows x 32 MN-elements] boxes in the 32-byte-atom form of the 128-byte swizzle
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t batch, uint64_t batch_stride, uint32_t box_rows,
+              bool mn_major = false) {
+    return make_map_3d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, rows, cols, batch, batch_stride, box_rows,
+                       mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 // D[M,N] = sum_k Aop[m,k] * Bop[n,k]; K-major operand = dense row-major [MN, K], MN-major = dense row-major [K, MN].
@@ -378,8 +385,8 @@ bool launch(const TcProduct& c, void* D, const char* where) {
     int* err = next_launch_error_word(&tag);
     if (!err) return false;
     CUtensorMap ma, mb, md;
-    const bool oka = a_mn ? make_map(&ma, A, K, M, batch, c.a_bs, BK) : make_map(&ma, A, M, K, batch, c.a_bs, BM);
-    const bool okb = b_mn ? make_map(&mb, B, K, N, batch, c.b_bs, BK) : make_map(&mb, B, N, K, batch, c.b_bs, BN);
+    const bool oka = a_mn ? make_map(&ma, A, K, M, batch, c.a_bs, BK, true) : make_map(&ma, A, M, K, batch, c.a_bs, BM);
+    const bool okb = b_mn ? make_map(&mb, B, K, N, batch, c.b_bs, BK, true) : make_map(&mb, B, N, K, batch, c.b_bs, BN);
     if (!oka || !okb || !make_map(&md, D, M, N, batch, M * N, 32)) return false;
     Params p;
     p.tiles_m = (int)((M + BM - 1) / BM);

@@ -154,6 +154,19 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr, uint32_t
     d |= (uint64_t)2 << 61;
     return d;
 }
+// MN-major operands of 32-bit elements (tf32) use the 128-byte swizzle with a 32-byte atom (layout type 1; TMA's
+// SWIZZLE_128B_ATOM_32B): 32-byte chunks of a 128-byte row are XOR-ed with the row index modulo 4, so the pattern
+// repeats every four K-rows (512 bytes): the stride byte offset is the distance between groups of FOUR K-rows and the
+// leading byte offset the distance between 128-byte-wide MN chunks.
+__device__ __forceinline__ uint64_t smem_desc_sw128_atom32(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(lbo_bytes >> 4) << 16;
+    d |= (uint64_t)(sbo_bytes >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;
+    return d;
+}
 
 // ---------------------------------------------------------------------------------
 // host side (defined in matmul_tc.cu)
@@ -169,7 +182,7 @@ bool make_map_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, con
 // the map then has extent 1 along the third dimension and the kernel passes coordinate 0); box = box_rows x
 // (128 / elem_bytes) columns x 1, 128-byte swizzle.
 bool make_map_3d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t rows, uint64_t cols, uint64_t batch,
-                 uint64_t batch_stride, uint32_t box_rows);
+                 uint64_t batch_stride, uint32_t box_rows, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B);
 
 // The error word of the calling thread's current device (allocated on first use) and the tag of the launch about
 // to be made.  Returns nullptr when there is no usable device.

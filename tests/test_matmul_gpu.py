@@ -95,8 +95,9 @@ def test_matmul_forward(oracle, cuda, dt):
             H.assert_same("matmul", dt, got, ref, float_rel=2e-2, what=name, scale=np.sqrt(a_sh[-1]))
         elif f32_tc:
             H.assert_same("matmul", dt, got, ref, float_rel=1e-4, what=name, scale=np.sqrt(a_sh[-1]))
-            # split tf32 is far inside that bound: a plain tf32 product (error ~1e-3) would not pass this one
-            H.assert_same("matmul", dt, got, ref, float_rel=5e-6, what=name + " (split-tf32 accuracy)", scale=np.sqrt(a_sh[-1]))
+            # split tf32 is far inside that bound (a few 1e-6: the tensor core's truncating accumulation over one
+            # 128-wide K chunk); a plain tf32 product (error ~5e-4) would not pass this one
+            H.assert_same("matmul", dt, got, ref, float_rel=1e-5, what=name + " (split-tf32 accuracy)", scale=np.sqrt(a_sh[-1]))
         else:
             H.assert_same("matmul", dt, got, ref, what=name)
 
