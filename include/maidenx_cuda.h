@@ -255,8 +255,11 @@ MX_DTYPES_ALL(MX_DECL_CONTIGUOUS_T, _)
 #define MX_DECL_CAST_FROM(FROM, ...) MX_CAST_TARGETS(MX_DECL_CAST, FROM)
 MX_DTYPES_ALL(MX_DECL_CAST_FROM, _)
 
-/* cuda_malloc serves requests of up to 2 KB (the per-call metadata blocks of the dispatch layer) from a pool of
- * fixed-size slots and cuda_free hands them back without a device synchronisation; 0 turns the pool off. */
+/* cuda_malloc / cuda_free keep a cache: requests of up to 64 MB are rounded up to a size class (2 KB slots for the
+ * per-call metadata blocks of the dispatch layer, powers of two above) and freed blocks go back to their class's
+ * free list without the device synchronisation of cudaFree (at most 2 GB per device stay cached).  A block freed by a
+ * thread that launches on its own stream (mx_set_stream) is handed out again only after the work queued on that
+ * stream at the time of the free has finished.  0 turns the cache off. */
 void mx_set_small_pool(int enabled);
 
 /* Stream used by this thread's subsequent op launches (NULL = legacy default stream). */

@@ -13,6 +13,7 @@
 #include <atomic>
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -27,8 +28,25 @@ int tc_status_after_sync();  // matmul_tc.cu
 namespace {
 constexpr size_t kSideTableMaxBytes = 2048;
 
+// Side table, ordered by device address so that every recorded block overlapping a range can be dropped when that
+// range is freed or overwritten through the wrappers.  It is a cache: a pointer that is not found is read back
+// from the device, so dropping entries is always safe.  (A kernel that writes into a recorded block is not seen;
+// the contract is the reference's own: a metadata block is uploaded with cuda_memcpy_h2d right before the call.)
+constexpr size_t kSideTableMaxEntries = 1 << 16;
 std::mutex g_meta_mutex;
-std::unordered_map<const void*, std::vector<size_t>> g_meta_table;
+std::map<uintptr_t, std::vector<size_t>> g_meta_table;
+
+// drops every recorded block that overlaps [p, p + bytes); caller holds g_meta_mutex
+void forget_range_locked(const void* p, size_t bytes) {
+    if (g_meta_table.empty()) return;
+    const uintptr_t lo = (uintptr_t)p, hi = lo + (bytes ? bytes : 1);
+    auto it = g_meta_table.lower_bound(lo);
+    if (it != g_meta_table.begin()) {
+        auto prev = std::prev(it);
+        if (prev->first + prev->second.size() * sizeof(size_t) > lo) it = prev;
+    }
+    while (it != g_meta_table.end() && it->first < hi) it = g_meta_table.erase(it);
+}
 
 struct ScratchSlot {
     void* ptr = nullptr;
@@ -71,7 +89,7 @@ const size_t* resolve_metadata(const size_t* meta, size_t count) {
     if (!meta) return nullptr;
     {
         std::lock_guard<std::mutex> lk(g_meta_mutex);
-        auto it = g_meta_table.find(meta);
+        auto it = g_meta_table.find((uintptr_t)meta);
         if (it != g_meta_table.end() && it->second.size() >= count) {
             t_meta_copy = it->second;
             return t_meta_copy.data();
@@ -155,9 +173,9 @@ void* scratch(size_t bytes) {
     return s.ptr;
 }
 
-static void side_table_forget(const void* p) {
+static void side_table_forget(const void* p, size_t bytes) {
     std::lock_guard<std::mutex> lk(g_meta_mutex);
-    if (!g_meta_table.empty()) g_meta_table.erase(p);
+    forget_range_locked(p, bytes);
 }
 
 }  // namespace mx
@@ -166,47 +184,141 @@ using namespace mx;
 
 namespace mx {
 namespace {
+// ---------------------------------------------------------------------------------
+// Caching allocator behind cuda_malloc / cuda_free.
+//
+// The reference's dispatch layer allocates and frees a metadata block around EVERY op call
+// (crates/maidenx_core/src/be/ops/binary.rs:112-133,161-163) and its tensor layer allocates every op's output with
+// cuda_malloc and drops it with cuda_free (crates/maidenx_core/src/buffer/cuda.rs:21-40,58-75); cudaFree synchronises
+// the device each time, which dominates small workloads such as the README training example.  Requests of up to
+// kPoolMaxBytes are therefore rounded up to a size class (2 KB slots carved from slabs for the metadata blocks,
+// powers of two above that) and a freed block goes to its class's free list instead of back to the driver; at most
+// kPoolCacheLimit bytes per device are kept, anything beyond is really freed.
+//
+// Reuse is ordered by the stream: a block is rewritten only by work queued after its previous user when everything
+// runs on the legacy default stream (the reference's model) or on blocking streams.  A thread that launches on a
+// stream of its own (mx_set_stream) gets an event recorded at cuda_free, and such a block is handed out again only
+// once that event has completed - the cudaMemcpy wrappers run on the legacy stream, which does not wait for
+// non-blocking streams.
+// ---------------------------------------------------------------------------------
 constexpr size_t kPoolSlotBytes = 2048;
 constexpr size_t kPoolSlabSlots = 256;
+constexpr size_t kPoolMaxBytes = (size_t)64 << 20;     // larger requests go straight to cudaMalloc / cudaFree
+constexpr size_t kPoolCacheLimit = (size_t)2 << 30;    // cached (free) bytes kept per device
+constexpr int kPoolClasses = 27;                       // class c holds blocks of 1 << c bytes (c = 12 .. 26); class 0 = slab slots
 std::atomic<bool> g_pool_enabled{true};
 
+struct CachedBlock {
+    void* ptr;
+    cudaEvent_t done;  // null: freed in legacy-stream order, reusable at once
+};
+struct LiveBlock {
+    int device;
+    int cls;  // 0 = slab slot
+};
 struct Slab {
     char* base;
     int device;
 };
 std::mutex g_pool_mutex;
 std::vector<Slab> g_slabs;
-std::vector<void*> g_free_slots[64];  // per device
+std::vector<CachedBlock> g_free[64][kPoolClasses];
+std::unordered_map<void*, LiveBlock> g_live;  // blocks handed out by the pool (not the slab slots: those are found by range)
+size_t g_cached_bytes[64] = {0};
 
-void* pool_take() {
+int size_class(size_t size) {
+    if (size <= kPoolSlotBytes) return 0;
+    int c = 12;
+    while (((size_t)1 << c) < size) c++;
+    return c;
+}
+
+// Pops a reusable block of the class, skipping blocks whose last user on a non-blocking stream is still running.
+void* take_cached(int dev, int cls) {
+    std::vector<CachedBlock>& fl = g_free[dev][cls];
+    for (size_t i = fl.size(); i-- > 0;) {
+        if (fl[i].done) {
+            if (cudaEventQuery(fl[i].done) != cudaSuccess) {
+                cudaGetLastError();
+                continue;
+            }
+            cudaEventDestroy(fl[i].done);
+        }
+        void* p = fl[i].ptr;
+        fl[i] = fl.back();
+        fl.pop_back();
+        if (cls) g_cached_bytes[dev] -= (size_t)1 << cls;
+        return p;
+    }
+    return nullptr;
+}
+
+void* pool_take(size_t size) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    const int cls = size_class(size);
     std::lock_guard<std::mutex> lk(g_pool_mutex);
-    std::vector<void*>& fl = g_free_slots[dev];
-    if (fl.empty()) {
+    if (void* p = take_cached(dev, cls)) {
+        if (cls) g_live[p] = {dev, cls};
+        return p;
+    }
+    if (cls == 0) {
         void* slab = nullptr;
         if (cudaMalloc(&slab, kPoolSlotBytes * kPoolSlabSlots) != cudaSuccess) {
             cudaGetLastError();
             return nullptr;  // the caller falls back to a plain allocation
         }
         g_slabs.push_back({static_cast<char*>(slab), dev});
-        for (size_t i = kPoolSlabSlots; i-- > 0;) fl.push_back(static_cast<char*>(slab) + i * kPoolSlotBytes);
+        std::vector<CachedBlock>& fl = g_free[dev][0];
+        for (size_t i = kPoolSlabSlots; i-- > 1;) fl.push_back({static_cast<char*>(slab) + i * kPoolSlotBytes, nullptr});
+        return slab;
     }
-    void* p = fl.back();
-    fl.pop_back();
+    void* p = nullptr;
+    if (cudaMalloc(&p, (size_t)1 << cls) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    g_live[p] = {dev, cls};
     return p;
 }
 
-bool pool_give_back(void* ptr) {
-    if (!ptr) return false;
+// 1: the block went back to a free list; 0: not a pool block; -1: a pool block that must really be freed (cache full).
+// *bytes = the block's size when it is a pool block.
+int pool_give_back(void* ptr, size_t* bytes) {
+    *bytes = 0;
+    if (!ptr) return 0;
+    cudaStream_t user_stream = ctx().stream;
     std::lock_guard<std::mutex> lk(g_pool_mutex);
-    for (const Slab& sl : g_slabs) {
-        if (ptr >= sl.base && ptr < sl.base + kPoolSlotBytes * kPoolSlabSlots) {
-            g_free_slots[sl.device].push_back(ptr);
-            return true;
+    int dev = -1, cls = -1;
+    auto it = g_live.find(ptr);
+    if (it != g_live.end()) {
+        dev = it->second.device;
+        cls = it->second.cls;
+        g_live.erase(it);
+        *bytes = (size_t)1 << cls;
+        if (g_cached_bytes[dev] + ((size_t)1 << cls) > kPoolCacheLimit) return -1;
+    } else {
+        for (const Slab& sl : g_slabs)
+            if (ptr >= sl.base && ptr < sl.base + kPoolSlotBytes * kPoolSlabSlots) {
+                dev = sl.device;
+                cls = 0;
+                break;
+            }
+        if (cls < 0) return 0;
+        *bytes = kPoolSlotBytes;
+    }
+    CachedBlock b{ptr, nullptr};
+    if (user_stream != 0) {
+        if (cudaEventCreateWithFlags(&b.done, cudaEventDisableTiming) == cudaSuccess) cudaEventRecord(b.done, user_stream);
+        else {
+            cudaGetLastError();
+            b.done = nullptr;
+            cudaStreamSynchronize(user_stream);  // no event to be had: make the block safe the slow way
         }
     }
-    return false;
+    g_free[dev][cls].push_back(b);
+    if (cls) g_cached_bytes[dev] += (size_t)1 << cls;
+    return 1;
 }
 }  // namespace
 }  // namespace mx
@@ -214,14 +326,9 @@ using namespace mx;
 
 extern "C" {
 
-// Small blocks come from a pool.  The reference's dispatch layer allocates and frees a metadata block
-// around EVERY op call (crates/maidenx_core/src/be/ops/binary.rs:112-133,161-163), and cudaFree
-// synchronises the device each time; requests of up to kPoolSlotBytes are served from slabs of
-// fixed-size slots that are handed back to a free list instead.  Reuse is safe in stream order: a
-// slot is only rewritten by work queued after its previous user.  mx_set_small_pool(0) turns it off.
 int cuda_malloc(void** ptr, size_t size) {
-    if (ptr && size <= kPoolSlotBytes && g_pool_enabled.load(std::memory_order_relaxed)) {
-        if (void* p = pool_take()) {
+    if (ptr && size <= kPoolMaxBytes && g_pool_enabled.load(std::memory_order_relaxed)) {
+        if (void* p = pool_take(size)) {
             *ptr = p;
             return (int)cudaSuccess;
         }
@@ -230,11 +337,15 @@ int cuda_malloc(void** ptr, size_t size) {
 }
 
 int cuda_free(void* ptr) {
-    side_table_forget(ptr);
-    if (pool_give_back(ptr)) return (int)cudaSuccess;
+    size_t bytes = 0;
+    const int r = pool_give_back(ptr, &bytes);
+    side_table_forget(ptr, bytes);  // every block recorded inside the freed allocation (its base alone when the size is unknown)
+    if (r == 1) return (int)cudaSuccess;
     return (int)cudaFree(ptr);
 }
 
+// 0 turns the caching allocator off (every request goes to cudaMalloc / cudaFree, as in the reference); blocks
+// already handed out are still recognised when they are freed.
 void mx_set_small_pool(int enabled) { g_pool_enabled.store(enabled != 0, std::memory_order_relaxed); }
 
 int cuda_memcpy_h2d(void* dst, const void* src, size_t size) {
@@ -243,9 +354,11 @@ int cuda_memcpy_h2d(void* dst, const void* src, size_t size) {
         std::vector<size_t> v(size / sizeof(size_t));
         std::memcpy(v.data(), src, size);
         std::lock_guard<std::mutex> lk(g_meta_mutex);
-        g_meta_table[dst] = std::move(v);
+        forget_range_locked(dst, size);
+        if (g_meta_table.size() >= kSideTableMaxEntries) g_meta_table.clear();
+        g_meta_table[(uintptr_t)dst] = std::move(v);
     } else {
-        side_table_forget(dst);
+        side_table_forget(dst, size);
     }
     return (int)e;
 }
@@ -261,7 +374,7 @@ static int surface_device_waits(int e) {
 int cuda_memcpy_d2h(void* dst, const void* src, size_t size) { return surface_device_waits((int)cudaMemcpy(dst, src, size, cudaMemcpyDeviceToHost)); }
 
 int cuda_memcpy_d2d(void* dst, const void* src, size_t size) {
-    side_table_forget(dst);
+    side_table_forget(dst, size);
     return (int)cudaMemcpy(dst, src, size, cudaMemcpyDeviceToDevice);
 }
 

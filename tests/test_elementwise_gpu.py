@@ -305,3 +305,39 @@ def test_small_block_pool_reuses_slots_and_can_be_switched_off(cuda):
         assert np.array_equal(got, x + y)
     finally:
         lib.mx_set_small_pool(1)
+
+
+def test_caching_allocator_size_classes_and_side_table_ranges(cuda):
+    """Blocks above the 2 KB slots are cached by power-of-two size class; requests above 64 MB bypass the cache.
+    A metadata-sized upload into the interior of an allocation is forgotten when the allocation is freed or when a
+    copy through the wrappers overwrites it (a stale entry would hand an op the old dims and strides)."""
+    import ctypes
+
+    from maidenx_b200 import _lib
+    lib = _lib.load()
+
+    def alloc(n):
+        p = ctypes.c_void_p()
+        assert lib.cuda_malloc(ctypes.byref(p), n) == 0
+        return p.value
+
+    lib.mx_set_small_pool(1)
+    a = alloc(100000)                      # class 2^17
+    assert lib.cuda_free(a) == 0
+    b = alloc(70000)                       # same class: the cached block comes back
+    assert b == a
+    c = alloc(100000)
+    assert c != b
+    huge = alloc((64 << 20) + 1)
+    assert lib.cuda_free(huge) == 0 and lib.cuda_free(c) == 0
+    base = lib.mx_metadata_table_size()
+    meta = np.arange(8, dtype=np.uint64)
+    assert lib.cuda_memcpy_h2d(b + 4096, meta.ctypes.data, meta.nbytes) == 0      # recorded, keyed by an interior address
+    assert lib.mx_metadata_table_size() == base + 1
+    big = np.zeros(1024, dtype=np.uint64)
+    assert lib.cuda_memcpy_h2d(b + 4096 - 64, big.ctypes.data, big.nbytes) == 0   # too large to record; overlaps the entry
+    assert lib.mx_metadata_table_size() == base
+    assert lib.cuda_memcpy_h2d(b + 8192, meta.ctypes.data, meta.nbytes) == 0
+    assert lib.mx_metadata_table_size() == base + 1
+    assert lib.cuda_free(b) == 0                                                   # frees the whole 128 KB block
+    assert lib.mx_metadata_table_size() == base

@@ -24,3 +24,15 @@ def test_cuda_matches_the_oracle(oracle, cuda):
     # reductions and dot products over 10000 f32 terms are summed in a different order: rel 1e-4
     assert np.allclose(losses, ref_losses, rtol=1e-4)
     assert np.allclose(W, ref_W, rtol=1e-4, atol=1e-6) and np.allclose(b, ref_b, rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_device_resident_example_matches_the_oracle(oracle, cuda):
+    """maidenx_b200.readme_example keeps every tensor on the device (the form the benchmark times); same parameters
+    and last loss as the oracle composition above."""
+    from maidenx_b200 import device, readme_example as E
+    ref_losses, ref_W, ref_b = R.train(oracle, STEPS)
+    losses, W, b = E.train(E.CudaEngine(), STEPS, read_every=1)
+    assert device.last_error() is None
+    assert np.allclose(losses, ref_losses, rtol=1e-4)
+    assert np.allclose(W, ref_W, rtol=1e-4, atol=1e-6) and np.allclose(b, ref_b, rtol=1e-4, atol=1e-6)
