@@ -259,7 +259,10 @@ MX_DTYPES_ALL(MX_DECL_CAST_FROM, _)
  * per-call metadata blocks of the dispatch layer, powers of two above) and freed blocks go back to their class's
  * free list without the device synchronisation of cudaFree (at most 2 GB per device stay cached).  A block freed by a
  * thread that launches on its own stream (mx_set_stream) is handed out again only after the work queued on that
- * stream at the time of the free has finished.  0 turns the cache off. */
+ * stream at the time of the free has finished.  Uploads of up to 2 KB through cuda_memcpy_h2d are staged in pinned
+ * memory and copied asynchronously on the calling thread's current stream (the source is consumed before the call
+ * returns; later work of the thread is ordered after the upload), so an op call no longer waits for the device.
+ * 0 turns both off: every request goes to cudaMalloc / cudaFree / cudaMemcpy, as in the reference. */
 void mx_set_small_pool(int enabled);
 
 /* Stream used by this thread's subsequent op launches (NULL = legacy default stream). */

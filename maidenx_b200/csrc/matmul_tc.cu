@@ -81,6 +81,7 @@ struct TcParams {
     int tiles_per_batch;   // tiles_m * tiles_n; num_tiles = batch * tiles_per_batch
     int a_batched, b_batched;  // 0: the operand is one matrix shared by every batch (third TMA coordinate stays 0)
     int is_bf16;
+    int out_f32;  // split-K partial results: the epilogue stores the f32 accumulators unrounded
     int a_mn, b_mn;  // operand is MN-major in global memory ([K, MN] row-major) instead of K-major ([MN, K])
 };
 
@@ -245,6 +246,27 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     __syncwarp();
                     if (lane == 0) mbar_arrive(tempty_bar(acc));
                 }
+                if (p.out_f32) {
+                    // two 32-column f32 chunks (128 bytes per row each), one per staging buffer
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const uint32_t* v = h ? v1 : v0;
+                        if (lane == 0) tma_store_wait_read<1>();
+                        __syncwarp();
+                        unsigned char* dst = stage_buf + buf * EPI_STAGE_BYTES + lane * 128;
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_3d(&map_d, smem_u32(stage_buf + buf * EPI_STAGE_BYTES), tn * BN + c * EPI_CHUNK_COLS + h * 32, tm * BM + quarter * 32, tb);
+                            tma_store_commit();
+                        }
+                        buf ^= 1;
+                    }
+                    continue;
+                }
                 // the staging buffer must have been read by its previous TMA store
                 if (lane == 0) tma_store_wait_read<1>();
                 __syncwarp();
@@ -321,34 +343,55 @@ bool opt_in_shared_memory() {
 bool launch_gemm(bool is_bf16, const TcProduct& c, void* D, const char* where) {
     const void *A = c.A, *B = c.B;
     const bool a_mn = c.a_mn, b_mn = c.b_mn;
-    const uint64_t M = c.m, N = c.n, K = c.k, batch = c.batch;
+    const uint64_t M = c.m, N = c.n;
+    uint64_t K = c.k, batch = c.batch;
     if (!opt_in_shared_memory()) return false;
-    int tag = 0;
-    int* err = next_launch_error_word(&tag);
-    if (!err) return false;
-    CUtensorMap ma, mb, md;
-    const bool oka = a_mn ? make_map(&ma, is_bf16, A, K, M, batch, c.a_bs, 64) : make_map(&ma, is_bf16, A, M, K, batch, c.a_bs, BM);
-    const bool okb = b_mn ? make_map(&mb, is_bf16, B, K, N, batch, c.b_bs, 64) : make_map(&mb, is_bf16, B, N, K, batch, c.b_bs, BN);
-    if (!oka || !okb || !make_map(&md, is_bf16, D, M, N, batch, M * N, 32)) return false;
     TcParams p;
     p.M = (int)M;
     p.N = (int)N;
-    p.K = (int)K;
     p.tiles_m = (int)((M + BM - 1) / BM);
     p.tiles_n = (int)((N + BN - 1) / BN);
     p.tiles_per_batch = p.tiles_m * p.tiles_n;
-    p.num_tiles = (int)batch * p.tiles_per_batch;
-    p.a_batched = (batch > 1 && c.a_bs != 0) ? 1 : 0;
-    p.b_batched = (batch > 1 && c.b_bs != 0) ? 1 : 0;
-    p.num_kb = (int)((K + BK - 1) / BK);
-    p.is_bf16 = is_bf16 ? 1 : 0;
-    p.a_mn = a_mn ? 1 : 0;
-    p.b_mn = b_mn ? 1 : 0;
     int grid = sm_count();
     if (ctx().gemm_sm_limit > 0 && ctx().gemm_sm_limit < grid) grid = ctx().gemm_sm_limit;
+    // few output tiles, long reduction: cut K into slices that run as the batches of this launch
+    const int slices = batch == 1 ? splitk_slices((uint64_t)p.tiles_per_batch, K, BK, grid) : 1;
+    float* partial = nullptr;
+    uint64_t a_bs = (uint64_t)c.a_bs, b_bs = (uint64_t)c.b_bs, a_pitch = 0, b_pitch = 0;
+    if (slices > 1) {
+        partial = static_cast<float*>(scratch((size_t)slices * M * N * sizeof(float)));
+        if (!partial) return false;
+        const uint64_t Ks = K / slices;
+        a_pitch = a_mn ? M : K;  // rows keep the pitch of the whole matrix
+        b_pitch = b_mn ? N : K;
+        a_bs = a_mn ? Ks * M : Ks;  // MN-major: Ks rows further; K-major: Ks columns further
+        b_bs = b_mn ? Ks * N : Ks;
+        K = Ks;
+        batch = (uint64_t)slices;
+    }
+    int tag = 0;
+    int* err = next_launch_error_word(&tag);
+    if (!err) return false;
+    const CUtensorMapDataType t16 = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
+    CUtensorMap ma, mb, md;
+    const bool oka = a_mn ? make_map_3d(&ma, t16, 2, A, K, M, batch, a_bs, 64, sw, a_pitch) : make_map_3d(&ma, t16, 2, A, M, K, batch, a_bs, BM, sw, a_pitch);
+    const bool okb = b_mn ? make_map_3d(&mb, t16, 2, B, K, N, batch, b_bs, 64, sw, b_pitch) : make_map_3d(&mb, t16, 2, B, N, K, batch, b_bs, BN, sw, b_pitch);
+    const bool okd = partial ? make_map_3d(&md, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, partial, M, N, batch, M * N, 32) : make_map(&md, is_bf16, D, M, N, batch, M * N, 32);
+    if (!oka || !okb || !okd) return false;
+    p.K = (int)K;
+    p.num_tiles = (int)batch * p.tiles_per_batch;
+    p.a_batched = (batch > 1 && a_bs != 0) ? 1 : 0;
+    p.b_batched = (batch > 1 && b_bs != 0) ? 1 : 0;
+    p.num_kb = (int)((K + BK - 1) / BK);
+    p.is_bf16 = is_bf16 ? 1 : 0;
+    p.out_f32 = partial ? 1 : 0;
+    p.a_mn = a_mn ? 1 : 0;
+    p.b_mn = b_mn ? 1 : 0;
     if (grid > p.num_tiles) grid = p.num_tiles;
     tc_gemm_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx().stream>>>(ma, mb, md, p, err, tag);
     check_launch(where);
+    if (partial) splitk_reduce(is_bf16 ? 0 : 1, partial, slices, (size_t)(M * N), D, where);
     return true;
 }
 
@@ -384,17 +427,77 @@ bool make_map_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, con
 }
 
 bool make_map_3d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t rows, uint64_t cols, uint64_t batch,
-                 uint64_t batch_stride, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+                 uint64_t batch_stride, uint32_t box_rows, CUtensorMapSwizzle swizzle, uint64_t pitch) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return false;
+    if (pitch == 0) pitch = cols;
     const bool bcast = batch_stride == 0 || batch <= 1;
     cuuint64_t dims[3] = {cols, rows, bcast ? 1 : batch};
-    cuuint64_t strides[2] = {cols * (uint64_t)elem_bytes, (bcast ? rows * cols : batch_stride) * (uint64_t)elem_bytes};
+    cuuint64_t strides[2] = {pitch * (uint64_t)elem_bytes, (bcast ? rows * pitch : batch_stride) * (uint64_t)elem_bytes};
     cuuint32_t box[3] = {(cuuint32_t)(128 / elem_bytes), box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(map, type, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
+}
+
+int splitk_slices(uint64_t tiles, uint64_t K, int block_k, int sms) {
+    if (tiles == 0 || tiles * 2 > (uint64_t)sms || K % block_k != 0 || K < 4096) return 1;
+    const uint64_t kb = K / block_k;
+    // Cost in units of one k-block of tensor-core time per CTA: every wave runs kb / s k-blocks plus about 12 for the
+    // pipeline fill and the f32 epilogue of a tile, and the second pass reads s partial tiles per output tile.
+    auto cost = [&](uint64_t s) {
+        const uint64_t t = tiles * s, waves = (t + sms - 1) / sms;
+        return (double)waves * ((double)kb / (double)s + 12.0) + 0.07 * (double)t;
+    };
+    int best = 1;
+    double best_cost = cost(1);
+    for (int s = 2; s <= 64; s++) {
+        if (kb % s != 0 || K / s < 512) continue;
+        const double c = cost((uint64_t)s);
+        if (c < best_cost * 0.97) {
+            best_cost = c;
+            best = s;
+        }
+    }
+    return best;
+}
+
+template <class T>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, int slices, size_t n, T* __restrict__ out) {
+    const size_t nvec = n / 4, stride = (size_t)gridDim.x * 256;
+    for (size_t v = (size_t)blockIdx.x * 256 + threadIdx.x; v < nvec; v += stride) {
+        float4 acc = *reinterpret_cast<const float4*>(partial + 4 * v);
+        for (int s = 1; s < slices; s++) {
+            const float4 q = *reinterpret_cast<const float4*>(partial + (size_t)s * n + 4 * v);
+            acc.x += q.x;
+            acc.y += q.y;
+            acc.z += q.z;
+            acc.w += q.w;
+        }
+        if constexpr (std::is_same<T, float>::value) {
+            *reinterpret_cast<float4*>(out + 4 * v) = acc;
+        } else {
+            Vec<T, 4> o;
+            o.v[0] = from_f32<T>(acc.x);
+            o.v[1] = from_f32<T>(acc.y);
+            o.v[2] = from_f32<T>(acc.z);
+            o.v[3] = from_f32<T>(acc.w);
+            *reinterpret_cast<Vec<T, 4>*>(out + 4 * v) = o;
+        }
+    }
+}
+
+void splitk_reduce(int dtype, const float* partial, int slices, size_t n, void* out, const char* where) {
+    // n is a multiple of 4 here: the tensor-core path requires N to be a multiple of 16 bytes' worth of elements
+    size_t blocks = (n / 4 + 255) / 256;
+    const size_t cap = (size_t)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    if (dtype == 0) splitk_reduce_kernel<bf16><<<(unsigned)blocks, 256, 0, ctx().stream>>>(partial, slices, n, static_cast<bf16*>(out));
+    else if (dtype == 1) splitk_reduce_kernel<f16><<<(unsigned)blocks, 256, 0, ctx().stream>>>(partial, slices, n, static_cast<f16*>(out));
+    else splitk_reduce_kernel<float><<<(unsigned)blocks, 256, 0, ctx().stream>>>(partial, slices, n, static_cast<float*>(out));
+    check_launch(where);
 }
 
 namespace {
@@ -587,6 +690,7 @@ static int debug_forward_path(size_t es, size_t num_els, const size_t* host_meta
     if (k) *k = c.k;
     return (int)c.batch;
 }
+extern "C" int mx_debug_splitk_slices(size_t tiles, size_t k, int block_k, int sms) { return mx::tc::splitk_slices(tiles, k, block_k, sms); }
 extern "C" int mx_debug_matmul_forward_path(size_t num_els, const size_t* host_metadata, const void* a, const void* b, const void* out, int* a_mn_major,
                                             int* b_mn_major, size_t* m, size_t* n, size_t* k) {
     return debug_forward_path(2, num_els, host_metadata, a, b, out, a_mn_major, b_mn_major, m, n, k);

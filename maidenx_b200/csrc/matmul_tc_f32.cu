@@ -370,39 +370,56 @@ bool opt_in_shared_memory() {
 
 // mn_major: the operand is loaded as [32 K-rows x 32 MN-elements] boxes in the 32-byte-atom form of the 128-byte swizzle
 bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t batch, uint64_t batch_stride, uint32_t box_rows,
-              bool mn_major = false) {
+              bool mn_major = false, uint64_t pitch = 0) {
     return make_map_3d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, rows, cols, batch, batch_stride, box_rows,
-                       mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
+                       mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, pitch);
 }
 
 // D[M,N] = sum_k Aop[m,k] * Bop[n,k]; K-major operand = dense row-major [MN, K], MN-major = dense row-major [K, MN].
 bool launch(const TcProduct& c, void* D, const char* where) {
     const void *A = c.A, *B = c.B;
     const bool a_mn = c.a_mn, b_mn = c.b_mn;
-    const uint64_t M = c.m, N = c.n, K = c.k, batch = c.batch;
+    const uint64_t M = c.m, N = c.n;
+    uint64_t K = c.k, batch = c.batch;
     if (!opt_in_shared_memory()) return false;
-    int tag = 0;
-    int* err = next_launch_error_word(&tag);
-    if (!err) return false;
-    CUtensorMap ma, mb, md;
-    const bool oka = a_mn ? make_map(&ma, A, K, M, batch, c.a_bs, BK, true) : make_map(&ma, A, M, K, batch, c.a_bs, BM);
-    const bool okb = b_mn ? make_map(&mb, B, K, N, batch, c.b_bs, BK, true) : make_map(&mb, B, N, K, batch, c.b_bs, BN);
-    if (!oka || !okb || !make_map(&md, D, M, N, batch, M * N, 32)) return false;
     Params p;
     p.tiles_m = (int)((M + BM - 1) / BM);
     p.tiles_n = (int)((N + BN - 1) / BN);
     p.tiles_per_batch = p.tiles_m * p.tiles_n;
+    int grid = sm_count();
+    if (ctx().gemm_sm_limit > 0 && ctx().gemm_sm_limit < grid) grid = ctx().gemm_sm_limit;
+    // few output tiles, long reduction: cut K into slices that run as the batches of this launch (see tc_ptx.cuh)
+    const int slices = batch == 1 ? splitk_slices((uint64_t)p.tiles_per_batch, K, BK, grid) : 1;
+    float* partial = nullptr;
+    uint64_t a_bs = (uint64_t)c.a_bs, b_bs = (uint64_t)c.b_bs, a_pitch = 0, b_pitch = 0;
+    if (slices > 1) {
+        partial = static_cast<float*>(scratch((size_t)slices * M * N * sizeof(float)));
+        if (!partial) return false;
+        const uint64_t Ks = K / slices;
+        a_pitch = a_mn ? M : K;
+        b_pitch = b_mn ? N : K;
+        a_bs = a_mn ? Ks * M : Ks;
+        b_bs = b_mn ? Ks * N : Ks;
+        K = Ks;
+        batch = (uint64_t)slices;
+    }
+    int tag = 0;
+    int* err = next_launch_error_word(&tag);
+    if (!err) return false;
+    CUtensorMap ma, mb, md;
+    const bool oka = a_mn ? make_map(&ma, A, K, M, batch, a_bs, BK, true, a_pitch) : make_map(&ma, A, M, K, batch, a_bs, BM, false, a_pitch);
+    const bool okb = b_mn ? make_map(&mb, B, K, N, batch, b_bs, BK, true, b_pitch) : make_map(&mb, B, N, K, batch, b_bs, BN, false, b_pitch);
+    if (!oka || !okb || !make_map(&md, partial ? static_cast<void*>(partial) : D, M, N, batch, M * N, 32)) return false;
     p.num_tiles = (int)batch * p.tiles_per_batch;
-    p.a_batched = (batch > 1 && c.a_bs != 0) ? 1 : 0;
-    p.b_batched = (batch > 1 && c.b_bs != 0) ? 1 : 0;
+    p.a_batched = (batch > 1 && a_bs != 0) ? 1 : 0;
+    p.b_batched = (batch > 1 && b_bs != 0) ? 1 : 0;
     p.num_kb = (int)((K + BK - 1) / BK);
     p.a_mn = a_mn ? 1 : 0;
     p.b_mn = b_mn ? 1 : 0;
-    int grid = sm_count();
-    if (ctx().gemm_sm_limit > 0 && ctx().gemm_sm_limit < grid) grid = ctx().gemm_sm_limit;
     if (grid > p.num_tiles) grid = p.num_tiles;
     tc_gemm_f32_kernel<<<grid, THREADS, SMEM_BYTES, ctx().stream>>>(ma, mb, md, p, err, tag);
     check_launch(where);
+    if (partial) splitk_reduce(2, partial, slices, (size_t)(M * N), D, where);
     return true;
 }
 

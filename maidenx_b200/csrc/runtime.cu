@@ -207,6 +207,7 @@ constexpr size_t kPoolMaxBytes = (size_t)64 << 20;     // larger requests go str
 constexpr size_t kPoolCacheLimit = (size_t)2 << 30;    // cached (free) bytes kept per device
 constexpr int kPoolClasses = 27;                       // class c holds blocks of 1 << c bytes (c = 12 .. 26); class 0 = slab slots
 std::atomic<bool> g_pool_enabled{true};
+std::atomic<bool> g_stage_enabled{true};
 
 struct CachedBlock {
     void* ptr;
@@ -346,10 +347,67 @@ int cuda_free(void* ptr) {
 
 // 0 turns the caching allocator off (every request goes to cudaMalloc / cudaFree, as in the reference); blocks
 // already handed out are still recognised when they are freed.
-void mx_set_small_pool(int enabled) { g_pool_enabled.store(enabled != 0, std::memory_order_relaxed); }
+void mx_set_small_pool(int enabled) {
+    g_pool_enabled.store(enabled != 0, std::memory_order_relaxed);
+    g_stage_enabled.store(enabled != 0, std::memory_order_relaxed);
+}
+
+// Small uploads (the per-call metadata blocks, scalars, tiny tensors) go through a per-thread ring of pinned
+// staging slots and an asynchronous copy on the thread's current stream: a plain cudaMemcpy from pageable memory
+// first waits for everything queued on the stream, which serialises host and device once per op call in the
+// reference's dispatch pattern.  The source is copied into the slot before the call returns, so the caller may reuse
+// it at once, and everything the thread queues afterwards (ops, the synchronous device-to-host copies) is ordered
+// after the upload by the stream.  A slot is reused only after the event recorded behind its group has completed.
+namespace {
+constexpr size_t kStageSlotBytes = 2048;
+constexpr int kStageSlots = 512, kStageGroup = 64;
+struct StageRing {
+    char* base = nullptr;
+    cudaEvent_t done[kStageSlots / kStageGroup] = {nullptr};
+    bool used[kStageSlots / kStageGroup] = {false};
+    int next = 0;
+    bool failed = false;
+};
+thread_local StageRing t_stage[64];
+
+// Returns false when the staged path is unavailable (the caller then uses the synchronous copy).
+bool staged_upload(void* dst, const void* src, size_t size, cudaError_t* result) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    StageRing& r = t_stage[dev];
+    if (r.failed) return false;
+    if (!r.base) {
+        if (cudaHostAlloc(reinterpret_cast<void**>(&r.base), kStageSlotBytes * kStageSlots, cudaHostAllocDefault) != cudaSuccess) {
+            cudaGetLastError();
+            r.failed = true;
+            return false;
+        }
+        for (auto& e : r.done)
+            if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) {
+                cudaGetLastError();
+                r.failed = true;
+                return false;
+            }
+    }
+    const int slot = r.next, group = slot / kStageGroup;
+    if (slot % kStageGroup == 0 && r.used[group]) cudaEventSynchronize(r.done[group]);  // the copies that last used this group have finished
+    char* stage = r.base + (size_t)slot * kStageSlotBytes;
+    std::memcpy(stage, src, size);
+    cudaStream_t stream = ctx().stream;
+    *result = cudaMemcpyAsync(dst, stage, size, cudaMemcpyHostToDevice, stream);
+    r.next = (slot + 1) % kStageSlots;
+    if (r.next % kStageGroup == 0) {
+        cudaEventRecord(r.done[group], stream);
+        r.used[group] = true;
+    }
+    return true;
+}
+}  // namespace
 
 int cuda_memcpy_h2d(void* dst, const void* src, size_t size) {
-    cudaError_t e = cudaMemcpy(dst, src, size, cudaMemcpyHostToDevice);
+    cudaError_t e;
+    if (!(size > 0 && size <= kStageSlotBytes && g_stage_enabled.load(std::memory_order_relaxed) && staged_upload(dst, src, size, &e)))
+        e = cudaMemcpy(dst, src, size, cudaMemcpyHostToDevice);
     if (e == cudaSuccess && size > 0 && size <= kSideTableMaxBytes && size % sizeof(size_t) == 0) {
         std::vector<size_t> v(size / sizeof(size_t));
         std::memcpy(v.data(), src, size);
@@ -371,9 +429,19 @@ static int surface_device_waits(int e) {
     return e;
 }
 
-int cuda_memcpy_d2h(void* dst, const void* src, size_t size) { return surface_device_waits((int)cudaMemcpy(dst, src, size, cudaMemcpyDeviceToHost)); }
+// The synchronous copies below run on the legacy stream, which does not wait for a non-blocking stream: when the
+// thread launches on a stream of its own, its queued work (ops, staged uploads) is waited for first.
+static void drain_thread_stream() {
+    if (ctx().stream != 0) cudaStreamSynchronize(ctx().stream);
+}
+
+int cuda_memcpy_d2h(void* dst, const void* src, size_t size) {
+    drain_thread_stream();
+    return surface_device_waits((int)cudaMemcpy(dst, src, size, cudaMemcpyDeviceToHost));
+}
 
 int cuda_memcpy_d2d(void* dst, const void* src, size_t size) {
+    drain_thread_stream();
     side_table_forget(dst, size);
     return (int)cudaMemcpy(dst, src, size, cudaMemcpyDeviceToDevice);
 }

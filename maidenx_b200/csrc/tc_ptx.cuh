@@ -181,8 +181,17 @@ bool make_map_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, con
 // `batch` row-major [rows, cols] matrices `batch_stride` elements apart (0 = one matrix read by every batch:
 // the map then has extent 1 along the third dimension and the kernel passes coordinate 0); box = box_rows x
 // (128 / elem_bytes) columns x 1, 128-byte swizzle.
+// `pitch` = elements between consecutive rows (0: dense, = cols).
 bool make_map_3d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t rows, uint64_t cols, uint64_t batch,
-                 uint64_t batch_stride, uint32_t box_rows, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B);
+                 uint64_t batch_stride, uint32_t box_rows, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, uint64_t pitch = 0);
+
+// Split-K plan for a product with few output tiles and a long reduction: the K range is cut into `slices` equal parts
+// that run as the batches of one launch (each operand's slice is a sub-matrix reachable through the tensor map: a column
+// range of a K-major operand, a row range of an MN-major one), the f32 partial results [slices, M, N] go to scratch and
+// splitk_reduce adds them up and rounds once.  Returns 1 when splitting does not pay.
+int splitk_slices(uint64_t tiles, uint64_t K, int block_k, int sms);
+// out[i] = round(sum_s partial[s * n + i]); dtype: 0 bf16, 1 f16, 2 f32.
+void splitk_reduce(int dtype, const float* partial, int slices, size_t n, void* out, const char* where);
 
 // The error word of the calling thread's current device (allocated on first use) and the tag of the launch about
 // to be made.  Returns nullptr when there is no usable device.

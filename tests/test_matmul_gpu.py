@@ -190,6 +190,9 @@ BIG_FWD = [
     ("tn-512-tiles", 4096, 4096, 8192, "mn", "mn"),
     ("nt-ragged-group", 2216, 840, 8192, "k", "k"),      # 18 row-tiles: the last group of 16 holds two; 40-row and 72-column edge tiles
     ("tt-ragged", 2216, 840, 4104, "mn", "k"),           # ragged K block (4104 = 64 * 64 + 8)
+    # few tiles, long reduction: K is cut into slices that run as batches, f32 partials summed by a second kernel
+    ("splitk-nt", 200, 264, 32768, "k", "k"),
+    ("splitk-tn", 264, 256, 65536, "mn", "mn"),          # the shape class of the conv weight gradient
 ]
 
 

@@ -116,3 +116,18 @@ def test_f32_products_take_the_split_tf32_kernel_when_rows_are_16_byte_multiples
     assert mm_path([2, 2, 2, 512, 516, 512, 512, 512, 516, 512, 1, 516, 1, 0, 0], 512 * 516, f32=True)[0] == 1   # 516 = 4 * 129
     assert mm_path([2, 2, 2, 512, 514, 512, 512, 512, 514, 512, 1, 514, 1, 0, 0], 512 * 514, f32=True)[0] == 0
     assert mm_path([2, 2, 2, 64, 64, 64, 64, 64, 64, 64, 1, 64, 1, 0, 0], 64 * 64, f32=True)[0] == 0             # small: SIMT, bit-exact order
+
+
+def test_split_k_plan():
+    """Few output tiles and a long reduction are cut along K so that every SM gets a tile; products that already fill
+    the GPU, short reductions and K that does not divide are left alone."""
+    lib = _lib.load()
+    sk = lib.mx_debug_splitk_slices
+    assert sk(18, 200704, 64, 148) == 8          # the conv weight gradient at the benchmark shape: 144 tiles on 148 SMs
+    assert sk(36, 200704, 32, 148) == 4          # the same product in f32 (128 x 128 tiles)
+    assert sk(4096, 8192, 64, 148) == 1          # the MLP products fill the GPU
+    assert sk(4, 2048, 64, 148) == 1             # reduction too short to be worth a second pass
+    assert sk(2, 65600, 64, 148) == 1 or 65600 % (64 * sk(2, 65600, 64, 148)) == 0
+    for tiles, k in ((1, 1 << 20), (3, 65536), (10, 16384)):
+        s_ = sk(tiles, k, 64, 148)
+        assert s_ >= 1 and (k // 64) % s_ == 0 and k // s_ >= 1024
