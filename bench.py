@@ -271,17 +271,17 @@ def verify_case(torch, c, a, b, out):
         rows = sample_rows(R, 12, C)
         idx = torch.as_tensor(rows, device="cuda")
 
-        def logical(buf, strides):
-            v = torch.as_strided(buf, (R, C), tuple(int(s) for s in strides))
+        def logical(buf, strides, off):
+            v = torch.as_strided(buf, (R, C), tuple(int(s) for s in strides), int(off))
             return to_store(v[idx])
 
         n = len(rows) * C
-        got = to_store(out.view(R, C)[idx])
+        got = to_store(out[:R * C].view(R, C)[idx])
         ref = np.empty(n, st)
         meta = np.asarray([n, 1, 1, 0, 0] if c.family == "binary" else [n, 1, 0], dtype=np.uint64)
-        la = logical(a, c.metadata[2:4])
+        la = logical(a, c.metadata[2:4], c.metadata[6] if c.family == "binary" else c.metadata[4])
         if c.family == "binary":
-            lb = logical(b, c.metadata[4:6])
+            lb = logical(b, c.metadata[4:6], c.metadata[7])
             oracle_call(c.op, dt, SZ(n), SZ(1), meta.ctypes.data, la.ctypes.data, lb.ctypes.data, ref.ctypes.data)
         else:
             oracle_call(c.op, dt, SZ(n), SZ(1), meta.ctypes.data, la.ctypes.data, ref.ctypes.data)
@@ -291,7 +291,7 @@ def verify_case(torch, c, a, b, out):
         return close(got, ref, dt, rel, np.abs(decode(la, dt)) if c.op == "gelu" else 0.0)
     if c.family == "reduce":
         R, C = c.metadata[0], c.metadata[1]
-        dim0 = c.metadata[4] == R and c.metadata[5] == C
+        dim0 = c.metadata[5] == C  # stride of the reduced dim: C for dim 0, 1 for dim 1
         x = a[:R * C].view(R, C)
         binding.set_wide(True)
         try:
@@ -825,9 +825,28 @@ def e2e_mlp(torch, lib, mlp, x, y, dist, world, steps, warm):
         t = torch.tensor([dt_s], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dt_s = float(t.item())
+    # the feed alone: the same pinned -> device copies with no compute beside them, every rank at the same time.  When this
+    # rate is below what the device-resident step consumes, the host link (not the kernels, not the exchange) bounds e2e.
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(4):
+        pipe.bufs[0][0].copy_(hx, non_blocking=True)
+        pipe.bufs[0][1].copy_(hy, non_blocking=True)
+    torch.cuda.synchronize()
+    copy_s = (time.perf_counter() - t0) / 4
+    if world > 1:
+        t = torch.tensor([copy_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        copy_s = float(t.item())
     return {"value": round(MLP_GLOBAL_BATCH / dt_s, 1), "unit": "samples/s", "h2d_bytes_per_step": 2 * nbytes * world, "d2h_bytes_per_step": 4 * world,
             "steps": steps, "ms_per_step": round(dt_s * 1e3, 3), "loss": float(loss_host[0]),
-            "pipeline": "double-buffered: host->device copies of step i+1 on a copy stream while step i computes"}
+            "pipeline": "double-buffered: host->device copies of step i+1 on a copy stream while step i computes",
+            "h2d_gbs_per_rank_achieved": round(2 * nbytes / dt_s / 1e9, 1),
+            "h2d_copy_only": {"ms_per_step_worth": round(copy_s * 1e3, 3), "gbs_per_rank": round(2 * nbytes / copy_s / 1e9, 1),
+                              "gbs_all_ranks": round(2 * nbytes * world / copy_s / 1e9, 1),
+                              "what": "the step's input copies alone (pinned host memory, all ranks at once, slowest rank): the floor under any e2e step time"}}
 
 
 def cpu_mlp_once(sample_batch, steps=1):
@@ -962,7 +981,7 @@ def main():
         raise SystemExit("the global batch must divide evenly over the ranks")
     mlp, x, y, local_batch = mlp_setup(torch, rank, world, dist if world > 1 else None, args.exchange, args.exchange_sms)
     verified = {}
-    if verify and rank == 0 and world == 1:
+    if verify and world == 1:
         rows_ok, loss_ok = verify_mlp(torch, mlp, x, y, local_batch)
         verified["mlp_output_rows_vs_oracle"] = rows_ok
         verified["mlp_loss_vs_f64"] = loss_ok
@@ -995,6 +1014,18 @@ def main():
         ms_step = float(t.item())
     loss = mlp.loss()
     mlp_exchange = mlp.exchange
+    if world > 1 and verify:
+        # data parallelism keeps replicas in step: after the timed steps every rank must hold bit-identical weights
+        from maidenx_b200.mlp import _as_tensor
+        sums = []
+        for l in range(MLP_LAYERS):
+            w = _as_tensor(torch, mlp.ptr("weight", l), MLP_DIM * MLP_DIM, torch.bfloat16).view(torch.int16).to(torch.int64)
+            sums.append((w * (torch.arange(w.numel(), device="cuda") % 8191 + 1)).sum())
+        mine = torch.stack(sums)
+        lo, hi = mine.clone(), mine.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        verified["weights_bit_identical_across_ranks"] = bool(torch.equal(lo, hi))
     if hasattr(mlp, "status") and mlp.status() != 0:
         raise RuntimeError(f"a cross-rank barrier gave up waiting for rank {mlp.status() - 1}")
     lib.mx_device_synchronize()

@@ -11,7 +11,7 @@ extern "C" {
 
 /* Host-only views of the launch planners, for tests that run without a GPU: which kernel class a call with this
  * HOST metadata and these base addresses would take.  Elementwise: 0 empty, 1 flat, 2 row, 3 tile, 4 generic,
- * 5 serial (an in-place lhs that overlaps itself), 6 error.  Reduction: 0 empty, 1 rows, 2 columns, 3 generic
+ * 5 serial (an in-place lhs that overlaps itself), 6 error, 7 flat with shifted loads (operands not 16-byte aligned).  Reduction: 0 empty, 1 rows, 2 columns, 3 generic
  * scatter, 4 error, with the recognised [outer, reduced, inner] extents. */
 int mx_debug_elementwise_plan(size_t num_els, size_t num_dims, const size_t* host_metadata, int num_inputs, int inplace, size_t elem_size,
                               size_t out_elem_size, const void* out, const void* a, const void* b, int* merged_rank, int* vector_ok,

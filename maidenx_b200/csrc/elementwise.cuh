@@ -12,7 +12,10 @@
 //   tile     an input is unit-stride along another dim (a transposed view): 64x64
 //            tiles staged through shared memory so both the transposed read and the
 //            output write are full 128-byte lines;
-//   generic  anything else (also misaligned bases): per-element fast-divmod gather.
+//   shifted  flat operands whose addresses are not 16-byte aligned (the offset-1 views of the reference's test
+//            fixtures): a scalar head brings the output to a 16-byte boundary, then every input vector is
+//            assembled from the two aligned 16-byte words it straddles with a funnel shift;
+//   generic  anything else: per-element fast-divmod gather.
 // In-place ops reuse the same kernels with the output aliased to the lhs and the dims
 // re-ordered by the lhs strides; an lhs that overlaps itself (stride 0) runs serially
 // on one thread, which is the order the CPU backend applies.
@@ -22,7 +25,7 @@
 
 namespace mx {
 
-enum EwKind { EW_EMPTY = 0, EW_FLAT, EW_ROW, EW_TILE, EW_GENERIC, EW_SERIAL, EW_ERROR };
+enum EwKind { EW_EMPTY = 0, EW_FLAT, EW_ROW, EW_TILE, EW_GENERIC, EW_SERIAL, EW_ERROR, EW_FLAT_SHIFT };
 
 struct EwPlan {
     int kind;
@@ -144,6 +147,82 @@ __global__ void __launch_bounds__(kEwThreads) ew_flat_kernel(F f, const T* a, co
         }
     } else {
         for (uint64_t i = base + threadIdx.x; i < n; i += kEwThreads) {
+            T x = a[sa ? i : 0];
+            if constexpr (NIN == 2) out[i] = f(x, b[sb ? i : 0]);
+            else out[i] = f(x);
+        }
+    }
+}
+
+// Funnel-shifts the 32 bytes (lo, hi) right by `sh` bytes and returns the low 16.
+__device__ __forceinline__ uint4 shift_pair(const uint4& lo, const uint4& hi, uint32_t sh) {
+    const uint32_t bits = (sh & 3u) * 8u;
+    switch (sh >> 2) {
+        case 0:
+            return make_uint4(__funnelshift_r(lo.x, lo.y, bits), __funnelshift_r(lo.y, lo.z, bits), __funnelshift_r(lo.z, lo.w, bits),
+                              __funnelshift_r(lo.w, hi.x, bits));
+        case 1:
+            return make_uint4(__funnelshift_r(lo.y, lo.z, bits), __funnelshift_r(lo.z, lo.w, bits), __funnelshift_r(lo.w, hi.x, bits),
+                              __funnelshift_r(hi.x, hi.y, bits));
+        case 2:
+            return make_uint4(__funnelshift_r(lo.z, lo.w, bits), __funnelshift_r(lo.w, hi.x, bits), __funnelshift_r(hi.x, hi.y, bits),
+                              __funnelshift_r(hi.y, hi.z, bits));
+        default:
+            return make_uint4(__funnelshift_r(lo.w, hi.x, bits), __funnelshift_r(hi.x, hi.y, bits), __funnelshift_r(hi.y, hi.z, bits),
+                              __funnelshift_r(hi.z, hi.w, bits));
+    }
+}
+
+// VEC elements starting at an arbitrary element-aligned address p, for a warp whose lanes hold CONSECUTIVE vectors: each
+// lane loads the aligned 16-byte word its vector starts in; the word the vector ends in is the next lane's word and
+// comes over by shuffle (only the last valid lane of the warp loads it itself), so a shifted operand costs one global
+// load per vector, not two.  `sh` = p modulo 16 (the same for every vector of a launch).  Every lane of the warp must
+// call this; `valid` says whether this lane has a vector, `next_valid` whether the next lane has one.  Both words
+// contain at least one byte of a valid vector, so no load leaves the allocation.
+template <class T, int VEC>
+__device__ __forceinline__ Vec<T, VEC> ld_vec_shifted(const T* p, uint32_t sh, bool valid, bool next_valid) {
+    static_assert(sizeof(T) * VEC == 16, "one 16-byte vector");
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(p) - sh;
+    uint4 lo = make_uint4(0, 0, 0, 0);
+    if (valid) lo = *reinterpret_cast<const uint4*>(addr);
+    if (sh == 0) return *reinterpret_cast<const Vec<T, VEC>*>(&lo);
+    uint4 hi;
+    hi.x = __shfl_down_sync(0xFFFFFFFFu, lo.x, 1);
+    hi.y = __shfl_down_sync(0xFFFFFFFFu, lo.y, 1);
+    hi.z = __shfl_down_sync(0xFFFFFFFFu, lo.z, 1);
+    hi.w = __shfl_down_sync(0xFFFFFFFFu, lo.w, 1);
+    if (valid && ((threadIdx.x & 31) == 31 || !next_valid)) hi = *reinterpret_cast<const uint4*>(addr + 16);
+    const uint4 r = shift_pair(lo, hi, sh);
+    return *reinterpret_cast<const Vec<T, VEC>*>(&r);
+}
+
+// Flat operands at addresses that are not 16-byte aligned.  Elements [0, head) and [tail_begin, n) are handled one at a
+// time by block 0; the body [head, tail_begin) starts where the OUTPUT is aligned for its vector store, and each input
+// is read with ld_vec_shifted (sha / shb = its address modulo 16 at the start of the body).  sa / sb: 1 = contiguous,
+// 0 = broadcast scalar.
+template <class F, class T, class O, int NIN, int VEC>
+__global__ void __launch_bounds__(kEwThreads) ew_flat_shift_kernel(F f, const T* a, const T* b, O* out, uint64_t n, uint64_t head, uint64_t body_vecs,
+                                                                   int sa, int sb, uint32_t sha, uint32_t shb) {
+    const uint64_t v0 = (uint64_t)blockIdx.x * kEwThreads * kEwUnroll + threadIdx.x;
+    Vec<T, VEC> va[kEwUnroll], vb[kEwUnroll];
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; u++) {
+        const uint64_t v = v0 + (uint64_t)u * kEwThreads;
+        const bool valid = v < body_vecs, next_valid = v + 1 < body_vecs;
+        const uint64_t i = head + v * VEC;
+        va[u] = sa ? ld_vec_shifted<T, VEC>(a + i, sha, valid, next_valid) : splat<T, VEC>(a[0]);
+        if constexpr (NIN == 2) vb[u] = sb ? ld_vec_shifted<T, VEC>(b + i, shb, valid, next_valid) : splat<T, VEC>(b[0]);
+    }
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; u++) {
+        const uint64_t v = v0 + (uint64_t)u * kEwThreads;
+        if (v < body_vecs) st_vec<O, VEC>(out + head + v * VEC, apply_vec<F, T, O, NIN, VEC>(f, va[u], vb[u]));
+    }
+    if (blockIdx.x == 0) {
+        const uint64_t tail_begin = head + body_vecs * VEC;
+        const uint64_t edge = head + (n - tail_begin);  // fewer than VEC elements on either side
+        for (uint64_t e = threadIdx.x; e < edge; e += kEwThreads) {
+            const uint64_t i = e < head ? e : tail_begin + (e - head);
             T x = a[sa ? i : 0];
             if constexpr (NIN == 2) out[i] = f(x, b[sb ? i : 0]);
             else out[i] = f(x);
@@ -492,6 +571,25 @@ void ew_launch(const EwPlan& pl, const F& f, const T* a, const T* b, O* out, con
                 return;
             }
             ew_flat_kernel<F, T, O, NIN, VEC><<<(uint32_t)blocks, kEwThreads, 0, s>>>(f, a, b, out, pl.n, (int)pl.st[1][0], NIN == 2 ? (int)pl.st[2][0] : 0);
+            break;
+        }
+        case EW_FLAT_SHIFT: {
+            // head: elements until the output reaches the alignment of its vector store
+            const uintptr_t oaddr = reinterpret_cast<uintptr_t>(out);
+            const size_t oalign = VEC * sizeof(O);
+            uint64_t head = ((oalign - oaddr % oalign) % oalign) / sizeof(O);
+            if (head > pl.n) head = pl.n;
+            const uint64_t body_vecs = (pl.n - head) / VEC;
+            const int sa = (int)pl.st[1][0], sb = NIN == 2 ? (int)pl.st[2][0] : 0;
+            const uint32_t sha = sa ? (uint32_t)(reinterpret_cast<uintptr_t>(a + head) % 16) : 0;
+            const uint32_t shb = (NIN == 2 && sb) ? (uint32_t)(reinterpret_cast<uintptr_t>(b + head) % 16) : 0;
+            uint64_t blocks = (body_vecs + (uint64_t)kEwThreads * kEwUnroll - 1) / ((uint64_t)kEwThreads * kEwUnroll);
+            if (blocks == 0) blocks = 1;
+            if (blocks > 0x7FFFFFFFull) {
+                set_error(kErrUnsupported, 0, where);
+                return;
+            }
+            ew_flat_shift_kernel<F, T, O, NIN, VEC><<<(uint32_t)blocks, kEwThreads, 0, s>>>(f, a, b, out, pl.n, head, body_vecs, sa, sb, sha, shb);
             break;
         }
         case EW_ROW: {

@@ -181,11 +181,16 @@ void ew_make_plan(EwPlan& pl, size_t num_els, size_t num_dims, const size_t* hm,
         bool ok = aligned_to(ptr[0], pl.off[0], esz[0], vec * esz[0]);
         for (int k = 1; k < nop; k++)
             if (st[k][0] == 1 && !aligned_to(ptr[k], pl.off[k], esz[k], 16)) ok = false;
-        if (ok) {
+        // every operand element-aligned (always true for typed pointers handed over by a sane caller): misaligned
+        // flat operands take the shifted form of the flat kernel instead of the per-element gather
+        bool elem_ok = true;
+        for (int k = 0; k < nop; k++)
+            if (!aligned_to(ptr[k], pl.off[k], esz[k], esz[k])) elem_ok = false;
+        if (ok || elem_ok) {
             pl.nd = 1;
             pl.dim[0] = (uint32_t)std::min<uint64_t>(dim[0], 0xFFFFFFFFull);
             for (int k = 0; k < 3; k++) pl.st[k][0] = st[k][0];
-            pl.kind = EW_FLAT;
+            pl.kind = ok ? EW_FLAT : EW_FLAT_SHIFT;
             pl.vec = true;
             return;
         }
@@ -315,7 +320,7 @@ void ew_fill_gen_params(const EwPlan& pl, EwGenParams& P) {
 // Host-only view of the planner for tests that run without a GPU: which kernel class a call would take.
 // metadata is HOST memory in the layout of the op family (binary: [dims | lhs strides | rhs strides | offsets],
 // unary: [dims | strides | offset]); returns the EwKind (0 empty, 1 flat, 2 row, 3 tile, 4 generic,
-// 5 serial, 6 error) and writes the merged rank, the vector flag and the tile's transposed-operand mask.
+// 5 serial, 6 error, 7 flat with shifted loads) and writes the merged rank, the vector flag and the tile's transposed-operand mask.
 extern "C" int mx_debug_elementwise_plan(size_t num_els, size_t num_dims, const size_t* host_metadata, int num_inputs, int inplace,
                                          size_t elem_size, size_t out_elem_size, const void* out, const void* a, const void* b, int* merged_rank,
                                          int* vector_ok, int* transposed_mask) {

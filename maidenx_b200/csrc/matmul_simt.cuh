@@ -164,6 +164,39 @@ __global__ void __launch_bounds__(kMmThreads) matmul_simt_kernel(const T* __rest
     }
 }
 
+// Few outputs, long reduction (the weight gradient of a narrow Linear layer: [1, batch] . [batch, in] in the reference's
+// README example): the tiled kernel would run the whole reduction in one or two blocks.  Here one block owns one output
+// element, its threads take k = t, t + 256, ... (each in ascending order) and the partial sums are folded by a fixed
+// shuffle tree, so the result is reproducible; integers stay exact (wrapping addition is associative), floats are summed
+// in a different order than the element-type loop of the reference and agree with it within the reduction tolerance.
+template <class T>
+__global__ void __launch_bounds__(kMmThreads) matmul_longk_kernel(const T* __restrict__ X, const T* __restrict__ Y, T* __restrict__ out, MmParams P) {
+    typedef typename MmAcc<T>::type Acc;
+    const uint64_t o = blockIdx.x;
+    const uint64_t row = o / P.N, col = o % P.N;
+    const uint64_t batch = row / P.M, mi = row % P.M;
+    const int64_t x0 = (int64_t)batch * P.xs_b + (int64_t)mi * P.xs_m, y0 = (int64_t)batch * P.ys_b + (int64_t)col * P.ys_c;
+    Acc acc = (Acc)0;
+    for (uint64_t r = threadIdx.x; r < P.K; r += kMmThreads) {
+        const uint64_t ix = (uint64_t)(x0 + (int64_t)r * P.xs_r), iy = (uint64_t)(y0 + (int64_t)r * P.ys_r);
+        const Acc xv = ix < P.x_limit ? mm_load<T>(X[ix]) : (Acc)0, yv = iy < P.y_limit ? mm_load<T>(Y[iy]) : (Acc)0;
+        if constexpr (is_half_v<T>) acc = fmaf(xv, yv, acc);
+        else acc = acc + xv * yv;
+    }
+    __shared__ Acc part[kMmThreads / 32];
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc = acc + __shfl_down_sync(0xFFFFFFFFu, acc, s);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        Acc total = part[0];
+#pragma unroll
+        for (int w = 1; w < kMmThreads / 32; w++) total = total + part[w];
+        if (o < P.out_elems) out[o] = mm_store<T>(total);
+    }
+}
+constexpr uint64_t kLongKMinK = 2048, kLongKMaxOutputs = 1024;
+
 // Host-side description of one matmul call, parsed from the metadata block
 // [out_ndim, a_ndim, b_ndim | out_shape | a_shape | b_shape | a_strides | b_strides | a_off, b_off]
 // (crates/maidenx_tensor/src/ops/matmul.rs:227-264).
@@ -183,6 +216,11 @@ size_t mm_meta_words(const size_t* head3);
 template <class T>
 void mm_launch(const MmParams& P, const T* X, const T* Y, T* out, const char* where) {
     if (P.rows == 0 || P.N == 0) return;
+    if (P.K >= kLongKMinK && P.out_elems <= kLongKMaxOutputs && P.rows * P.N <= kLongKMaxOutputs) {
+        matmul_longk_kernel<T><<<(unsigned)P.out_elems, kMmThreads, 0, ctx().stream>>>(X, Y, out, P);
+        check_launch(where);
+        return;
+    }
     uint64_t gx = (P.rows + kMmTile - 1) / kMmTile, gy = (P.N + kMmTile - 1) / kMmTile;
     if (gy > 65535 || gx > 0x7FFFFFFFull) {  // more than 4M output columns
         set_error(kErrUnsupported, 0, where);

@@ -259,7 +259,7 @@ tc_gemm_f32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             for (int j = 0; j < BN; j++) total[j] = 0.0f;
             for (int kb0 = 0; kb0 < p.num_kb; kb0 += CHUNK_KB) {
                 // the TMEM loads below are warp-collective: leave the loops only as a whole warp
-                const bool ready = mbar_wait(tfull_bar(acc), acc_phase, err, tag, 4);
+                const bool ready = mbar_wait_relaxed(tfull_bar(acc), acc_phase, err, tag, 4, 200);
                 if (!__all_sync(0xFFFFFFFFu, ready)) {
                     ok = false;
                     break;
@@ -312,7 +312,7 @@ tc_gemm_f32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         bool ok = true;
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
             for (int kb = 0; kb < p.num_kb; kb++) {
-                const bool landed = mbar_wait(full_bar(stage), phase, err, tag, 5);
+                const bool landed = mbar_wait_relaxed(full_bar(stage), phase, err, tag, 5, 40);
                 if (!__all_sync(0xFFFFFFFFu, landed)) {
                     ok = false;
                     break;

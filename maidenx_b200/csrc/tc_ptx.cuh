@@ -65,6 +65,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
     }
 }
 
+// The same bounded wait for roles in which many threads wait at once (whole warps of splitter or epilogue threads):
+// between polls the thread sleeps, so that a hundred spinning threads do not take shared-memory bandwidth and issue
+// slots from the TMA writes and the tensor core's operand reads.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, int* err, int tag, int code, unsigned sleep_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        for (int i = 0; i < 64; i++) {
+            __nanosleep(sleep_ns);
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (tc_err_mine(err, tag)) return false;
+        if (clock64() - t0 > TC_WAIT_BUDGET_CYCLES) {
+            tc_err_report(err, tag, code);
+            return false;
+        }
+    }
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
                  "l"(map), "r"(x), "r"(y), "r"(bar)

@@ -2,7 +2,8 @@
 
 Shapes, value ranges and layouts are the ones the target configurations name:
   * elementwise: 2^28-element tensors viewed as [16384, 16384]; contiguous, transposed lhs
-    (strides [1, 16384]) and rhs broadcast from [1, 16384] (strides [0, 1]); add/sub/mul/div
+    (strides [1, 16384]), rhs broadcast from [1, 16384] (strides [0, 1]) and contiguous views that
+    start at element 1 of their buffers (the reference's test fixtures); add/sub/mul/div
     and exp/relu/gelu/neg in f32 / bf16 / f16, add/mul in i32;
   * reductions: [8192, 16384] sum along dim 0 and dim 1, mean, max in f32 / bf16, i32 sum,
     and the sum_to_shape fold [64, 512, 4096] -> [1, 1, 4096];
@@ -38,23 +39,27 @@ def elementwise_cases(R: int = 16384, C: int = 16384, dtypes=("f32", "bf16", "f1
         "contiguous": ([R, C, C, 1, C, 1, 0, 0], n, n),
         "transposed_lhs": ([R, C, 1, R, C, 1, 0, 0], n, n),
         "rhs_broadcast": ([R, C, C, 1, 0, 1, 0, 0], n, C),
+        # both operands viewed from element 1 of their buffers, as every fixture of the reference's test-suite is
+        # (crates/maidenx_tensor/tests/utils/mod.rs:30-37): contiguous, but not 16-byte aligned
+        "offset1": ([R, C, C, 1, C, 1, 1, 1], n + 1, n + 1),
     }
     layouts_u = {
         "contiguous": ([R, C, C, 1, 0], n),
         "transposed": ([R, C, 1, R, 0], n),
         "broadcast": ([R, C, 0, 1, 0], C),
+        "offset1": ([R, C, C, 1, 1], n + 1),
     }
     for dt in dtypes:
         s = ELEM_SIZE[dt]
         for op in ("add", "sub", "mul", "div"):
             for lname, (meta, la, lb) in layouts_b.items():
-                cases.append(Case(f"{op}_{dt}/{lname}", op, dt, "binary", meta, n, [la, lb], n, (la + lb + n) * s))
+                cases.append(Case(f"{op}_{dt}/{lname}", op, dt, "binary", meta, n, [la, lb], n, (min(la, n) + min(lb, n) + n) * s))
         for op in ("exp", "relu", "gelu", "neg"):
             for lname, (meta, la) in layouts_u.items():
-                cases.append(Case(f"{op}_{dt}/{lname}", op, dt, "unary", meta, n, [la], n, (la + n) * s))
+                cases.append(Case(f"{op}_{dt}/{lname}", op, dt, "unary", meta, n, [la], n, (min(la, n) + n) * s))
     for op in ("add", "mul"):
         for lname, (meta, la, lb) in layouts_b.items():
-            cases.append(Case(f"{op}_i32/{lname}", op, "i32", "binary", meta, n, [la, lb], n, (la + lb + n) * 4))
+            cases.append(Case(f"{op}_i32/{lname}", op, "i32", "binary", meta, n, [la, lb], n, (min(la, n) + min(lb, n) + n) * 4))
     return cases
 
 

@@ -40,6 +40,8 @@ def fwd_cases():
     add("mm-odd", [65, 33], [65, 70], [70, 33])
     add("mm-tiles", [128, 192], [128, 96], [96, 192])
     add("mm-tall-k", [7, 5], [7, 1000], [1000, 5])
+    add("long-k", [3, 2], [3, 5000], [5000, 2])                            # few outputs, long reduction: one block per output element
+    add("long-k-tn", [1, 3], [1, 10000], [10000, 3], ast=[1, 1])           # the weight gradient of the README example
     add("nt-linear", [50, 24], [50, 40], [40, 24], bst=[1, 40])            # x . W^T with W [24, 40]
     add("tn", [30, 20], [30, 16], [16, 20], ast=[1, 30])
     add("batched", [3, 20, 17], [3, 20, 30], [3, 30, 17])
@@ -85,7 +87,8 @@ def test_matmul_forward(oracle, cuda, dt):
         # f32 products large enough for the tensor cores run on split tf32 operands: summation order and the
         # last bits differ from element-type accumulation, so they are held to the stated 1e-4 against the wide oracle
         f32_tc = dt.name == "f32" and name.startswith("tc-")
-        binding.set_wide(dt.name in ("bf16", "f16") or f32_tc)
+        long_k = name.startswith("long-k") and dt.kind == "float"   # summed in a different order than the element-type loop
+        binding.set_wide(dt.name in ("bf16", "f16") or f32_tc or long_k)
         try:
             ref = H.run_matmul(oracle, dt, meta, n, a, b)
         finally:
@@ -93,6 +96,8 @@ def test_matmul_forward(oracle, cuda, dt):
         got = H.run_matmul(cuda, dt, meta, n, a, b)
         if dt.name in ("bf16", "f16"):
             H.assert_same("matmul", dt, got, ref, float_rel=2e-2, what=name, scale=np.sqrt(a_sh[-1]))
+        elif long_k:
+            H.assert_same("matmul", dt, got, ref, float_rel=1e-4 if dt.name == "f32" else 1e-12, what=name, scale=10 * np.sqrt(a_sh[-1]))
         elif f32_tc:
             H.assert_same("matmul", dt, got, ref, float_rel=1e-4, what=name, scale=np.sqrt(a_sh[-1]))
             # split tf32 is far inside that bound (a few 1e-6: the tensor core's truncating accumulation over one

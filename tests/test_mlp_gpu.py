@@ -183,3 +183,43 @@ def test_input_pipeline_delivers_batches_in_order(cuda):
         seen.append((float(out[0]), float(out[-1]), float(xb[n // 2])))
     assert seen == [(float(i), float(i), float(-i)) for i in range(5)]
     assert device.last_error() is None
+
+
+def test_one_training_step_matches_the_oracle_composed_model(cuda):
+    """The engine against oracle/mlp_reference.py - the op-by-op composition on the CPU oracle that the benchmark's CPU
+    arm times - from the engine's own weights: loss, network output, every gradient and the updated weights."""
+    from maidenx_b200.mlp import Mlp
+    from oracle import binding, mlp_reference
+    L, Dm, B, seed, lr = 3, 256, 512, 9, 0.05
+    rng = np.random.default_rng(8)
+    dt = D.BF16
+    x, y = H.random_store(rng, dt, B * Dm, dist="normal"), H.random_store(rng, dt, B * Dm, dist="normal")
+    xb, yb = device.CudaBuffer.from_host(x), device.CudaBuffer.from_host(y)
+    m = Mlp(L, Dm, B, "bf16", seed)
+    W = [device_read(m.ptr("weight", l), np.uint16, Dm * Dm) for l in range(L)]
+    b = [D.encode(device_read(m.ptr("master_bias", l), np.float32, 1), dt) for l in range(L)]
+    ref = mlp_reference.CpuMlp(L, Dm, B, "bf16", [w.copy() for w in W], [v.copy() for v in b])
+    binding.set_wide(True)   # f32 accumulation, as the tensor-core products and the fused passes accumulate
+    try:
+        loss, gWs, gbs = ref.gradients(x, y)
+    finally:
+        binding.set_wide(False)
+    m.train_step(xb.ptr, yb.ptr, lr)
+    device.synchronize()
+    assert device.last_error() is None
+    assert np.isclose(m.loss(), float(D.decode(loss, dt)[0]), rtol=1e-2)   # the oracle's loss is a bf16 scalar
+    out = device_read(m.ptr("output"), np.uint16, B * Dm)
+    H.assert_same("mlp output", dt, out, ref.last_output, float_rel=2e-2, scale=0.25, what="output")
+    for l in range(L):
+        g = device_read(m.ptr("weight_grad", l), np.uint16, Dm * Dm)
+        # The oracle evaluates the GELU derivative as the reference's chain of ~15 elementwise ops, each rounded to bf16
+        # (crates/maidenx_tensor/src/ops/unary.rs:324-346); the engine evaluates it once in f32.  The per-op 2e-2 compounds
+        # along that chain, so gradients are held to 5e-2 of max(|ref|, a quarter of the largest entry).
+        scale = 0.25 * np.abs(D.decode(gWs[l], dt)).max()
+        H.assert_same("mlp dW", dt, g, gWs[l], float_rel=5e-2, scale=scale, what=f"dW layer {l}")
+        gb = D.decode(device_read(m.ptr("bias_grad", l), np.uint16, 1), dt)[0]
+        want = D.decode(gbs[l], dt)[0]
+        assert abs(gb - want) <= 5e-2 * max(abs(want), 1e-3), f"db layer {l}"
+    m.close()
+    xb.free()
+    yb.free()

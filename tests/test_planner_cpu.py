@@ -7,7 +7,7 @@ import numpy as np
 
 from maidenx_b200 import _lib
 
-FLAT, ROW, TILE, GENERIC, SERIAL = 1, 2, 3, 4, 5
+FLAT, ROW, TILE, GENERIC, SERIAL, FLAT_SHIFT = 1, 2, 3, 4, 5, 7
 ROWS, COLS, SCATTER = 1, 2, 3
 BASE = 0x7F0000000000  # a 256-byte aligned pretend device address: the planner only looks at alignment
 
@@ -35,9 +35,9 @@ def test_benchmark_layouts_take_their_kernels():
 
 
 def test_odd_layouts_degrade_gracefully():
-    # offset 1 (the layout of the reference's test fixtures) breaks 16-byte alignment: the vector kernels are
-    # not legal and the call takes the per-element gather kernel - correct, but not a bandwidth path
-    assert ew_plan([1000, 1, 1, 1, 1], 1, 1000)[:3] == (GENERIC, 1, 0)
+    # offset 1 (the layout of the reference's test fixtures) breaks 16-byte alignment: the call takes the flat kernel's
+    # shifted form (aligned 16-byte loads + funnel shift), not the per-element gather
+    assert ew_plan([1000, 1, 1, 1, 1], 1, 1000)[:3] == (FLAT_SHIFT, 1, 1)
     # the same view at an aligned offset is flat again
     assert ew_plan([1000, 1, 1, 4, 8], 1, 1000)[:3] == (FLAT, 1, 1)
     # a permuted 3-d view has no unit-stride pairing the tile kernel handles
