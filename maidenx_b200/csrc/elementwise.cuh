@@ -173,25 +173,18 @@ __device__ __forceinline__ uint4 shift_pair(const uint4& lo, const uint4& hi, ui
     }
 }
 
-// VEC elements starting at an arbitrary element-aligned address p, for a warp whose lanes hold CONSECUTIVE vectors: each
-// lane loads the aligned 16-byte word its vector starts in; the word the vector ends in is the next lane's word and
-// comes over by shuffle (only the last valid lane of the warp loads it itself), so a shifted operand costs one global
-// load per vector, not two.  `sh` = p modulo 16 (the same for every vector of a launch).  Every lane of the warp must
-// call this; `valid` says whether this lane has a vector, `next_valid` whether the next lane has one.  Both words
-// contain at least one byte of a valid vector, so no load leaves the allocation.
+// VEC elements starting at an arbitrary element-aligned address: the two aligned 16-byte words the vector straddles,
+// shifted together.  `sh` = the address modulo 16 (the same for every vector of a launch).  Both words contain at
+// least one byte of the vector, so neither load leaves the allocation.  The second word is the next lane's first
+// word, so it comes from L1; handing it over by warp shuffle instead was measured slower (four shuffles per operand
+// and vector cost more issue slots than the cached load).
 template <class T, int VEC>
-__device__ __forceinline__ Vec<T, VEC> ld_vec_shifted(const T* p, uint32_t sh, bool valid, bool next_valid) {
+__device__ __forceinline__ Vec<T, VEC> ld_vec_shifted(const T* p, uint32_t sh) {
     static_assert(sizeof(T) * VEC == 16, "one 16-byte vector");
     const uintptr_t addr = reinterpret_cast<uintptr_t>(p) - sh;
-    uint4 lo = make_uint4(0, 0, 0, 0);
-    if (valid) lo = *reinterpret_cast<const uint4*>(addr);
+    const uint4 lo = *reinterpret_cast<const uint4*>(addr);
     if (sh == 0) return *reinterpret_cast<const Vec<T, VEC>*>(&lo);
-    uint4 hi;
-    hi.x = __shfl_down_sync(0xFFFFFFFFu, lo.x, 1);
-    hi.y = __shfl_down_sync(0xFFFFFFFFu, lo.y, 1);
-    hi.z = __shfl_down_sync(0xFFFFFFFFu, lo.z, 1);
-    hi.w = __shfl_down_sync(0xFFFFFFFFu, lo.w, 1);
-    if (valid && ((threadIdx.x & 31) == 31 || !next_valid)) hi = *reinterpret_cast<const uint4*>(addr + 16);
+    const uint4 hi = *reinterpret_cast<const uint4*>(addr + 16);
     const uint4 r = shift_pair(lo, hi, sh);
     return *reinterpret_cast<const Vec<T, VEC>*>(&r);
 }
@@ -208,10 +201,11 @@ __global__ void __launch_bounds__(kEwThreads) ew_flat_shift_kernel(F f, const T*
 #pragma unroll
     for (int u = 0; u < kEwUnroll; u++) {
         const uint64_t v = v0 + (uint64_t)u * kEwThreads;
-        const bool valid = v < body_vecs, next_valid = v + 1 < body_vecs;
-        const uint64_t i = head + v * VEC;
-        va[u] = sa ? ld_vec_shifted<T, VEC>(a + i, sha, valid, next_valid) : splat<T, VEC>(a[0]);
-        if constexpr (NIN == 2) vb[u] = sb ? ld_vec_shifted<T, VEC>(b + i, shb, valid, next_valid) : splat<T, VEC>(b[0]);
+        if (v < body_vecs) {
+            const uint64_t i = head + v * VEC;
+            va[u] = sa ? ld_vec_shifted<T, VEC>(a + i, sha) : splat<T, VEC>(a[0]);
+            if constexpr (NIN == 2) vb[u] = sb ? ld_vec_shifted<T, VEC>(b + i, shb) : splat<T, VEC>(b[0]);
+        }
     }
 #pragma unroll
     for (int u = 0; u < kEwUnroll; u++) {
