@@ -281,12 +281,14 @@ int mx_tc_gemm_status(void);
 /* Number of metadata blocks currently remembered by cuda_memcpy_h2d (diagnostics). */
 int mx_metadata_table_size(void);
 
-/* cuda_sum_f32 for callers that must not allocate (inside a stream capture, in a latency-critical
- * loop, or with all device memory owned by their own allocator).  No counterpart in the reference.
+/* cuda_sum_f32 for callers that must not allocate (in a latency-critical loop that has to stay free of
+ * driver allocation calls, with all device memory owned by their own allocator, or where the allocating
+ * runtime calls are not permitted).  No counterpart in the reference.
  * Same arguments as cuda_sum_f32 except that `metadata` must be host memory.  The second-pass
  * workspace is a fixed 1 MiB array inside the library (held on every GPU that loads it); a reduction
  * whose partials do not fit is rejected with status 3 and leaves `out` untouched.  The first call on
- * a device resolves the array's address and should come before any stream capture; calls share the
+ * a device does the set-up (address of the array, SM count, occupancy) and should come before any stream
+ * capture; calls share the
  * array, so calls that overlap on one GPU race.  Details: maidenx_b200/csrc/noalloc.cu. */
 void mx_sum_f32_noalloc(size_t num_els, size_t num_dims, size_t num_red_dims, const size_t* metadata, const mx_f32* inp, mx_f32* out);
 

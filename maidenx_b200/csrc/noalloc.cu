@@ -1,11 +1,11 @@
 // mx_sum_f32_noalloc: cuda_sum_f32 for callers that must not allocate.
 //
 // The regular reductions take their second-pass workspace from a cudaMalloc'ed scratch block
-// that grows on demand.  Some callers cannot tolerate that: code running inside a CUDA stream
-// capture (cudaMalloc and the implicit synchronisation of cudaFree are not capturable), a
-// latency-critical loop that has to stay free of driver allocation calls, or a process that
-// has handed all device memory to its own allocator.  This entry point computes the same
-// result with the workspace in a fixed array that is part of the library image.
+// that grows on demand.  Some callers cannot tolerate that: a latency-critical loop that has to
+// stay free of driver allocation calls (cudaMalloc may block, cudaFree synchronises the device),
+// a process that has handed all device memory to its own allocator, or code that runs where the
+// allocating runtime calls are not permitted.  This entry point computes the same sum with the
+// workspace in a fixed array that is part of the library image.
 //
 // Contract
 //   * Arguments are those of cuda_sum_f32, except that `metadata` must be HOST memory
@@ -17,8 +17,9 @@
 //     fit is rejected: mx_last_error() == 3 (unsupported) and the output is left untouched.
 //     (Rows/columns reductions need splits * outputs * 4 bytes; the scatter path, used for
 //     several reduced dims or a non-contiguous input, needs outputs * 4 bytes.)
-//   * The first call on each device looks up the array's device address (cudaGetSymbolAddress,
-//     with that device current).  Make that first call before starting a stream capture.
+//   * The first call on each device does the set-up: it looks up the array's device address
+//     (cudaGetSymbolAddress, with that device current) and queries the SM count and the kernels'
+//     occupancy.  Make that first call before starting any stream capture.
 //   * All calls share the array.  Every element a call reads was written by that same call
 //     (partials are overwritten, the scatter workspace is re-initialised by its fill kernel),
 //     so leftovers from earlier calls are harmless; but two calls that overlap on the GPU —
@@ -112,7 +113,9 @@ extern "C" void mx_sum_f32_noalloc(size_t num_els, size_t num_dims, size_t num_r
         const u64 O = pl.O, R = pl.R;
         const bool vec = base_aligned && R % VEC == 0;
         const u64 unit = (u64)kRedThreads * VEC * 4;
-        // same split selection as cuda_sum_f32, so both entry points round identically
+        // same split selection as cuda_sum_f32's block kernel; where cuda_sum_f32 would pick its per-thread or per-warp
+        // kernels (very short rows, or many short rows) the two entry points add in a different order and agree
+        // within the reduction tolerance, not bit for bit
         static int occ = 0;
         if (!occ) occ = resident_blocks((const void*)reduce_rows_block_kernel<f32, RED_SUM, VEC>, kRedThreads);
         u64 want = split_count(O, (u64)sms * occ);

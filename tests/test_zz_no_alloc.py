@@ -1,6 +1,6 @@
-"""mx_sum_f32_noalloc — the reduction for callers that cannot allocate device memory (code under
-stream capture, allocation-free hot loops, processes whose allocator owns the whole GPU) — must
-give exactly what cuda_sum_f32 gives, call after call, from its fixed in-library workspace.
+"""mx_sum_f32_noalloc — the reduction for callers that cannot allocate device memory (hot loops
+that must stay free of driver allocation calls, processes whose allocator owns the whole GPU) —
+must give what cuda_sum_f32 gives, call after call, from its fixed in-library workspace.
 
 This file is named to be collected last, so a run that stops at the first failure has already
 executed every other test.  It passes alone in a fresh process and after the rest of the suite.
@@ -77,3 +77,41 @@ def test_noalloc_rejects_reductions_beyond_its_workspace_and_device_metadata():
     lib.mx_clear_error()
     for b in (x, out, mdev):
         b.free()
+
+
+def test_noalloc_paths_the_first_test_does_not_reach(oracle):
+    """Against the CPU oracle (wide accumulation, 1e-4 of max(|ref|, sqrt(terms))): the scatter path (two reduced
+    dims), more rows than a grid has y-blocks, rows shorter than a warp, and an input that starts at element 1."""
+    import harness as H
+    from maidenx_b200 import dtypes as D
+    from oracle import binding
+    lib = _lib.load()
+    rng = np.random.default_rng(43)
+    cases = [
+        # dims, strides, reduced lens, reduced strides, offset, terms per output
+        ([6, 5, 7], [35, 7, 1], [6, 7], [35, 1], 0, 42),        # two reduced dims: scatter path, workspace zero-filled per call
+        ([70000, 40], [40, 1], [40], [1], 0, 40),               # 70000 rows: beyond the grid's y limit
+        ([5000, 7], [7, 1], [7], [1], 0, 7),                    # rows shorter than a warp
+        ([300, 1000], [1000, 1], [1000], [1], 1, 1000),         # the reference's fixture layout: offset 1, not 16-byte aligned
+        ([2000, 96], [96, 1], [2000], [96], 1, 2000),           # column fold at offset 1
+    ]
+    for _ in range(2):
+        for dims, strides, rl, rs, off, terms in cases:
+            n = int(np.prod(dims))
+            x = rng.standard_normal(n + off).astype(np.float32)
+            n_out = n // int(np.prod(rl))
+            binding.set_wide(True)
+            try:
+                ref = H.run_reduce(oracle, "sum", D.F32, dims, strides, rl, rs, off, x)
+            finally:
+                binding.set_wide(False)
+            xb = device.CudaBuffer.from_host(x)
+            ob = device.CudaBuffer.from_host(np.full(n_out, 9.0, np.float32))
+            meta = np.asarray(dims + strides + rl + rs + [off], dtype=np.uint64)
+            lib.mx_sum_f32_noalloc(n, len(dims), len(rl), meta.ctypes.data, xb.ptr, ob.ptr)
+            device.synchronize()
+            assert device.last_error() is None, (dims, device.last_error())
+            got = ob.to_host(np.float32, n_out)
+            xb.free()
+            ob.free()
+            H.assert_same("sum", D.F32, got, ref, float_rel=1e-4, scale=np.sqrt(terms), what=f"noalloc {dims} reduce {rl} offset {off}")
