@@ -697,6 +697,7 @@ def config1_row(torch, lib, steps=200, with_cpu=True):
         from oracle import binding
         binding.load()
         binding.set_num_threads(os.cpu_count() or 1)
+        binding.set_reduce_parallel(True)  # the reference's reductions: a parallel loop with one lock per output element
         t0 = time.perf_counter()
         cl, cW, cb = E.train(OracleEngine(), steps)
         dt_s = time.perf_counter() - t0
@@ -710,10 +711,11 @@ def config1_row(torch, lib, steps=200, with_cpu=True):
 # ---------------------------------------------------------------------------------------
 MLP_LAYERS, MLP_DIM, MLP_GLOBAL_BATCH, MLP_LR = 4, 8192, 16384, 1e-3
 MLP_GEMMS_PER_STEP = 3 * MLP_LAYERS - 1       # dX of the first layer is not needed and not computed
-# kernels launched per step: 11 GEMMs + 4 bias(/gelu) passes + 2 (mse, mse finish) + 3 gelu backward
-# + 4 bias-gradient sums (partials folded inside the same launch) + 8 SGD updates (weights and bias per layer);
-# with the NVLink exchange the 8 SGD launches become 4 x (barrier, fused reduce + update, barrier)
-MLP_KERNELS_PER_STEP = MLP_GEMMS_PER_STEP + MLP_LAYERS + 2 + (MLP_LAYERS - 1) + MLP_LAYERS + 2 * MLP_LAYERS
+# kernels launched per step: 11 GEMMs (the 4 forward ones carry the bias add and GELU in their epilogue) + 2 (mse,
+# mse finish) + 3 gelu backward + 4 bias-gradient sums (partials folded inside the same launch) + 8 SGD updates (weights
+# and bias per layer; on a side stream at N = 1); with the NVLink exchange the 8 SGD launches become
+# 4 x (barrier, fused reduce + update, barrier)
+MLP_KERNELS_PER_STEP = MLP_GEMMS_PER_STEP + 2 + (MLP_LAYERS - 1) + MLP_LAYERS + 2 * MLP_LAYERS
 
 
 EXCHANGE_TEXT = {
@@ -946,6 +948,7 @@ def main():
     ap.add_argument("--exchange", default="auto", choices=["auto", "multimem-exclusive", "copy", "multimem", "peer", "nccl"],
                     help="N > 1: how gradients are exchanged (auto: the library's NVLink kernels, NCCL if symmetric memory is unavailable)")
     ap.add_argument("--exchange-sms", type=int, default=8, help="multimem-exclusive: SMs given to the exchange kernel")
+    ap.add_argument("--cta-group", type=int, default=2, choices=[1, 2], help="bf16 / f16 tensor-core products: 2 = pairs of CTAs share the B tile (default), 1 = one CTA per tile")
     ap.add_argument("--only-case", default=None, help="profiling aid: launch just this sweep case --steps times and exit")
     ap.add_argument("--small", action="store_true", help="profiling aid: 8192x8192 / quarter-size tensors for ncu captures")
     args = ap.parse_args()
@@ -964,6 +967,7 @@ def main():
     torch.cuda.set_device(local_rank)
     lib = lib_mod.load()  # raises if the CUDA library is not built: there is no fallback
     assert lib.cuda_set_device(local_rank) == 0
+    lib.mx_set_gemm_cta_group(args.cta_group)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks = measured_peaks()

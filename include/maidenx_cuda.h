@@ -304,6 +304,14 @@ void mx_sum_f32_noalloc(size_t num_els, size_t num_dims, size_t num_red_dims, co
 MX_DECL_FUSED_T(bf16, _)
 MX_DECL_FUSED_T(f16, _)
 MX_DECL_FUSED_T(f32, _)
+/* Linear forward in one call: u[rows, out] = x[rows, in] . w[out, in]^T + bias (one element), act = gelu(u); act may be
+ * NULL.  Large layers run the product on the tensor cores with the bias add and the activation in its epilogue; the
+ * results are the bits of cuda_matmul, cuda_add and cuda_gelu applied one after the other
+ * (crates/maidenx_nn/src/layers/linear.rs:60-81). */
+void mx_linear_bias_gelu_bf16(size_t rows, size_t in_features, size_t out_features, const mx_bf16* x, const mx_bf16* w, const mx_bf16* bias,
+                              mx_bf16* u, mx_bf16* act);
+void mx_linear_bias_gelu_f16(size_t rows, size_t in_features, size_t out_features, const mx_f16* x, const mx_f16* w, const mx_f16* bias,
+                             mx_f16* u, mx_f16* act);
 
 /* ---- Conv2d forward / backward composed from the ops above (maidenx_b200/csrc/conv2d_layer.cu) ---------------
  * The call sequence of the reference's layer (crates/maidenx_nn/src/layers/conv.rs:185-307,333-420): im2col,
@@ -339,6 +347,10 @@ void mx_mlp_forward(void* mlp, const void* x);
 void mx_mlp_loss_backward(void* mlp, const void* y);
 void mx_mlp_backward_layer(void* mlp, int layer);
 void mx_mlp_sgd_layer(void* mlp, int layer, float lr, float grad_scale);
+/* forward, loss, backward and the optimizer update of every layer in one call (single-device engine); the updates run
+ * on a side stream beside the backward of the layers below.  mx_mlp_dp_join makes the calling thread's stream wait for
+ * them (the next mx_mlp_train_step / mx_mlp_forward waits by itself). */
+void mx_mlp_train_step(void* mlp, const void* x, const void* y, float lr, float grad_scale);
 void* mx_mlp_weight_grad(void* mlp, int layer);
 void* mx_mlp_bias_grad(void* mlp, int layer);
 float* mx_mlp_master_weight(void* mlp, int layer);
@@ -389,6 +401,9 @@ int mx_mlp_dp_set_exchange(void* mlp, int mode, int exclusive_sms);
 /* The tensor-core GEMM of the calling thread launches at most `sms` CTAs (0: all SMs), leaving the other SMs to a
  * concurrent kernel such as the exchange above. */
 void mx_set_gemm_sm_limit(int sms);
+/* 2 (default): bf16 / f16 products on the tensor cores run as pairs of CTAs on neighbouring SMs that share the B tile
+ * (tcgen05.mma.cta_group::2); 1: one CTA per tile.  Same results either way; process-wide. */
+void mx_set_gemm_cta_group(int ctas);
 
 #ifdef __cplusplus
 }

@@ -41,6 +41,7 @@ RUNTIME_SIGNATURES = {
     "mx_mlp_loss_backward": ([ctypes.c_void_p, ctypes.c_void_p], None),
     "mx_mlp_backward_layer": ([ctypes.c_void_p, ctypes.c_int], None),
     "mx_mlp_sgd_layer": ([ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_float], None),
+    "mx_mlp_train_step": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_float], None),
     "mx_mlp_weight_grad": ([ctypes.c_void_p, ctypes.c_int], ctypes.c_void_p),
     "mx_mlp_bias_grad": ([ctypes.c_void_p, ctypes.c_int], ctypes.c_void_p),
     "mx_mlp_master_weight": ([ctypes.c_void_p, ctypes.c_int], ctypes.c_void_p),
@@ -60,6 +61,7 @@ RUNTIME_SIGNATURES = {
     "mx_mlp_dp_join": ([ctypes.c_void_p], None),
     "mx_mlp_dp_set_exchange": ([ctypes.c_void_p, ctypes.c_int, ctypes.c_int], ctypes.c_int),
     "mx_set_gemm_sm_limit": ([ctypes.c_int], None),
+    "mx_set_gemm_cta_group": ([ctypes.c_int], None),
     "mx_set_small_pool": ([ctypes.c_int], None),
     "mx_debug_elementwise_plan": ([ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t,
                                    ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
@@ -101,6 +103,9 @@ def load() -> ctypes.CDLL:
         fn.argtypes = args
         fn.restype = res
     P, S, F = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
+    for t in ("bf16", "f16"):
+        fn = getattr(lib, f"mx_linear_bias_gelu_{t}")
+        fn.argtypes, fn.restype = [S, S, S, P, P, P, P, P], None
     for t in ("bf16", "f16", "f32"):
         for name, args in (("mx_bias_gelu", [S, P, P, P, P]), ("mx_gelu_backward", [S, P, P, P]),
                            ("mx_mse_loss_grad", [S, P, P, P, P]), ("mx_sgd_update", [S, P, P, P, F, F])):

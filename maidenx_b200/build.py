@@ -46,7 +46,7 @@ def _register_optional():
     for name, dts in (("reduction.cu", ARITH), ("matmul_simt.cu", ARITH), ("conv.cu", FLOATS), ("extras.cu", ARITH)):
         if (CSRC / name).exists():
             PER_DTYPE_SOURCES[name] = dts
-    for name in ("reduce_plan.cu", "matmul_plan.cu", "matmul_tc.cu", "matmul_tc_f32.cu", "fused.cu", "mlp.cu", "noalloc.cu", "dp_sync.cu", "cast.cu", "conv2d_layer.cu"):
+    for name in ("reduce_plan.cu", "matmul_plan.cu", "matmul_tc.cu", "matmul_tc2.cu", "matmul_tc_f32.cu", "fused.cu", "mlp.cu", "noalloc.cu", "dp_sync.cu", "cast.cu", "conv2d_layer.cu"):
         if (CSRC / name).exists() and name not in SINGLE_SOURCES:
             SINGLE_SOURCES.append(name)
 

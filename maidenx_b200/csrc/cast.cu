@@ -10,8 +10,7 @@
 //   u8 / i8 -> 16-bit float  exact; wider integers -> 16-bit float keep only their low byte (`as u8` / `as i8`
 //                            comes first in the reference)
 //   int -> int               truncate or sign-/zero-extend
-// Buffers are dense (the reference casts whole buffers); each thread converts one 16-byte vector of the
-// source: HBM-bound, sizeof(from) + sizeof(to) bytes per element.
+// Buffers are dense (the reference casts whole buffers): HBM-bound, sizeof(from) + sizeof(to) bytes per element.
 #include "abi_common.cuh"
 #include "ops.cuh"
 
@@ -46,29 +45,47 @@ __device__ __forceinline__ To cast_one(From x) {
 
 constexpr int kCastThreads = 256;
 
+// N bytes moved as one access (N a power of two, 1 .. 16)
+template <int N>
+struct CastWord;
+template <>
+struct CastWord<16> { typedef uint4 type; };
+template <>
+struct CastWord<8> { typedef uint2 type; };
+template <>
+struct CastWord<4> { typedef uint32_t type; };
+template <>
+struct CastWord<2> { typedef uint16_t type; };
+template <>
+struct CastWord<1> { typedef uint8_t type; };
+
+// Each thread converts VEC = 16 / max(sizeof(From), sizeof(To)) elements per step, so that the WIDER side moves as
+// full 16-byte vectors and the narrower side as one contiguous 8-, 4-, 2- or 1-byte piece per lane: every warp-level
+// load and store is a dense run of bytes (a widening cast used to store two 16-byte halves 32 bytes apart per lane,
+// which half-filled every sector it touched).  Four steps are in flight per thread.
 template <class From, class To>
 __global__ void __launch_bounds__(kCastThreads) cast_kernel(const From* __restrict__ in, To* __restrict__ out, u64 n, int vector_ok) {
-    constexpr int VEC = 16 / (int)sizeof(From);
+    constexpr int WIDE = sizeof(From) > sizeof(To) ? (int)sizeof(From) : (int)sizeof(To);
+    constexpr int VEC = 16 / WIDE;
+    constexpr int UNROLL = 4;
+    typedef typename CastWord<VEC * (int)sizeof(From)>::type InWord;
+    typedef typename CastWord<VEC * (int)sizeof(To)>::type OutWord;
     const u64 stride = (u64)gridDim.x * kCastThreads;
     const u64 nvec = vector_ok ? n / VEC : 0;
-    for (u64 v = (u64)blockIdx.x * kCastThreads + threadIdx.x; v < nvec; v += stride) {
-        const Vec<From, VEC> x = *reinterpret_cast<const Vec<From, VEC>*>(in + v * VEC);
-        Vec<To, VEC> y;
+    for (u64 v0 = (u64)blockIdx.x * kCastThreads + threadIdx.x; v0 < nvec; v0 += stride * UNROLL) {
+        InWord x[UNROLL];
 #pragma unroll
-        for (int j = 0; j < VEC; j++) y.v[j] = cast_one<From, To>(x.v[j]);
-        // the destination vector is VEC * sizeof(To) bytes: stored in 16-byte pieces (or one smaller piece)
-        constexpr int kBytes = VEC * (int)sizeof(To);
-        if constexpr (kBytes >= 16) {
-            const uint4* src = reinterpret_cast<const uint4*>(&y);
-            uint4* dst = reinterpret_cast<uint4*>(out + v * VEC);
+        for (int u = 0; u < UNROLL; u++)
+            if (v0 + u * stride < nvec) x[u] = *reinterpret_cast<const InWord*>(in + (v0 + u * stride) * VEC);
 #pragma unroll
-            for (int k = 0; k < kBytes / 16; k++) dst[k] = src[k];
-        } else if constexpr (kBytes == 8) {
-            *reinterpret_cast<uint2*>(out + v * VEC) = *reinterpret_cast<const uint2*>(&y);
-        } else if constexpr (kBytes == 4) {
-            *reinterpret_cast<uint32_t*>(out + v * VEC) = *reinterpret_cast<const uint32_t*>(&y);
-        } else {
-            *reinterpret_cast<uint16_t*>(out + v * VEC) = *reinterpret_cast<const uint16_t*>(&y);
+        for (int u = 0; u < UNROLL; u++) {
+            if (v0 + u * stride >= nvec) break;
+            const From* xs = reinterpret_cast<const From*>(&x[u]);
+            OutWord y;
+            To* ys = reinterpret_cast<To*>(&y);
+#pragma unroll
+            for (int j = 0; j < VEC; j++) ys[j] = cast_one<From, To>(xs[j]);
+            *reinterpret_cast<OutWord*>(out + (v0 + u * stride) * VEC) = y;
         }
     }
     for (u64 i = nvec * VEC + (u64)blockIdx.x * kCastThreads + threadIdx.x; i < n; i += stride) out[i] = cast_one<From, To>(in[i]);
@@ -77,9 +94,10 @@ __global__ void __launch_bounds__(kCastThreads) cast_kernel(const From* __restri
 template <class From, class To>
 void cast_entry(size_t n, const From* in, To* out, const char* where) {
     if (n == 0) return;
-    constexpr int VEC = 16 / (int)sizeof(From);
-    const bool vector_ok = ((uintptr_t)in) % 16 == 0 && ((uintptr_t)out) % (VEC * sizeof(To) >= 16 ? 16 : VEC * sizeof(To)) == 0;
-    u64 blocks = (n / VEC + kCastThreads - 1) / kCastThreads;
+    constexpr int WIDE = sizeof(From) > sizeof(To) ? (int)sizeof(From) : (int)sizeof(To);
+    constexpr int VEC = 16 / WIDE;
+    const bool vector_ok = ((uintptr_t)in) % (VEC * sizeof(From)) == 0 && ((uintptr_t)out) % (VEC * sizeof(To)) == 0;
+    u64 blocks = (n / VEC + (u64)kCastThreads * 4 - 1) / ((u64)kCastThreads * 4);
     const u64 cap = (u64)sm_count() * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;

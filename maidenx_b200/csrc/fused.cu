@@ -12,6 +12,7 @@
 // one rounding per stored value.
 #include "abi_common.cuh"
 #include "ops.cuh"
+#include "matmul_tc.cuh"
 
 namespace mx {
 
@@ -247,8 +248,24 @@ void sgd_launch(size_t n, float* w32, const T* g, T* w16, float lr, float grad_s
         mx::sgd_launch<mx_##T>(n, w32, grad, w16, lr, grad_scale, "mx_sgd_update_" #T);                                                 \
     }
 
+// Linear forward in one call: u[rows, out] = x[rows, in] . w[out, in]^T + bias (one element), act = gelu(u) (act may be NULL).
+// Large bf16 / f16 layers run the product on the tensor cores with bias and activation in its epilogue; any other
+// shape runs cuda_matmul into u followed by the in-place bias / activation pass.  Both give the bits of the three separate
+// ops of crates/maidenx_nn/src/layers/linear.rs:60-81 followed by gelu.
+#define DEF_LINEAR(T, IS_BF16)                                                                                                          \
+    void mx_linear_bias_gelu_##T(size_t rows, size_t in_features, size_t out_features, const mx_##T* x, const mx_##T* w, const mx_##T* bias, \
+                                 mx_##T* u, mx_##T* act) {                                                                              \
+        if (!rows || !in_features || !out_features) return;                                                                             \
+        if (mx::tc_linear_bias_act(IS_BF16, rows, in_features, out_features, x, w, bias, u, act, "mx_linear_bias_gelu_" #T)) return;       \
+        const size_t meta[] = {2, 2, 2, rows, out_features, rows, in_features, in_features, out_features, in_features, 1, 1, in_features, 0, 0}; \
+        cuda_matmul_##T(rows * out_features, meta, x, w, u);                                                                            \
+        mx::bias_gelu_launch<mx_##T>(rows * out_features, u, bias, u, act, "mx_linear_bias_gelu_" #T);                                    \
+    }
+
 extern "C" {
 DEF_FUSED(bf16)
 DEF_FUSED(f16)
 DEF_FUSED(f32)
+DEF_LINEAR(bf16, true)
+DEF_LINEAR(f16, false)
 }

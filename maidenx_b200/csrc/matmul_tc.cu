@@ -26,10 +26,12 @@
 // error word, stops issuing work and falls through to the common exit, where TMEM is freed.
 #include <cuda.h>
 
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 
 #include "matmul_tc.cuh"
+#include "matmul_tc2.cuh"
 #include "tc_ptx.cuh"
 
 namespace mx {
@@ -37,6 +39,10 @@ namespace mx {
 using namespace tc;
 
 namespace {
+
+// true: products go to the two-CTA kernel (matmul_tc2.cu); false (default): to the one-CTA kernel below.  On a B200 under
+// its power cap the two run at the same rate (the pair form only moves less data through shared memory).
+std::atomic<bool> g_two_cta{false};
 
 constexpr int BM = 128, BN = 256, BK = 64;    // CTA tile; BK * 2 bytes = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
@@ -82,6 +88,8 @@ struct TcParams {
     int a_batched, b_batched;  // 0: the operand is one matrix shared by every batch (third TMA coordinate stays 0)
     int is_bf16;
     int out_f32;  // split-K partial results: the epilogue stores the f32 accumulators unrounded
+    int fuse;     // 0: store the product; 1: u = round(round(product) + bias) through map_d; 2: also act = round(gelu(u)) through map_d2
+    const void* bias;  // fuse != 0: one element of the operand type in device memory
     int a_mn, b_mn;  // operand is MN-major in global memory ([K, MN] row-major) instead of K-major ([MN, K])
 };
 
@@ -107,9 +115,14 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// v rounded to the operand type and widened again
+__device__ __forceinline__ float round16(float v, int is_bf16) {
+    return is_bf16 ? to_f32(from_f32<bf16>(v)) : to_f32(from_f32<f16>(v));
+}
+
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_d,
-               TcParams p, int* err, int tag) {
+               const __grid_constant__ CUtensorMap map_d2, TcParams p, int* err, int tag) {
     extern __shared__ unsigned char tc_smem_raw[];
     // 128-byte swizzled TMA tiles and UMMA descriptors want 1024-byte aligned bases
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -226,6 +239,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         unsigned char* stage_buf = smem + SmemLayout::epi + ew * 2 * EPI_STAGE_BYTES;
         int acc = 0, buf = 0;
         uint32_t acc_phase = 0;
+        float fused_bias = 0.0f;
+        if (p.fuse) fused_bias = p.is_bf16 ? to_f32(*static_cast<const bf16*>(p.bias)) : to_f32(*static_cast<const f16*>(p.bias));
         for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
             int tm, tn, tb;
             tile_coords(tile, p, tm, tn, tb);
@@ -245,6 +260,50 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(tempty_bar(acc));
+                }
+                if (p.fuse) {
+                    // Linear + bias (+ GELU) in one pass, with the roundings of the separate ops: the product is rounded to
+                    // the operand type, the bias is added in f32 and rounded (u), the activation is evaluated on u in f32
+                    // and rounded (act) - bit for bit what cuda_matmul, cuda_add and cuda_gelu give one after the other.
+                    uint32_t act0[32], act1[32];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float u0 = round16(round16(__uint_as_float(v0[j]), p.is_bf16) + fused_bias, p.is_bf16);
+                        const float u1 = round16(round16(__uint_as_float(v1[j]), p.is_bf16) + fused_bias, p.is_bf16);
+                        v0[j] = __float_as_uint(u0);
+                        v1[j] = __float_as_uint(u1);
+                        if (p.fuse == 2) {
+                            act0[j] = __float_as_uint(gelu_f32_fast(u0));
+                            act1[j] = __float_as_uint(gelu_f32_fast(u1));
+                        }
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        if (h == 1 && p.fuse != 2) break;
+                        const uint32_t* w0 = h ? act0 : v0;
+                        const uint32_t* w1 = h ? act1 : v1;
+                        if (lane == 0) tma_store_wait_read<1>();
+                        __syncwarp();
+                        unsigned char* dst = stage_buf + buf * EPI_STAGE_BYTES + lane * 128;
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            const uint32_t* src = j < 4 ? &w0[j * 8] : &w1[(j - 4) * 8];
+                            uint4 q;
+                            q.x = pack2(__uint_as_float(src[0]), __uint_as_float(src[1]), p.is_bf16);
+                            q.y = pack2(__uint_as_float(src[2]), __uint_as_float(src[3]), p.is_bf16);
+                            q.z = pack2(__uint_as_float(src[4]), __uint_as_float(src[5]), p.is_bf16);
+                            q.w = pack2(__uint_as_float(src[6]), __uint_as_float(src[7]), p.is_bf16);
+                            *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = q;
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_3d(h ? &map_d2 : &map_d, smem_u32(stage_buf + buf * EPI_STAGE_BYTES), tn * BN + c * EPI_CHUNK_COLS, tm * BM + quarter * 32, tb);
+                            tma_store_commit();
+                        }
+                        buf ^= 1;
+                    }
+                    continue;
                 }
                 if (p.out_f32) {
                     // two 32-column f32 chunks (128 bytes per row each), one per staging buffer
@@ -340,7 +399,8 @@ bool opt_in_shared_memory() {
 
 // D[M,N] = sum_k Aop[m,k] * Bop[n,k].  A K-major operand is a dense row-major [MN, K] matrix, an
 // MN-major operand a dense row-major [K, MN] matrix; D is dense row-major [M, N].
-bool launch_gemm(bool is_bf16, const TcProduct& c, void* D, const char* where) {
+// fuse: 0 plain product; 1 D = round(round(product) + bias); 2 also D2 = round(gelu(D)) (see the kernel's epilogue)
+bool launch_gemm(bool is_bf16, const TcProduct& c, void* D, const char* where, int fuse = 0, const void* bias = nullptr, void* D2 = nullptr) {
     const void *A = c.A, *B = c.B;
     const bool a_mn = c.a_mn, b_mn = c.b_mn;
     const uint64_t M = c.m, N = c.n;
@@ -355,7 +415,7 @@ bool launch_gemm(bool is_bf16, const TcProduct& c, void* D, const char* where) {
     int grid = sm_count();
     if (ctx().gemm_sm_limit > 0 && ctx().gemm_sm_limit < grid) grid = ctx().gemm_sm_limit;
     // few output tiles, long reduction: cut K into slices that run as the batches of this launch
-    const int slices = batch == 1 ? splitk_slices((uint64_t)p.tiles_per_batch, K, BK, grid) : 1;
+    const int slices = (batch == 1 && !fuse) ? splitk_slices((uint64_t)p.tiles_per_batch, K, BK, grid) : 1;
     float* partial = nullptr;
     uint64_t a_bs = (uint64_t)c.a_bs, b_bs = (uint64_t)c.b_bs, a_pitch = 0, b_pitch = 0;
     if (slices > 1) {
@@ -375,10 +435,39 @@ bool launch_gemm(bool is_bf16, const TcProduct& c, void* D, const char* where) {
     const CUtensorMapDataType t16 = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
     CUtensorMap ma, mb, md;
+    if (g_two_cta.load(std::memory_order_relaxed) && grid >= 2 && !fuse) {
+        // the two-CTA kernel: B is staged in halves of 128 columns, a pair of CTAs owns a 256 x 256 tile
+        const bool oka2 = a_mn ? make_map_3d(&ma, t16, 2, A, K, M, batch, a_bs, 64, sw, a_pitch) : make_map_3d(&ma, t16, 2, A, M, K, batch, a_bs, tc2::BM, sw, a_pitch);
+        const bool okb2 = b_mn ? make_map_3d(&mb, t16, 2, B, K, N, batch, b_bs, 64, sw, b_pitch) : make_map_3d(&mb, t16, 2, B, N, K, batch, b_bs, tc2::BN_HALF, sw, b_pitch);
+        const bool okd2 = partial ? make_map_3d(&md, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, partial, M, N, batch, M * N, 32) : make_map(&md, is_bf16, D, M, N, batch, M * N, 32);
+        if (oka2 && okb2 && okd2) {
+            tc2::Params q;
+            q.tile_pairs_m = (p.tiles_m + 1) / 2;
+            q.tiles_n = p.tiles_n;
+            q.tiles_per_batch = q.tile_pairs_m * q.tiles_n;
+            q.num_tiles = (int)batch * q.tiles_per_batch;
+            q.num_kb = (int)((K + BK - 1) / BK);
+            q.a_batched = (batch > 1 && a_bs != 0) ? 1 : 0;
+            q.b_batched = (batch > 1 && b_bs != 0) ? 1 : 0;
+            q.is_bf16 = is_bf16 ? 1 : 0;
+            q.out_f32 = partial ? 1 : 0;
+            q.a_mn = a_mn ? 1 : 0;
+            q.b_mn = b_mn ? 1 : 0;
+            if (tc2::launch(ma, mb, md, q, grid, err, tag, ctx().stream)) {
+                check_launch(where);
+                if (partial) splitk_reduce(is_bf16 ? 0 : 1, partial, slices, (size_t)(M * N), D, where);
+                return true;
+            }
+        }
+    }
     const bool oka = a_mn ? make_map_3d(&ma, t16, 2, A, K, M, batch, a_bs, 64, sw, a_pitch) : make_map_3d(&ma, t16, 2, A, M, K, batch, a_bs, BM, sw, a_pitch);
     const bool okb = b_mn ? make_map_3d(&mb, t16, 2, B, K, N, batch, b_bs, 64, sw, b_pitch) : make_map_3d(&mb, t16, 2, B, N, K, batch, b_bs, BN, sw, b_pitch);
     const bool okd = partial ? make_map_3d(&md, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, partial, M, N, batch, M * N, 32) : make_map(&md, is_bf16, D, M, N, batch, M * N, 32);
     if (!oka || !okb || !okd) return false;
+    CUtensorMap md2 = md;
+    if (fuse == 2 && !make_map(&md2, is_bf16, D2, M, N, batch, M * N, 32)) return false;
+    p.fuse = fuse;
+    p.bias = bias;
     p.K = (int)K;
     p.num_tiles = (int)batch * p.tiles_per_batch;
     p.a_batched = (batch > 1 && a_bs != 0) ? 1 : 0;
@@ -389,7 +478,7 @@ bool launch_gemm(bool is_bf16, const TcProduct& c, void* D, const char* where) {
     p.a_mn = a_mn ? 1 : 0;
     p.b_mn = b_mn ? 1 : 0;
     if (grid > p.num_tiles) grid = p.num_tiles;
-    tc_gemm_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx().stream>>>(ma, mb, md, p, err, tag);
+    tc_gemm_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx().stream>>>(ma, mb, md, md2, p, err, tag);
     check_launch(where);
     if (partial) splitk_reduce(is_bf16 ? 0 : 1, partial, slices, (size_t)(M * N), D, where);
     return true;
@@ -665,6 +754,22 @@ bool tc_classify(const MmDesc& d, int which, size_t es, size_t num_els, size_t n
     return eligible(es, c.m, c.n, c.k, 1, c.a_mn, c.b_mn, c.A, c.B, out);
 }
 
+// x [rows, in] . w[out, in]^T with the bias add (and GELU) in the epilogue; false = shape not taken (the caller runs the ops one by one)
+bool tc_linear_bias_act(bool is_bf16, uint64_t rows, uint64_t in_features, uint64_t out_features, const void* x, const void* w, const void* bias,
+                        void* u, void* act, const char* where) {
+    TcProduct c;
+    c.A = static_cast<const char*>(x);
+    c.B = static_cast<const char*>(w);
+    c.a_mn = c.b_mn = false;
+    c.m = rows;
+    c.n = out_features;
+    c.k = in_features;
+    c.batch = 1;
+    c.a_bs = c.b_bs = 0;
+    if (!bias || !u || !eligible(2, c.m, c.n, c.k, 1, false, false, x, w, u) || (act && (uintptr_t)act % 16 != 0)) return false;
+    return launch_gemm(is_bf16, c, u, where, act ? 2 : 1, bias, act);
+}
+
 bool tc_gemm_bf16_f16(bool is_bf16, const MmDesc& d, int which, size_t num_els, size_t nea, size_t neb, const void* x, const void* y, void* out,
                       const char* where) {
     TcProduct c;
@@ -690,6 +795,8 @@ static int debug_forward_path(size_t es, size_t num_els, const size_t* host_meta
     if (k) *k = c.k;
     return (int)c.batch;
 }
+// 2: bf16 / f16 products run on the two-CTA kernel (pairs of SMs share the B tile); 1: on the one-CTA kernel.
+extern "C" void mx_set_gemm_cta_group(int ctas) { mx::g_two_cta.store(ctas == 2, std::memory_order_relaxed); }
 extern "C" int mx_debug_splitk_slices(size_t tiles, size_t k, int block_k, int sms) { return mx::tc::splitk_slices(tiles, k, block_k, sms); }
 extern "C" int mx_debug_matmul_forward_path(size_t num_els, const size_t* host_metadata, const void* a, const void* b, const void* out, int* a_mn_major,
                                             int* b_mn_major, size_t* m, size_t* n, size_t* k) {

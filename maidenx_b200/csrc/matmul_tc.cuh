@@ -23,6 +23,11 @@ bool tc_classify(const MmDesc& d, int which, size_t elem_size, size_t num_els, s
 
 bool tc_gemm_bf16_f16(bool is_bf16, const MmDesc& d, int which, size_t num_els, size_t nea, size_t neb, const void* x, const void* y, void* out,
                       const char* where);
+// Linear forward with its bias add and activation folded into the product's epilogue (bf16 / f16): u = x . w^T + bias and,
+// when `act` is not NULL, act = gelu(u), each rounded exactly as the separate ops round.  `bias` is one element in device
+// memory.  Returns false when the shape does not qualify for the tensor-core kernel; nothing was launched then.
+bool tc_linear_bias_act(bool is_bf16, uint64_t rows, uint64_t in_features, uint64_t out_features, const void* x, const void* w, const void* bias,
+                        void* u, void* act, const char* where);
 bool tc_gemm_f32(const MmDesc& d, int which, size_t num_els, size_t nea, size_t neb, const void* x, const void* y, void* out, const char* where);
 
 template <class T>

@@ -32,6 +32,8 @@ void mx_gelu_backward_bf16(size_t, const mx_bf16*, const mx_bf16*, mx_bf16*);
 void mx_gelu_backward_f16(size_t, const mx_f16*, const mx_f16*, mx_f16*);
 void mx_mse_loss_grad_bf16(size_t, const mx_bf16*, const mx_bf16*, mx_bf16*, float*);
 void mx_mse_loss_grad_f16(size_t, const mx_f16*, const mx_f16*, mx_f16*, float*);
+void mx_linear_bias_gelu_bf16(size_t, size_t, size_t, const mx_bf16*, const mx_bf16*, const mx_bf16*, mx_bf16*, mx_bf16*);
+void mx_linear_bias_gelu_f16(size_t, size_t, size_t, const mx_f16*, const mx_f16*, const mx_f16*, mx_f16*, mx_f16*);
 void mx_sgd_update_bf16(size_t, float*, const mx_bf16*, mx_bf16*, float, float);
 void mx_sgd_update_f16(size_t, float*, const mx_f16*, mx_f16*, float, float);
 void mx_dp_barrier(void* const*, size_t, int, int, uint32_t, uint32_t*, void*);
@@ -127,17 +129,16 @@ static void forward_t(Mlp* m, const T* x) {
     m->x = reinterpret_cast<const uint16_t*>(x);
     const T* prev = x;
     for (int l = 0; l < m->layers; l++) {
-        // data-parallel mode: the layer's weights of the previous step must have landed from every rank
-        if (m->dp) cudaStreamWaitEvent(ctx().stream, m->ev_done[l], 0);
-        // out [B, D], A [B, D] strides [D, 1], B = W^T view: shape [D, D] strides [1, D]
-        const size_t meta[] = {2, 2, 2, B, D, B, D, D, D, D, 1, 1, D, 0, 0};
-        matmul_call<T>(B * D, meta, prev, reinterpret_cast<const T*>(m->w16[l]), reinterpret_cast<T*>(m->z));
+        // the layer's weights of the previous step must have landed: from every rank in data-parallel mode, from the
+        // side stream's optimizer update in mx_mlp_train_step (an event that was never recorded does not block)
+        if (l < (int)m->ev_done.size()) cudaStreamWaitEvent(ctx().stream, m->ev_done[l], 0);
+        // u[l] = prev . W^T + bias, a[l] = gelu(u[l]): the product with bias and activation in its epilogue
         const bool last = l == m->layers - 1;
         T* act = last ? nullptr : reinterpret_cast<T*>(m->a[l]);
         if constexpr (std::is_same<T, bf16>::value)
-            mx_bias_gelu_bf16(B * D, reinterpret_cast<const T*>(m->z), reinterpret_cast<const T*>(m->b16[l]), reinterpret_cast<T*>(m->u[l]), act);
+            mx_linear_bias_gelu_bf16(B, D, D, prev, reinterpret_cast<const T*>(m->w16[l]), reinterpret_cast<const T*>(m->b16[l]), reinterpret_cast<T*>(m->u[l]), act);
         else
-            mx_bias_gelu_f16(B * D, reinterpret_cast<const T*>(m->z), reinterpret_cast<const T*>(m->b16[l]), reinterpret_cast<T*>(m->u[l]), act);
+            mx_linear_bias_gelu_f16(B, D, D, prev, reinterpret_cast<const T*>(m->w16[l]), reinterpret_cast<const T*>(m->b16[l]), reinterpret_cast<T*>(m->u[l]), act);
         prev = act;
     }
 }
@@ -265,7 +266,7 @@ static Mlp* mlp_create_impl(int layers, size_t dim, size_t batch, int dtype, uin
     m->loss = static_cast<float*>(dmalloc(m, 256));
     m->dp_err = static_cast<uint32_t*>(dmalloc(m, 256));
     ok = ok && m->z && m->d_act && m->du[0] && m->du[1] && m->loss && m->dp_err;
-    if (ok && peer) {
+    if (ok) {
         int lo = 0, hi = 0;
         cudaDeviceGetStreamPriorityRange(&lo, &hi);
         ok = cudaStreamCreateWithPriority(&m->side, cudaStreamNonBlocking, hi) == cudaSuccess;
@@ -365,6 +366,32 @@ void mx_mlp_sgd_layer(void* h, int l, float lr, float grad_scale) {
     if (m->is_bf16) sgd_layer_t<bf16>(m, l, lr, grad_scale);
     else sgd_layer_t<f16>(m, l, lr, grad_scale);
 }
+// One whole training step of the single-device engine.  The optimizer update of layer l is memory-bound and nothing
+// below it in the backward pass needs its result, so it runs on the side stream beside the backward products of the
+// layers below (which are bound by the tensor cores, not by HBM); the next forward waits, per layer, for that layer's
+// update only.  Readers of the weights after the step call mx_mlp_dp_join (or synchronise the device).
+void mx_mlp_train_step(void* h, const void* x, const void* y, float lr, float grad_scale) {
+    Mlp* m = static_cast<Mlp*>(h);
+    if (m->dp || !m->side) {
+        set_error(kErrUnsupported, 0, "mx_mlp_train_step");
+        return;
+    }
+    cudaStream_t main_stream = ctx().stream;
+    mx_mlp_forward(h, x);
+    mx_mlp_loss_backward(h, y);
+    for (int l = m->layers - 1; l >= 0; l--) {
+        mx_mlp_backward_layer(h, l);
+        cudaEventRecord(m->ev_grad[l], main_stream);
+        cudaStreamWaitEvent(m->side, m->ev_grad[l], 0);
+        ctx().stream = m->side;
+        if (m->is_bf16) sgd_layer_t<bf16>(m, l, lr, grad_scale);
+        else sgd_layer_t<f16>(m, l, lr, grad_scale);
+        ctx().stream = main_stream;
+        cudaEventRecord(m->ev_done[l], m->side);
+    }
+    check_launch("mx_mlp_train_step");
+}
+
 // One whole data-parallel training step: forward, loss, backward, and per layer the fused
 // gradient exchange + SGD update (dp_sync.cu) on a side stream, so that the exchange of layer l
 // runs beside the backward of the layers below it.  `grad_scale` multiplies the summed gradient
@@ -460,10 +487,10 @@ int mx_mlp_dp_set_exchange(void* h, int mode, int exclusive_sms) {
 }
 
 // The calling thread's stream waits (on the device) for the exchange of the last step.
+// Also valid for the single-device engine after mx_mlp_train_step (its updates run on the side stream).
 void mx_mlp_dp_join(void* h) {
     Mlp* m = static_cast<Mlp*>(h);
-    if (!m->dp) return;
-    for (int l = 0; l < m->layers; l++) cudaStreamWaitEvent(ctx().stream, m->ev_done[l], 0);
+    for (int l = 0; l < m->layers && l < (int)m->ev_done.size(); l++) cudaStreamWaitEvent(ctx().stream, m->ev_done[l], 0);
 }
 
 // Waits for the exchange of the last step and returns 0, or 1 + the peer rank a barrier stopped waiting for.

@@ -78,6 +78,10 @@ class Mlp:
 
     # --- one training step ---------------------------------------------------------------
     def train_step(self, x_ptr: int, y_ptr: int, lr: float, torch=None, dist=None, world: int = 1):
+        if world <= 1:
+            # one call: the optimizer update of each layer runs on a side stream beside the backward of the layers below
+            self.lib.mx_mlp_train_step(self.h, x_ptr, y_ptr, lr, 1.0)
+            return
         self.forward(x_ptr)
         self.loss_backward(y_ptr)
         works = []
@@ -95,6 +99,10 @@ class Mlp:
         else:
             for l in range(self.layers):
                 self.sgd_layer(l, lr, 1.0)
+
+    def join(self):
+        """Make the calling thread's stream wait for optimizer updates still running on the engine's side stream."""
+        self.lib.mx_mlp_dp_join(self.h)
 
 
 class DpMlp(Mlp):

@@ -291,3 +291,16 @@ def test_stale_device_wait_report_is_surfaced_and_does_not_poison_later_products
         lib.mx_clear_error()
         for x in bufs:
             x.free()
+
+
+@pytest.mark.parametrize("case", [BIG_FWD[0], BIG_FWD[3], BIG_FWD[6]], ids=lambda c: c[0])
+def test_one_cta_kernel_matches_too(oracle, cuda, case):
+    """The default for bf16 / f16 is the two-CTA kernel; the one-CTA kernel (mx_set_gemm_cta_group(1)) stays in the
+    library (odd SM budgets, A/B timing) and must give the same products."""
+    from maidenx_b200 import _lib
+    lib = _lib.load()
+    lib.mx_set_gemm_cta_group(1)
+    try:
+        test_matmul_forward_many_tiles(oracle, cuda, D.BF16, case)
+    finally:
+        lib.mx_set_gemm_cta_group(2)

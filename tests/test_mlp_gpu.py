@@ -223,3 +223,34 @@ def test_one_training_step_matches_the_oracle_composed_model(cuda):
     m.close()
     xb.free()
     yb.free()
+
+
+@pytest.mark.parametrize("dt", [D.BF16, D.F16], ids=lambda d: d.name)
+@pytest.mark.parametrize("shape", [(256, 512, 256), (200, 264, 392), (40, 24, 56)], ids=lambda s: "x".join(map(str, s)))
+def test_linear_with_bias_and_gelu_in_the_epilogue_equals_the_three_ops(cuda, dt, shape):
+    """mx_linear_bias_gelu against cuda_matmul (W^T view), cuda_add (scalar bias broadcast) and cuda_gelu run one after
+    the other, bit for bit - on shapes the tensor-core kernel takes (epilogue fusion) and on one it does not."""
+    rows, out_f, in_f = shape
+    rng = np.random.default_rng(31)
+    x = H.random_store(rng, dt, rows * in_f, dist="normal")
+    w = H.random_store(rng, dt, out_f * in_f, lo=-0.1, hi=0.1)
+    b = H.random_store(rng, dt, 1, lo=-0.5, hi=0.5)
+    meta = H.matmul_metadata([rows, out_f], [rows, in_f], [in_f, out_f], [in_f, 1], [1, in_f], 0, 0)
+    z = H.run_matmul(cuda, dt, meta, rows * out_f, x, w)
+    u_ref = H.run_binary(cuda, "add", dt, [rows, out_f], [out_f, 1], [0, 0], 0, 0, z, b)
+    a_ref = H.run_unary(cuda, "gelu", dt, [rows * out_f], [1], 0, u_ref)
+    lib = _lib.load()
+    fn = getattr(lib, f"mx_linear_bias_gelu_{dt.name}")
+    bufs = [device.CudaBuffer.from_host(v) for v in (x, w, b)]
+    for with_act in (True, False):
+        ub, ab = device.CudaBuffer.from_host(np.full(rows * out_f, 7).astype(dt.np_storage)), device.CudaBuffer.from_host(np.full(rows * out_f, 7).astype(dt.np_storage))
+        fn(rows, in_f, out_f, bufs[0].ptr, bufs[1].ptr, bufs[2].ptr, ub.ptr, ab.ptr if with_act else None)
+        device.synchronize()
+        assert device.last_error() is None
+        H.assert_same("linear", dt, ub.to_host(dt.np_storage, rows * out_f), u_ref, what="u")
+        if with_act:
+            H.assert_same("linear", dt, ab.to_host(dt.np_storage, rows * out_f), a_ref, what="act")
+        ub.free()
+        ab.free()
+    for v in bufs:
+        v.free()
