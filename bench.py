@@ -799,11 +799,12 @@ def e2e_mlp(torch, lib, mlp, x, y, dist, world, steps, warm):
     """The same step fed from pinned host memory: every step copies its shard's inputs host -> device and reads the
     loss back.  The copies of step i + 1 run on a copy stream into the second of two device buffers while step i
     computes (an input pipeline: the user-facing loop of maidenx_b200.mlp.InputPipeline)."""
-    from maidenx_b200.mlp import InputPipeline
+    from maidenx_b200.mlp import InputPipeline, LossReader
     hx, hy = x.cpu().pin_memory(), y.cpu().pin_memory()
     nbytes = x.numel() * x.element_size()
-    loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
     pipe = InputPipeline(torch, x, y)
+    reader = LossReader(torch, mlp)
+    losses = []
 
     def run(n):
         pipe.prefetch(hx, hy)
@@ -813,7 +814,10 @@ def e2e_mlp(torch, lib, mlp, x, y, dist, world, steps, warm):
                 pipe.prefetch(hx, hy)           # next batch: copies overlap this step
             mlp.train_step(xb.data_ptr(), yb.data_ptr(), MLP_LR, torch, dist, world)
             pipe.release()                      # the buffers may be overwritten once this step's kernels are done
-            lib.cuda_memcpy_d2h(loss_host.data_ptr(), mlp.ptr("loss_ptr"), 4)
+            prev = reader.after_step()          # this step's loss copy is queued; the previous step's loss is on the host now
+            if prev is not None:
+                losses.append(prev)
+        losses.append(reader.last())            # the last step's loss: read inside the timed region too
 
     run(warm)
     torch.cuda.synchronize()
@@ -843,8 +847,9 @@ def e2e_mlp(torch, lib, mlp, x, y, dist, world, steps, warm):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         copy_s = float(t.item())
     return {"value": round(MLP_GLOBAL_BATCH / dt_s, 1), "unit": "samples/s", "h2d_bytes_per_step": 2 * nbytes * world, "d2h_bytes_per_step": 4 * world,
-            "steps": steps, "ms_per_step": round(dt_s * 1e3, 3), "loss": float(loss_host[0]),
-            "pipeline": "double-buffered: host->device copies of step i+1 on a copy stream while step i computes",
+            "steps": steps, "ms_per_step": round(dt_s * 1e3, 3), "loss": losses[-1], "losses_read": len(losses),
+            "pipeline": "double-buffered: host->device copies of step i+1 on a copy stream while step i computes; every step's loss is copied "
+                        "to pinned host memory on its own stream and collected by the host one step later (maidenx_b200.mlp.LossReader)",
             "h2d_gbs_per_rank_achieved": round(2 * nbytes / dt_s / 1e9, 1),
             "h2d_copy_only": {"ms_per_step_worth": round(copy_s * 1e3, 3), "gbs_per_rank": round(2 * nbytes / copy_s / 1e9, 1),
                               "gbs_all_ranks": round(2 * nbytes * world / copy_s / 1e9, 1),

@@ -236,6 +236,54 @@ class InputPipeline:
         self.taken += 1
 
 
+class LossReader:
+    """Per-step loss read-back that does not stall the training loop.
+
+        reader = LossReader(torch, mlp)
+        for ...:
+            mlp.train_step(...)
+            prev = reader.after_step()     # loss of the PREVIOUS step (None after the first), this step's copy is queued
+        final = reader.last()              # waits for the newest copy
+
+    The 4-byte device-to-host copy of step i runs on a stream of its own behind step i (pinned destination), and the host
+    collects it after it has queued step i + 1 - so the device never waits for the host between steps, which a
+    synchronous read after every step forces (and which exposes whatever the step left running on side streams, such as
+    the gradient exchange of its last layer).  The compute stream waits for the copy before the next step may overwrite
+    the loss word."""
+
+    def __init__(self, torch, mlp, compute_stream=None):
+        self.torch = torch
+        self.compute = compute_stream or torch.cuda.current_stream()
+        self.stream = torch.cuda.Stream()
+        self.dev = torch.as_tensor(_CudaArray(mlp.ptr("loss_ptr"), 1, "<f4"), device="cuda")
+        self.host = [torch.empty(1, dtype=torch.float32).pin_memory(), torch.empty(1, dtype=torch.float32).pin_memory()]
+        self.done = [torch.cuda.Event(), torch.cuda.Event()]
+        self.ready = torch.cuda.Event()
+        self.count = 0
+
+    def after_step(self):
+        slot = self.count % 2
+        self.ready.record(self.compute)
+        with self.torch.cuda.stream(self.stream):
+            self.stream.wait_event(self.ready)
+            self.host[slot].copy_(self.dev, non_blocking=True)
+            self.done[slot].record(self.stream)
+        self.compute.wait_event(self.done[slot])
+        self.count += 1
+        if self.count < 2:
+            return None
+        prev = (self.count - 2) % 2
+        self.done[prev].synchronize()
+        return float(self.host[prev][0])
+
+    def last(self):
+        if self.count == 0:
+            return None
+        slot = (self.count - 1) % 2
+        self.done[slot].synchronize()
+        return float(self.host[slot][0])
+
+
 class _CudaArray:
     """Minimal __cuda_array_interface__ holder so torch can alias memory owned by the library."""
 

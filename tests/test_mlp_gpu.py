@@ -254,3 +254,34 @@ def test_linear_with_bias_and_gelu_in_the_epilogue_equals_the_three_ops(cuda, dt
         ab.free()
     for v in bufs:
         v.free()
+
+
+def test_loss_reader_returns_every_steps_loss_one_step_later(cuda):
+    """maidenx_b200.mlp.LossReader against the synchronous read of a twin engine (same seed, same batch)."""
+    import torch
+
+    from maidenx_b200.mlp import LossReader, Mlp
+    L, Dm, B, seed, lr = 2, 256, 256, 3, 0.05
+    rng = np.random.default_rng(5)
+    x, y = H.random_store(rng, D.BF16, B * Dm, dist="normal"), H.random_store(rng, D.BF16, B * Dm, dist="normal")
+    xb, yb = device.CudaBuffer.from_host(x), device.CudaBuffer.from_host(y)
+    a, b = Mlp(L, Dm, B, "bf16", seed), Mlp(L, Dm, B, "bf16", seed)
+    want = []
+    for _ in range(5):
+        a.train_step(xb.ptr, yb.ptr, lr)
+        want.append(a.loss())
+    reader = LossReader(torch, b)
+    got = []
+    for i in range(5):
+        b.train_step(xb.ptr, yb.ptr, lr)
+        prev = reader.after_step()
+        assert (prev is None) == (i == 0)
+        if prev is not None:
+            got.append(prev)
+    got.append(reader.last())
+    assert got == want and want[-1] < want[0]
+    assert device.last_error() is None
+    a.close()
+    b.close()
+    xb.free()
+    yb.free()
