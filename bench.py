@@ -953,7 +953,7 @@ def main():
     ap.add_argument("--exchange", default="auto", choices=["auto", "multimem-exclusive", "copy", "multimem", "peer", "nccl"],
                     help="N > 1: how gradients are exchanged (auto: the library's NVLink kernels, NCCL if symmetric memory is unavailable)")
     ap.add_argument("--exchange-sms", type=int, default=8, help="multimem-exclusive: SMs given to the exchange kernel")
-    ap.add_argument("--cta-group", type=int, default=2, choices=[1, 2], help="bf16 / f16 tensor-core products: 2 = pairs of CTAs share the B tile (default), 1 = one CTA per tile")
+    ap.add_argument("--cta-group", type=int, default=1, choices=[1, 2], help="bf16 / f16 tensor-core products: 1 = one CTA per tile (default), 2 = pairs of CTAs share the B tile (same rate on a power-capped B200)")
     ap.add_argument("--only-case", default=None, help="profiling aid: launch just this sweep case --steps times and exit")
     ap.add_argument("--small", action="store_true", help="profiling aid: 8192x8192 / quarter-size tensors for ncu captures")
     args = ap.parse_args()

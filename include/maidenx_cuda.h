@@ -401,8 +401,9 @@ int mx_mlp_dp_set_exchange(void* mlp, int mode, int exclusive_sms);
 /* The tensor-core GEMM of the calling thread launches at most `sms` CTAs (0: all SMs), leaving the other SMs to a
  * concurrent kernel such as the exchange above. */
 void mx_set_gemm_sm_limit(int sms);
-/* 2 (default): bf16 / f16 products on the tensor cores run as pairs of CTAs on neighbouring SMs that share the B tile
- * (tcgen05.mma.cta_group::2); 1: one CTA per tile.  Same results either way; process-wide. */
+/* 1 (default): one CTA per output tile; 2: bf16 / f16 products on the tensor cores run as pairs of CTAs on neighbouring
+ * SMs that share the B tile (tcgen05.mma.cta_group::2).  Same results and, on a power-capped B200, the same rate;
+ * process-wide. */
 void mx_set_gemm_cta_group(int ctas);
 
 #ifdef __cplusplus

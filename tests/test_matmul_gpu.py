@@ -293,14 +293,28 @@ def test_stale_device_wait_report_is_surfaced_and_does_not_poison_later_products
             x.free()
 
 
-@pytest.mark.parametrize("case", [BIG_FWD[0], BIG_FWD[3], BIG_FWD[6]], ids=lambda c: c[0])
-def test_one_cta_kernel_matches_too(oracle, cuda, case):
-    """The default for bf16 / f16 is the two-CTA kernel; the one-CTA kernel (mx_set_gemm_cta_group(1)) stays in the
-    library (odd SM budgets, A/B timing) and must give the same products."""
+@pytest.mark.parametrize("dt", [D.BF16, D.F16], ids=lambda d: d.name)
+@pytest.mark.parametrize("case", BIG_FWD, ids=lambda c: c[0])
+def test_two_cta_kernel_matches_too(oracle, cuda, dt, case):
+    """mx_set_gemm_cta_group(2): pairs of CTAs share the B tile (tcgen05.mma.cta_group::2, matmul_tc2.cu).  Same products
+    as the default one-CTA kernel, on every many-tile case: odd numbers of row tiles (a pair with an empty half),
+    ragged edges, both operand majors, split-K."""
     from maidenx_b200 import _lib
     lib = _lib.load()
-    lib.mx_set_gemm_cta_group(1)
+    lib.mx_set_gemm_cta_group(2)
     try:
-        test_matmul_forward_many_tiles(oracle, cuda, D.BF16, case)
+        test_matmul_forward_many_tiles(oracle, cuda, dt, case)
     finally:
-        lib.mx_set_gemm_cta_group(2)
+        lib.mx_set_gemm_cta_group(1)
+
+
+@pytest.mark.parametrize("dt", [D.BF16, D.F16], ids=lambda d: d.name)
+def test_two_cta_kernel_on_the_small_batched_and_backward_cases(oracle, cuda, dt):
+    from maidenx_b200 import _lib
+    lib = _lib.load()
+    lib.mx_set_gemm_cta_group(2)
+    try:
+        test_matmul_forward(oracle, cuda, dt)
+        test_matmul_backward(oracle, cuda, dt)
+    finally:
+        lib.mx_set_gemm_cta_group(1)
