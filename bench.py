@@ -954,6 +954,7 @@ def main():
                     help="N > 1: how gradients are exchanged (auto: the library's NVLink kernels, NCCL if symmetric memory is unavailable)")
     ap.add_argument("--exchange-sms", type=int, default=8, help="multimem-exclusive: SMs given to the exchange kernel")
     ap.add_argument("--cta-group", type=int, default=1, choices=[1, 2], help="bf16 / f16 tensor-core products: 1 = one CTA per tile (default), 2 = pairs of CTAs share the B tile (same rate on a power-capped B200)")
+    ap.add_argument("--group-m", type=int, default=0, help="tuning aid: row-tiles per column sweep of the GEMM's tile order (0 = the library's default)")
     ap.add_argument("--only-case", default=None, help="profiling aid: launch just this sweep case --steps times and exit")
     ap.add_argument("--small", action="store_true", help="profiling aid: 8192x8192 / quarter-size tensors for ncu captures")
     args = ap.parse_args()
@@ -973,6 +974,8 @@ def main():
     lib = lib_mod.load()  # raises if the CUDA library is not built: there is no fallback
     assert lib.cuda_set_device(local_rank) == 0
     lib.mx_set_gemm_cta_group(args.cta_group)
+    if args.group_m:
+        lib.mx_debug_set_gemm_group_m(args.group_m)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks = measured_peaks()

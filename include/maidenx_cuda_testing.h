@@ -26,6 +26,8 @@ int mx_debug_reduce_plan(size_t num_els, size_t num_dims, size_t num_red_dims, c
 /* Would cuda_matmul_f32 with this HOST metadata run on the tcgen05 split-tf32 kernel (1) or on the SIMT kernel (0)? */
 int mx_debug_matmul_forward_path_f32(size_t num_els, const size_t* host_metadata, const void* a, const void* b, const void* out, int* a_mn_major,
                                      int* b_mn_major, size_t* m, size_t* n, size_t* k);
+/* Tuning aid: row-tiles per column sweep in the one-CTA tensor-core kernel's tile order (default 16). */
+void mx_debug_set_gemm_group_m(int rows);
 /* How many K slices the tensor-core path cuts a product with `tiles` output tiles and reduction length `k` into
  * (1 = no split) on `sms` SMs; block_k = 64 for bf16 / f16, 32 for f32. */
 int mx_debug_splitk_slices(size_t tiles, size_t k, int block_k, int sms);

@@ -43,6 +43,7 @@ namespace {
 // true: products go to the two-CTA kernel (matmul_tc2.cu); false (default): to the one-CTA kernel below.  On a B200 under
 // its power cap the two run at the same rate (the pair form only moves less data through shared memory).
 std::atomic<bool> g_two_cta{false};
+std::atomic<int> g_group_m{16};  // row-tiles per column sweep of the one-CTA kernel's tile order
 
 constexpr int BM = 128, BN = 256, BK = 64;    // CTA tile; BK * 2 bytes = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
@@ -91,16 +92,17 @@ struct TcParams {
     int fuse;     // 0: store the product; 1: u = round(round(product) + bias) through map_d; 2: also act = round(gelu(u)) through map_d2
     const void* bias;  // fuse != 0: one element of the operand type in device memory
     int a_mn, b_mn;  // operand is MN-major in global memory ([K, MN] row-major) instead of K-major ([MN, K])
+    int group_m;     // row-tiles per column sweep (L2 re-use of the A panels)
 };
 
 __device__ __forceinline__ void tile_coords(int tile, const TcParams& p, int& tm, int& tn, int& tb) {
     tb = tile / p.tiles_per_batch;
     tile -= tb * p.tiles_per_batch;
     // sweep GROUP_M row-tiles for each column tile before moving to the next column tile
-    const int group_size = GROUP_M * p.tiles_n;
+    const int group_size = p.group_m * p.tiles_n;
     const int group = tile / group_size;
-    const int first_m = group * GROUP_M;
-    const int rows = min(GROUP_M, p.tiles_m - first_m);
+    const int first_m = group * p.group_m;
+    const int rows = min(p.group_m, p.tiles_m - first_m);
     const int in_group = tile - group * group_size;
     tm = first_m + in_group % rows;
     tn = in_group / rows;
@@ -468,6 +470,7 @@ bool launch_gemm(bool is_bf16, const TcProduct& c, void* D, const char* where, i
     if (fuse == 2 && !make_map(&md2, is_bf16, D2, M, N, batch, M * N, 32)) return false;
     p.fuse = fuse;
     p.bias = bias;
+    p.group_m = g_group_m.load(std::memory_order_relaxed);
     p.K = (int)K;
     p.num_tiles = (int)batch * p.tiles_per_batch;
     p.a_batched = (batch > 1 && a_bs != 0) ? 1 : 0;
@@ -797,6 +800,7 @@ static int debug_forward_path(size_t es, size_t num_els, const size_t* host_meta
 }
 // 2: bf16 / f16 products run on the two-CTA kernel (pairs of SMs share the B tile); 1: on the one-CTA kernel.
 extern "C" void mx_set_gemm_cta_group(int ctas) { mx::g_two_cta.store(ctas == 2, std::memory_order_relaxed); }
+extern "C" void mx_debug_set_gemm_group_m(int rows) { mx::g_group_m.store(rows > 0 ? rows : 16, std::memory_order_relaxed); }
 extern "C" int mx_debug_splitk_slices(size_t tiles, size_t k, int block_k, int sms) { return mx::tc::splitk_slices(tiles, k, block_k, sms); }
 extern "C" int mx_debug_matmul_forward_path(size_t num_els, const size_t* host_metadata, const void* a, const void* b, const void* out, int* a_mn_major,
                                             int* b_mn_major, size_t* m, size_t* n, size_t* k) {

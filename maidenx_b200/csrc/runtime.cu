@@ -254,15 +254,37 @@ void* take_cached(int dev, int cls) {
     return nullptr;
 }
 
+// A cached block that carries no event was freed in legacy-stream order: work queued on the legacy stream (by any thread)
+// may still read it.  A thread that launches on a non-blocking stream of its own is not ordered behind that work, so
+// its stream is made to wait for everything queued on the legacy stream so far before it may touch the block.
+thread_local cudaEvent_t t_legacy_mark[64] = {nullptr};
+void order_after_legacy_stream(int dev, cudaStream_t user_stream) {
+    if (user_stream == 0) return;
+    if (!t_legacy_mark[dev] && cudaEventCreateWithFlags(&t_legacy_mark[dev], cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        t_legacy_mark[dev] = nullptr;
+        cudaStreamSynchronize(0);
+        return;
+    }
+    cudaEventRecord(t_legacy_mark[dev], 0);
+    cudaStreamWaitEvent(user_stream, t_legacy_mark[dev], 0);
+}
+
 void* pool_take(size_t size) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
     const int cls = size_class(size);
-    std::lock_guard<std::mutex> lk(g_pool_mutex);
-    if (void* p = take_cached(dev, cls)) {
-        if (cls) g_live[p] = {dev, cls};
-        return p;
+    void* reused = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_pool_mutex);
+        reused = take_cached(dev, cls);
+        if (reused && cls) g_live[reused] = {dev, cls};
     }
+    if (reused) {
+        order_after_legacy_stream(dev, ctx().stream);
+        return reused;
+    }
+    std::lock_guard<std::mutex> lk(g_pool_mutex);
     if (cls == 0) {
         void* slab = nullptr;
         if (cudaMalloc(&slab, kPoolSlotBytes * kPoolSlabSlots) != cudaSuccess) {
