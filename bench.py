@@ -823,6 +823,7 @@ def e2e_mlp(torch, lib, mlp, x, y, dist, world, steps, warm):
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+    del losses[:]
     t0 = time.perf_counter()
     run(steps)
     torch.cuda.synchronize()
