@@ -224,6 +224,112 @@ __global__ void __launch_bounds__(kEwThreads) ew_flat_shift_kernel(F f, const T*
     }
 }
 
+// The same work with the shifted operands staged through shared memory: one thread asks the copy engine of the SM
+// (cp.async.bulk, global -> shared, completion on an mbarrier) for the 16-byte-aligned span that covers the block's part
+// of each shifted operand - every byte crosses from L2 exactly once, in full lines - and each thread then assembles its
+// vectors from two aligned 16-byte shared-memory words.  Used for large operands; the body of the block is kEwThreads *
+// kEwUnroll vectors, i.e. 16 KB (+ 16 bytes) of shared memory per shifted operand.  The wait on the barrier is bounded.
+constexpr int kEwStageBytes = kEwThreads * kEwUnroll * 16 + 16;
+
+__device__ __forceinline__ bool ew_stage_wait(uint32_t bar) {
+    for (int i = 0; i < (1 << 26); i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+template <class F, class T, class O, int NIN, int VEC>
+__global__ void __launch_bounds__(kEwThreads) ew_flat_shift_staged_kernel(F f, const T* a, const T* b, O* out, uint64_t n, uint64_t head,
+                                                                          uint64_t body_vecs, int sa, int sb, uint32_t sha, uint32_t shb) {
+    extern __shared__ __align__(128) unsigned char ew_stage[];
+    __shared__ __align__(8) unsigned long long stage_bar;
+    const uint64_t block_v0 = (uint64_t)blockIdx.x * kEwThreads * kEwUnroll;
+    const uint64_t left = body_vecs - block_v0;
+    const uint32_t nv = left < (uint64_t)kEwThreads * kEwUnroll ? (uint32_t)left : (uint32_t)(kEwThreads * kEwUnroll);  // vectors of this block
+    const bool stage_a = sa && sha != 0, stage_b = NIN == 2 && sb && shb != 0;
+    unsigned char* buf_a = ew_stage;
+    unsigned char* buf_b = ew_stage + (stage_a ? kEwStageBytes : 0);
+    const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&stage_bar);
+    if (stage_a || stage_b) {
+        if (threadIdx.x == 0) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            const uint32_t bytes = nv * 16 + 16;  // the aligned words the block's vectors straddle
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((stage_a ? bytes : 0) + (stage_b ? bytes : 0)) : "memory");
+            if (stage_a) {
+                const uintptr_t src = reinterpret_cast<uintptr_t>(a + head + block_v0 * VEC) - sha;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 (uint32_t)__cvta_generic_to_shared(buf_a)),
+                             "l"(src), "r"(bytes), "r"(bar)
+                             : "memory");
+            }
+            if (stage_b) {
+                const uintptr_t src = reinterpret_cast<uintptr_t>(b + head + block_v0 * VEC) - shb;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 (uint32_t)__cvta_generic_to_shared(buf_b)),
+                             "l"(src), "r"(bytes), "r"(bar)
+                             : "memory");
+            }
+        }
+    }
+    // operands that need no staging are read straight from global memory while the copies fly
+    Vec<T, VEC> va[kEwUnroll], vb[kEwUnroll];
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; u++) {
+        const uint32_t lv = (uint32_t)u * kEwThreads + threadIdx.x;
+        if (lv < nv) {
+            const uint64_t i = head + (block_v0 + lv) * VEC;
+            if (!stage_a) va[u] = sa ? ld_vec<T, VEC>(a + i) : splat<T, VEC>(a[0]);
+            if constexpr (NIN == 2)
+                if (!stage_b) vb[u] = sb ? ld_vec<T, VEC>(b + i) : splat<T, VEC>(b[0]);
+        }
+    }
+    bool landed = true;
+    if (stage_a || stage_b) {
+        __syncthreads();  // the barrier is initialised before anyone polls it
+        landed = ew_stage_wait(bar);
+    }
+    if (landed) {
+#pragma unroll
+        for (int u = 0; u < kEwUnroll; u++) {
+            const uint32_t lv = (uint32_t)u * kEwThreads + threadIdx.x;
+            if (lv >= nv) continue;
+            if (stage_a) {
+                const uint4 lo = *reinterpret_cast<const uint4*>(buf_a + lv * 16), hi = *reinterpret_cast<const uint4*>(buf_a + lv * 16 + 16);
+                const uint4 r = shift_pair(lo, hi, sha);
+                va[u] = *reinterpret_cast<const Vec<T, VEC>*>(&r);
+            }
+            if constexpr (NIN == 2) {
+                if (stage_b) {
+                    const uint4 lo = *reinterpret_cast<const uint4*>(buf_b + lv * 16), hi = *reinterpret_cast<const uint4*>(buf_b + lv * 16 + 16);
+                    const uint4 r = shift_pair(lo, hi, shb);
+                    vb[u] = *reinterpret_cast<const Vec<T, VEC>*>(&r);
+                }
+            }
+            st_vec<O, VEC>(out + head + (block_v0 + lv) * VEC, apply_vec<F, T, O, NIN, VEC>(f, va[u], vb[u]));
+        }
+    }
+    if (blockIdx.x == 0) {
+        const uint64_t tail_begin = head + body_vecs * VEC;
+        const uint64_t edge = head + (n - tail_begin);
+        for (uint64_t e = threadIdx.x; e < edge; e += kEwThreads) {
+            const uint64_t i = e < head ? e : tail_begin + (e - head);
+            T x = a[sa ? i : 0];
+            if constexpr (NIN == 2) out[i] = f(x, b[sb ? i : 0]);
+            else out[i] = f(x);
+        }
+    }
+}
+
 struct EwRowParams {
     int nd_outer;
     uint32_t total_vecs;
@@ -582,6 +688,13 @@ void ew_launch(const EwPlan& pl, const F& f, const T* a, const T* b, O* out, con
             if (blocks > 0x7FFFFFFFull) {
                 set_error(kErrUnsupported, 0, where);
                 return;
+            }
+            const int staged = (sa && sha != 0 ? 1 : 0) + (NIN == 2 && sb && shb != 0 ? 1 : 0);
+            if (staged && body_vecs >= 4096) {
+                // large operands: the shifted ones go through shared memory, one bulk copy per block and operand
+                ew_flat_shift_staged_kernel<F, T, O, NIN, VEC>
+                    <<<(uint32_t)blocks, kEwThreads, (size_t)staged * kEwStageBytes, s>>>(f, a, b, out, pl.n, head, body_vecs, sa, sb, sha, shb);
+                break;
             }
             ew_flat_shift_kernel<F, T, O, NIN, VEC><<<(uint32_t)blocks, kEwThreads, 0, s>>>(f, a, b, out, pl.n, head, body_vecs, sa, sb, sha, shb);
             break;
