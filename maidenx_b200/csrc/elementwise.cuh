@@ -248,13 +248,15 @@ __device__ __forceinline__ bool ew_stage_wait(uint32_t bar) {
 
 template <class F, class T, class O, int NIN, int VEC>
 __global__ void __launch_bounds__(kEwThreads) ew_flat_shift_staged_kernel(F f, const T* a, const T* b, O* out, uint64_t n, uint64_t head,
-                                                                          uint64_t body_vecs, int sa, int sb, uint32_t sha, uint32_t shb) {
+                                                                          uint64_t body_vecs, int sa, int sb, uint32_t sha, uint32_t shb, int stage_aligned) {
     extern __shared__ __align__(128) unsigned char ew_stage[];
     __shared__ __align__(8) unsigned long long stage_bar;
     const uint64_t block_v0 = (uint64_t)blockIdx.x * kEwThreads * kEwUnroll;
-    const uint64_t left = body_vecs - block_v0;
+    const uint64_t left = block_v0 < body_vecs ? body_vecs - block_v0 : 0;
     const uint32_t nv = left < (uint64_t)kEwThreads * kEwUnroll ? (uint32_t)left : (uint32_t)(kEwThreads * kEwUnroll);  // vectors of this block
-    const bool stage_a = sa && sha != 0, stage_b = NIN == 2 && sb && shb != 0;
+    // stage_aligned: aligned operands go through shared memory as well (register-heavy functors keep too few loads in flight
+    // on their own; the copy engine's queue does not depend on how many threads are resident)
+    const bool stage_a = nv && sa && (sha != 0 || stage_aligned), stage_b = nv && NIN == 2 && sb && (shb != 0 || stage_aligned);
     unsigned char* buf_a = ew_stage;
     unsigned char* buf_b = ew_stage + (stage_a ? kEwStageBytes : 0);
     const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&stage_bar);
@@ -304,14 +306,16 @@ __global__ void __launch_bounds__(kEwThreads) ew_flat_shift_staged_kernel(F f, c
             const uint32_t lv = (uint32_t)u * kEwThreads + threadIdx.x;
             if (lv >= nv) continue;
             if (stage_a) {
-                const uint4 lo = *reinterpret_cast<const uint4*>(buf_a + lv * 16), hi = *reinterpret_cast<const uint4*>(buf_a + lv * 16 + 16);
-                const uint4 r = shift_pair(lo, hi, sha);
+                const uint4 lo = *reinterpret_cast<const uint4*>(buf_a + lv * 16);
+                uint4 r = lo;
+                if (sha) r = shift_pair(lo, *reinterpret_cast<const uint4*>(buf_a + lv * 16 + 16), sha);
                 va[u] = *reinterpret_cast<const Vec<T, VEC>*>(&r);
             }
             if constexpr (NIN == 2) {
                 if (stage_b) {
-                    const uint4 lo = *reinterpret_cast<const uint4*>(buf_b + lv * 16), hi = *reinterpret_cast<const uint4*>(buf_b + lv * 16 + 16);
-                    const uint4 r = shift_pair(lo, hi, shb);
+                    const uint4 lo = *reinterpret_cast<const uint4*>(buf_b + lv * 16);
+                    uint4 r = lo;
+                    if (shb) r = shift_pair(lo, *reinterpret_cast<const uint4*>(buf_b + lv * 16 + 16), shb);
                     vb[u] = *reinterpret_cast<const Vec<T, VEC>*>(&r);
                 }
             }
@@ -670,6 +674,17 @@ void ew_launch(const EwPlan& pl, const F& f, const T* a, const T* b, O* out, con
                 set_error(kErrUnsupported, 0, where);
                 return;
             }
+            if constexpr (F::kChecked) {
+                // 16-bit division (approximate quotient + exact redo): 88 registers per thread leave few loads in flight, so
+                // large operands are fed by bulk copies through shared memory instead
+                const int sa = (int)pl.st[1][0], sb = NIN == 2 ? (int)pl.st[2][0] : 0;
+                const int staged = (sa ? 1 : 0) + (sb ? 1 : 0);
+                if (staged && pl.n / VEC >= 4096) {
+                    ew_flat_shift_staged_kernel<F, T, O, NIN, VEC>
+                        <<<(uint32_t)blocks, kEwThreads, (size_t)staged * kEwStageBytes, s>>>(f, a, b, out, pl.n, 0, pl.n / VEC, sa, sb, 0, 0, 1);
+                    break;
+                }
+            }
             ew_flat_kernel<F, T, O, NIN, VEC><<<(uint32_t)blocks, kEwThreads, 0, s>>>(f, a, b, out, pl.n, (int)pl.st[1][0], NIN == 2 ? (int)pl.st[2][0] : 0);
             break;
         }
@@ -693,7 +708,7 @@ void ew_launch(const EwPlan& pl, const F& f, const T* a, const T* b, O* out, con
             if (staged && body_vecs >= 4096) {
                 // large operands: the shifted ones go through shared memory, one bulk copy per block and operand
                 ew_flat_shift_staged_kernel<F, T, O, NIN, VEC>
-                    <<<(uint32_t)blocks, kEwThreads, (size_t)staged * kEwStageBytes, s>>>(f, a, b, out, pl.n, head, body_vecs, sa, sb, sha, shb);
+                    <<<(uint32_t)blocks, kEwThreads, (size_t)staged * kEwStageBytes, s>>>(f, a, b, out, pl.n, head, body_vecs, sa, sb, sha, shb, 0);
                 break;
             }
             ew_flat_shift_kernel<F, T, O, NIN, VEC><<<(uint32_t)blocks, kEwThreads, 0, s>>>(f, a, b, out, pl.n, head, body_vecs, sa, sb, sha, shb);
