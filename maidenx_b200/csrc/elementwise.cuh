@@ -265,20 +265,21 @@ __global__ void __launch_bounds__(kEwThreads) ew_flat_shift_staged_kernel(F f, c
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            const uint32_t bytes = nv * 16 + 16;  // the aligned words the block's vectors straddle
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((stage_a ? bytes : 0) + (stage_b ? bytes : 0)) : "memory");
+            // the aligned words the block's vectors straddle: one extra word only for an operand that is really shifted
+            const uint32_t bytes_a = nv * 16 + (sha ? 16 : 0), bytes_b = nv * 16 + (shb ? 16 : 0);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((stage_a ? bytes_a : 0) + (stage_b ? bytes_b : 0)) : "memory");
             if (stage_a) {
                 const uintptr_t src = reinterpret_cast<uintptr_t>(a + head + block_v0 * VEC) - sha;
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                                  (uint32_t)__cvta_generic_to_shared(buf_a)),
-                             "l"(src), "r"(bytes), "r"(bar)
+                             "l"(src), "r"(bytes_a), "r"(bar)
                              : "memory");
             }
             if (stage_b) {
                 const uintptr_t src = reinterpret_cast<uintptr_t>(b + head + block_v0 * VEC) - shb;
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                                  (uint32_t)__cvta_generic_to_shared(buf_b)),
-                             "l"(src), "r"(bytes), "r"(bar)
+                             "l"(src), "r"(bytes_b), "r"(bar)
                              : "memory");
             }
         }
