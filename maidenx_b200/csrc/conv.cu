@@ -228,6 +228,21 @@ void col2im_entry(size_t num_els, const size_t* meta, const T* col, T* out, cons
             Q.num_els = num_els;
             const uint32_t items = P.H * (P.W / VEC);
             dim3 grid((items + kConvS1Threads - 1) / kConvS1Threads, (unsigned)planes);
+            // every plane readable, 16-byte-multiple planes, at least two blocks' worth of shared memory per SM: staged form
+            const uint64_t plane_elems = (uint64_t)P.KH * P.KW * P.OH * P.OW;
+            const size_t stage_bytes = (size_t)plane_elems * sizeof(T);
+            if (num_els >= planes * plane_elems && stage_bytes % 16 == 0 && stage_bytes <= 112 * 1024 && plane_elems < (1ull << 30)) {
+                auto go = [&](auto kernel) {
+                    if (stage_bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stage_bytes);
+                    kernel<<<(unsigned)planes, kConvS1Threads, stage_bytes, s>>>(col, out, Q);
+                    check_launch(where);
+                };
+                if (kw == 1 && pw == 0) { go(col2im_s1_staged_kernel<T, VEC, 1, 0>); return; }
+                if (kw == 3 && pw == 1) { go(col2im_s1_staged_kernel<T, VEC, 3, 1>); return; }
+                if (kw == 3 && pw == 0 && VEC > 2) { go(col2im_s1_staged_kernel<T, VEC, 3, 0>); return; }
+                if (kw == 5 && pw == 2 && VEC > 2) { go(col2im_s1_staged_kernel<T, VEC, 5, 2>); return; }
+                if (kw == 7 && pw == 3 && VEC > 3) { go(col2im_s1_staged_kernel<T, VEC, 7, 3>); return; }
+            }
             bool done = true;
             if (kw == 1 && pw == 0) col2im_s1_kernel<T, VEC, 1, 0><<<grid, kConvS1Threads, 0, s>>>(col, out, Q);
             else if (kw == 3 && pw == 1) col2im_s1_kernel<T, VEC, 3, 1><<<grid, kConvS1Threads, 0, s>>>(col, out, Q);

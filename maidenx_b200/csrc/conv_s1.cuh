@@ -132,4 +132,63 @@ __global__ void __launch_bounds__(kConvS1Threads) col2im_s1_kernel(const T* __re
     *reinterpret_cast<Vec<T, VEC>*>(out + bc * (uint64_t)P.H * P.W + (uint64_t)h * P.W + w0) = sum;
 }
 
+// col2im with the block's column planes staged in shared memory: one block per (b, c) plane asks the SM's copy engine
+// (cp.async.bulk, completion on an mbarrier, bounded wait) for the KH * KW consecutive [OH, OW] planes that feed it - every
+// column entry crosses from L2 once, in full lines - and the shifted windows are then cut out of shared memory by the same
+// term walk as above (same order, same rounding).  Needs the whole column buffer readable (num_els covers every plane) and
+// KH * KW * OH * OW elements to fit the shared memory of at least two resident blocks.
+template <class T, int VEC, int KW, int PW>
+__global__ void __launch_bounds__(kConvS1Threads) col2im_s1_staged_kernel(const T* __restrict__ col, T* __restrict__ out, ConvS1Params P) {
+    extern __shared__ __align__(128) unsigned char conv_s1_stage[];
+    __shared__ __align__(8) unsigned long long stage_bar;
+    const T* planes = reinterpret_cast<const T*>(conv_s1_stage);
+    const uint64_t bc = blockIdx.x;
+    const uint32_t OHW = P.OH * P.OW;
+    const uint32_t plane_elems = P.KH * KW * OHW;
+    const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&stage_bar);
+    if (threadIdx.x == 0) {
+        const uint32_t bytes = plane_elems * (uint32_t)sizeof(T);
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                         (uint32_t)__cvta_generic_to_shared(conv_s1_stage)),
+                     "l"(col + bc * (uint64_t)plane_elems), "r"(bytes), "r"(bar)
+                     : "memory");
+    }
+    __syncthreads();
+    bool landed = false;
+    for (int i = 0; i < (1 << 26) && !landed; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar)
+            : "memory");
+        landed = ok != 0;
+    }
+    if (!landed) return;
+    ConvS1Params L = P;
+    L.num_els = plane_elems;  // everything staged is readable
+    const uint32_t wv = P.W / VEC;
+    Vec<T, VEC> zero_vec;
+#pragma unroll
+    for (int j = 0; j < VEC; j++) zero_vec.v[j] = zero_of<T>();
+    for (uint32_t item = threadIdx.x; item < P.H * wv; item += kConvS1Threads) {
+        const uint32_t h = item / wv, w0 = (item - h * wv) * VEC;
+        const uint32_t hp = h + P.PH;
+        Vec<T, VEC> sum = zero_vec;
+        for (int kh = (int)min(P.KH - 1, hp); kh >= 0; kh--) {
+            const uint32_t ho = hp - kh;
+            if (ho >= P.OH) continue;
+            const uint64_t kh_base = (uint64_t)kh * KW * OHW + (uint64_t)ho * P.OW;
+            col2im_s1_terms<T, VEC, KW, PW, KW - 1>(planes, L, kh_base, w0, OHW, zero_vec, sum);
+        }
+        *reinterpret_cast<Vec<T, VEC>*>(out + bc * (uint64_t)P.H * P.W + (uint64_t)h * P.W + w0) = sum;
+    }
+}
+
 }  // namespace mx
