@@ -419,6 +419,39 @@ __global__ void __launch_bounds__(kEwThreads) ew_bcast_rows_kernel(F f, const T*
     }
 }
 
+// The same store stream issued by the SM's copy engine: the block evaluates its chunk of the row into shared memory once
+// and one thread then queues one cp.async.bulk (shared -> global) per output row of the block's slab; no per-element store
+// instructions at all.  The chunk is kEwThreads * kEwUnroll output vectors (16 KB when the output type is as wide as the
+// input type); rows are VEC * sizeof(O)-byte multiples here, so every copy is 16-byte aligned and sized.
+template <class F, class T, class O, int VEC>
+__global__ void __launch_bounds__(kEwThreads) ew_bcast_rows_bulk_kernel(F f, const T* a, O* out, uint32_t qv, uint32_t rows, uint32_t rows_per_block) {
+    extern __shared__ __align__(128) unsigned char ew_stage[];
+    const uint32_t chunk_v0 = blockIdx.x * (kEwThreads * kEwUnroll);
+    const uint32_t nv = min(qv - chunk_v0, (uint32_t)(kEwThreads * kEwUnroll));
+    const uint32_t r0 = blockIdx.y * rows_per_block;
+    const uint32_t r1 = min(rows, r0 + rows_per_block);
+    Vec<T, VEC> dummy;
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; u++) {
+        const uint32_t lv = u * kEwThreads + threadIdx.x;
+        if (lv < nv)
+            *reinterpret_cast<Vec<O, VEC>*>(ew_stage + (size_t)lv * VEC * sizeof(O)) =
+                apply_vec<F, T, O, 1, VEC>(f, ld_vec<T, VEC>(a + (size_t)(chunk_v0 + lv) * VEC), dummy);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copy engine reads what the threads just wrote
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t bytes = nv * VEC * (uint32_t)sizeof(O);
+        const uint32_t src = (uint32_t)__cvta_generic_to_shared(ew_stage);
+        for (uint32_t r = r0; r < r1; r++) {
+            O* dst = out + ((size_t)r * qv + chunk_v0) * VEC;
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // shared memory stays valid until the copies have read it (and landed)
+    }
+}
+
 // Short rows: one fast-divmod per vector to find its row.
 template <class F, class T, class O, int NIN, int VEC>
 __global__ void __launch_bounds__(kEwThreads) ew_row_kernel(F f, const T* a, const T* b, O* out, EwRowParams P) {
@@ -729,6 +762,11 @@ void ew_launch(const EwPlan& pl, const F& f, const T* a, const T* b, O* out, con
                     if (gy > 65535) gy = 65535;
                     uint32_t rpb = (uint32_t)((rows + gy - 1) / gy);
                     gy = (uint32_t)((rows + rpb - 1) / rpb);
+                    if ((VEC * sizeof(O)) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
+                        const size_t stage = (size_t)kEwThreads * kEwUnroll * VEC * sizeof(O);
+                        ew_bcast_rows_bulk_kernel<F, T, O, VEC><<<dim3(P.chunks_per_row, gy), kEwThreads, stage, s>>>(f, a, out, P.qv, (uint32_t)rows, rpb);
+                        break;
+                    }
                     ew_bcast_rows_kernel<F, T, O, VEC><<<dim3(P.chunks_per_row, gy), kEwThreads, 0, s>>>(f, a, out, P.qv, (uint32_t)rows, rpb);
                     break;
                 }
