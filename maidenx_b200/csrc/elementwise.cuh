@@ -22,6 +22,7 @@
 #pragma once
 #include "common.cuh"
 #include "ops.cuh"
+#include "tc_ptx.cuh"
 
 namespace mx {
 
@@ -647,6 +648,91 @@ __global__ void __launch_bounds__(kEwThreads, sizeof(T) == 2 ? 6 : 4) ew_tile_ke
     }
 }
 
+// Tile kernel for 2-byte element types (both in and out), vector-aligned layouts with at most one batch dim.  Every
+// operand tile crosses between global and shared memory as ONE tensor copy (a 64 x 64 box, 128-byte swizzle; the inputs
+// complete on an mbarrier, the output tile is written back the same way; ragged edges are clipped by the copy engine),
+// so no thread spends load/store slots on global memory.  A transposed operand sits in shared memory as [q][p];
+// ldmatrix.x4.trans hands each thread the 2 x 4 neighbouring-q pairs of one p-row, i.e. the transposition happens
+// inside the instruction, and a direct operand and the output are read/written in that same fragment layout with
+// 32-bit accesses.  Under the swizzle the eight 16-byte rows of an 8x8 block, and the 32 words of a fragment access,
+// fall in distinct banks.
+constexpr int kEwT16 = 64;
+constexpr int kEwT16Bytes = kEwT16 * 128;
+
+struct EwTile16Params {
+    FastDiv tiles_q_div, tiles_p_div;
+    int transposed[3];
+    int batched[3];  // 0: the operand's map has one batch entry (broadcast along the batch dim)
+};
+
+template <class F, class T, class O, int NIN>
+__global__ void __launch_bounds__(kEwThreads) ew_tile16_kernel(F f, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                                               const __grid_constant__ CUtensorMap map_o, EwTile16Params P) {
+    static_assert(sizeof(T) == 2 && sizeof(O) == 2, "2-byte elements on both sides");
+    extern __shared__ unsigned char ew_smem_raw[];
+    __shared__ __align__(8) unsigned long long tile_bar;
+
+    uint32_t t = blockIdx.x, tq, tp, bidx;
+    P.tiles_q_div.divmod(t, t, tq);
+    P.tiles_p_div.divmod(t, bidx, tp);
+    const int p0 = (int)tp * kEwT16, q0 = (int)tq * kEwT16;
+    const uint32_t smem0 = ((uint32_t)__cvta_generic_to_shared(ew_smem_raw) + 1023u) & ~1023u;  // the swizzle pattern repeats every 1024 bytes
+    unsigned char* tiles = ew_smem_raw + (smem0 - (uint32_t)__cvta_generic_to_shared(ew_smem_raw));
+    const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&tile_bar);
+
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)NIN * kEwT16Bytes) : "memory");
+#pragma unroll
+        for (int x = 0; x < NIN; x++) {
+            const bool tr = P.transposed[x + 1] != 0;
+            tc::tma_load_3d(smem0 + x * kEwT16Bytes, x ? &map_b : &map_a, tr ? p0 : q0, tr ? q0 : p0, P.batched[x + 1] ? (int)bidx : 0, bar);
+        }
+    }
+    __syncthreads();  // the barrier is initialised before anyone polls it
+    const bool landed = ew_stage_wait(bar);
+    if (landed) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        unsigned char* obuf = tiles + NIN * kEwT16Bytes;
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+            const int ws = warp + 8 * s, pb = ws >> 1, qh = ws & 1;  // an 8-row p-block x one 32-wide half of q per warp step
+            // fragment word m of this lane: row p = pb*8 + lane/4, 16-byte chunk qh*4 + m (swizzled by the row), word lane%4
+            const uint32_t frag_row = (uint32_t)(pb * 8 + (lane >> 2)) * 128u + (uint32_t)(lane & 3) * 4u;
+            uint32_t w[2][4] = {};
+#pragma unroll
+            for (int x = 0; x < NIN; x++) {
+                if (P.transposed[x + 1]) {
+                    const uint32_t row = (uint32_t)(qh * 32 + lane);
+                    const uint32_t addr = smem0 + x * kEwT16Bytes + row * 128u + (((uint32_t)pb ^ (row & 7u)) << 4);
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(w[x][0]), "=r"(w[x][1]), "=r"(w[x][2]), "=r"(w[x][3])
+                                 : "r"(addr)
+                                 : "memory");
+                } else {
+                    const unsigned char* src = tiles + x * kEwT16Bytes + frag_row;
+#pragma unroll
+                    for (int m = 0; m < 4; m++) w[x][m] = *reinterpret_cast<const uint32_t*>(src + (((uint32_t)(qh * 4 + m) ^ (uint32_t)(lane >> 2)) << 4));
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                const Vec<O, 2> r = apply_vec<F, T, O, NIN, 2>(f, *reinterpret_cast<const Vec<T, 2>*>(&w[0][m]), *reinterpret_cast<const Vec<T, 2>*>(&w[1][m]));
+                *reinterpret_cast<uint32_t*>(obuf + frag_row + (((uint32_t)(qh * 4 + m) ^ (uint32_t)(lane >> 2)) << 4)) = *reinterpret_cast<const uint32_t*>(&r);
+            }
+        }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copy engine reads what the threads just wrote
+    __syncthreads();
+    if (landed && threadIdx.x == 0) {
+        tc::tma_store_3d(&map_o, smem0 + NIN * kEwT16Bytes, q0, p0, (int)bidx);
+        tc::tma_store_commit();
+        tc::tma_store_wait_read<0>();  // shared memory stays valid until the copy has read it
+    }
+}
+
 struct EwGenParams {
     int nd;
     uint64_t n;
@@ -690,6 +776,38 @@ __global__ void __launch_bounds__(kEwThreads) ew_generic_kernel(F f, const T* a,
 void ew_fill_row_params(const EwPlan& pl, int vec, EwRowParams& P);
 void ew_fill_tile_params(const EwPlan& pl, int tile, EwTileParams& P, uint32_t& blocks);
 void ew_fill_gen_params(const EwPlan& pl, EwGenParams& P);
+
+// Host side of the 2-byte tile kernel: one tensor map per operand (rows along the operand's strided dim, columns along
+// its unit-stride dim, the one batch dim as the third coordinate).  Returns false - nothing launched - for layouts the
+// maps cannot express (a stride-0 or negative row pitch, two or more batch dims, a pitch the encoder rejects); the
+// caller then runs the general tile kernel.
+template <class F, class T, class O, int NIN>
+bool ew_launch_tile16(const EwPlan& pl, const EwTileParams& TP, uint32_t blocks, const F& f, const T* a, const T* b, O* out, cudaStream_t s) {
+    if (TP.nd_batch > 1) return false;
+    const uint64_t nb = blocks / ((uint64_t)TP.tiles_p * TP.tiles_q);
+    const void* base[3] = {out, a, b};
+    CUtensorMap maps[3];
+    EwTile16Params P;
+    P.tiles_q_div = TP.tiles_q_div;
+    P.tiles_p_div = TP.tiles_p_div;
+    for (int k = 0; k <= NIN; k++) {
+        const bool tr = k != 0 && TP.transposed[k];
+        const uint64_t rows = tr ? TP.Q : TP.P, cols = tr ? TP.P : TP.Q;
+        const int64_t pitch = tr ? TP.st_q[k] : TP.st_p[k], unit = tr ? TP.st_p[k] : TP.st_q[k];
+        const int64_t bs = TP.nd_batch ? TP.st_batch[k][0] : 0;
+        if (unit != 1 || pitch <= 0 || bs < 0 || (k == 0 && nb > 1 && bs == 0)) return false;
+        P.transposed[k] = tr ? 1 : 0;
+        P.batched[k] = (nb > 1 && bs != 0) ? 1 : 0;
+        if (!tc::make_map_3d(&maps[k], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, base[k], rows, cols, nb, (uint64_t)bs, kEwT16, CU_TENSOR_MAP_SWIZZLE_128B, (uint64_t)pitch))
+            return false;
+    }
+    if (NIN == 1) {
+        maps[2] = maps[1];
+        P.transposed[2] = P.batched[2] = 0;
+    }
+    ew_tile16_kernel<F, T, O, NIN><<<blocks, kEwThreads, (NIN + 1) * kEwT16Bytes + 1024, s>>>(f, maps[1], maps[2], maps[0], P);
+    return true;
+}
 
 template <class F, class T, class O, int NIN>
 void ew_launch(const EwPlan& pl, const F& f, const T* a, const T* b, O* out, const char* where) {
@@ -785,6 +903,9 @@ void ew_launch(const EwPlan& pl, const F& f, const T* a, const T* b, O* out, con
             ew_fill_tile_params(pl, EwTile<T>::kTile, P, blocks);
             int nslots = (P.transposed[1] ? 1 : 0) + (P.transposed[2] ? 1 : 0);
             size_t smem = (size_t)nslots * EwTile<T>::kBytes;
+            if constexpr (sizeof(T) == 2 && sizeof(O) == 2) {
+                if (pl.vec && ew_launch_tile16<F, T, O, NIN>(pl, P, blocks, f, a, b, out, s)) break;
+            }
             if (pl.vec) ew_tile_kernel<F, T, O, NIN, VEC><<<blocks, kEwThreads, smem, s>>>(f, a, b, out, P);
             else ew_tile_kernel<F, T, O, NIN, 1><<<blocks, kEwThreads, smem, s>>>(f, a, b, out, P);
             break;

@@ -366,3 +366,34 @@ def test_flat_operands_at_unaligned_offsets(oracle, cuda, dt):
     a, b = H.random_store(rng, dt, 64 * 70 + 1), H.random_store(rng, dt, 2)
     args = ("add", dt, [64, 70], [70, 1], [0, 0], 1, 1, a, b)
     H.assert_same("add", dt, H.run_binary(cuda, *args), H.run_binary(oracle, *args), what="2-d + scalar")
+
+
+@pytest.mark.parametrize("dt", [D.BF16, D.F16, D.I16, D.U16], ids=lambda d: d.name)
+def test_two_byte_transposed_tiles(oracle, cuda, dt):
+    """2-byte types with vector-aligned transposed operands run on the tensor-copy tile kernel (64 x 64 boxes, ldmatrix
+    transposition): ragged edges in both dims, padded pitches, aligned base offsets, one batch dim (also broadcast for
+    one operand), and the layouts that kernel hands back to the general one (two batch dims, a stride-0 direct operand)."""
+    rng = np.random.default_rng(zlib.crc32(dt.name.encode()) + 16)
+    P, Q = 200, 136
+    cases = [
+        ("ragged", [P, Q], [1, P], [Q, 1], 0, 0, P * Q, P * Q),
+        ("ragged-both-transposed", [P, Q], [1, P], [1, P], 8, 16, P * Q + 8, P * Q + 16),
+        ("padded-pitches", [P, Q], [1, P + 24], [Q + 8, 1], 0, 8, (P + 24) * Q, (Q + 8) * P + 8),
+        ("rhs-transposed", [72, 328], [328, 1], [1, 72], 0, 0, 72 * 328, 72 * 328),
+        ("batched", [5, 72, 136], [72 * 136, 1, 72], [72 * 136, 136, 1], 0, 0, 5 * 72 * 136, 5 * 72 * 136),
+        ("batch-broadcast-rhs", [5, 72, 136], [72 * 136, 1, 72], [0, 136, 1], 0, 0, 5 * 72 * 136, 72 * 136),
+        ("two-batch-dims", [2, 3, 72, 136], [3 * 72 * 136, 72 * 136, 1, 72], [0, 72 * 136, 136, 1], 0, 0, 6 * 72 * 136, 3 * 72 * 136),
+        ("row-broadcast-rhs", [P, Q], [1, P], [0, 1], 0, 0, P * Q, Q),
+        ("single-tile", [64, 64], [1, 64], [64, 1], 0, 0, 4096, 4096),
+        ("small", [8, 16], [1, 8], [16, 1], 0, 0, 128, 128),
+    ]
+    for name, dims, ls, rs, lo, ro, ll, rl in cases:
+        if dt.kind == "float":
+            lhs, rhs = H.random_store(rng, dt, ll), H.random_store(rng, dt, rl, lo=0.5, hi=2.0)
+        else:
+            lhs, rhs = H.random_store(rng, dt, ll, lo=0 if dt.kind == "uint" else -90, hi=90), H.random_store(rng, dt, rl, lo=1, hi=90)
+        for op in ("add", "div", "maximum"):
+            args = (op, dt, dims, ls, rs, lo, ro, lhs, rhs)
+            H.assert_same(op, dt, H.run_binary(cuda, *args), H.run_binary(oracle, *args), what=name)
+        uop = "square" if dt.kind == "uint" else "neg"
+        H.assert_same(uop, dt, H.run_unary(cuda, uop, dt, dims, ls, lo, lhs), H.run_unary(oracle, uop, dt, dims, ls, lo, lhs), what=f"unary {name}")
