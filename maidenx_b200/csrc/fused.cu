@@ -35,8 +35,7 @@ __device__ __forceinline__ float up(T v) {
 }
 template <class T>
 __device__ __forceinline__ float gelu_fwd(float x) {
-    if constexpr (is_half_v<T>) return gelu_f32_fast(x);  // the same function cuda_gelu_<T> evaluates
-    else return gelu_f32(x);
+    return gelu_f32_fast(x);  // the same function cuda_gelu_<T> evaluates
 }
 
 // u = round(z + b), a = round(gelu(u)); `a` may be NULL (bias add only).  The sum is rounded to
