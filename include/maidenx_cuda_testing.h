@@ -28,6 +28,11 @@ int mx_debug_matmul_forward_path_f32(size_t num_els, const size_t* host_metadata
                                      int* b_mn_major, size_t* m, size_t* n, size_t* k);
 /* Tuning aid: row-tiles per column sweep in the one-CTA tensor-core kernel's tile order (default 16). */
 void mx_debug_set_gemm_group_m(int rows);
+/* Short reductions (K <= 256, one batch, many row tiles) keep the B panel of a column tile in shared memory and stream
+ * only A.  set: 1 = on (default), 0 = always the general schedule.  The query returns the CTAs per column tile a launch
+ * with these tile counts takes (0 = general schedule). */
+void mx_debug_set_gemm_keep_b(int on);
+int mx_debug_gemm_keep_b_ctas(int tiles_m, int tiles_n, int num_kb, int batch, int ctas);
 /* How many K slices the tensor-core path cuts a product with `tiles` output tiles and reduction length `k` into
  * (1 = no split) on `sms` SMs; block_k = 64 for bf16 / f16, 32 for f32. */
 int mx_debug_splitk_slices(size_t tiles, size_t k, int block_k, int sms);

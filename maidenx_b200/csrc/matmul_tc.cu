@@ -93,6 +93,10 @@ struct TcParams {
     const void* bias;  // fuse != 0: one element of the operand type in device memory
     int a_mn, b_mn;  // operand is MN-major in global memory ([K, MN] row-major) instead of K-major ([MN, K])
     int group_m;     // row-tiles per column sweep (L2 re-use of the A panels)
+    // Short reductions (num_kb <= STAGES, one batch): `b_keep` CTAs share each column tile, CTA j of them takes the row
+    // tiles j, j + b_keep, ...; the B panel of the column tile is loaded once into the B slots of the ring (slot = k-block,
+    // the ring is num_kb slots long) and only A streams.  0: the general schedule.
+    int b_keep;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, const TcParams& p, int& tm, int& tn, int& tb) {
@@ -106,6 +110,20 @@ __device__ __forceinline__ void tile_coords(int tile, const TcParams& p, int& tm
     const int in_group = tile - group * group_size;
     tm = first_m + in_group % rows;
     tn = in_group / rows;
+}
+
+// The it-th tile of this CTA; false when it has none left.
+__device__ __forceinline__ bool next_tile(int it, const TcParams& p, int& tm, int& tn, int& tb) {
+    if (p.b_keep) {
+        tn = (int)blockIdx.x / p.b_keep;
+        tm = (int)blockIdx.x % p.b_keep + it * p.b_keep;
+        tb = 0;
+        return tn < p.tiles_n && tm < p.tiles_m;
+    }
+    const int tile = (int)blockIdx.x + it * (int)gridDim.x;
+    if (tile >= p.num_tiles) return false;
+    tile_coords(tile, p, tm, tn, tb);
+    return true;
 }
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
@@ -165,16 +183,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-                int tm, tn, tb;
-                tile_coords(tile, p, tm, tn, tb);
+            const int ring = p.b_keep ? p.num_kb : STAGES;
+            int tm, tn, tb;
+            for (int it = 0; ok && next_tile(it, p, tm, tn, tb); it++) {
                 const int za = p.a_batched ? tb : 0, zb = p.b_batched ? tb : 0;
+                const bool load_b = !p.b_keep || it == 0;  // the kept B panel arrives with the first tile's A blocks
                 for (int kb = 0; kb < p.num_kb; kb++) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1, err, tag, 1)) {
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(full_bar(stage), A_STAGE_BYTES + B_STAGE_BYTES);
+                    mbar_expect_tx(full_bar(stage), A_STAGE_BYTES + (load_b ? B_STAGE_BYTES : 0));
                     const uint32_t sa = smem_base + SmemLayout::a + stage * A_STAGE_BYTES;
                     const uint32_t sb = smem_base + SmemLayout::b + stage * B_STAGE_BYTES;
                     if (!p.a_mn) {
@@ -183,13 +202,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int h = 0; h < BM / 64; h++) tma_load_3d(sa + h * MN_CHUNK_BYTES, &map_a, tm * BM + h * 64, kb * BK, za, full_bar(stage));
                     }
-                    if (!p.b_mn) {
+                    if (!load_b) {
+                    } else if (!p.b_mn) {
                         tma_load_3d(sb, &map_b, kb * BK, tn * BN, zb, full_bar(stage));
                     } else {
 #pragma unroll
                         for (int h = 0; h < BN / 64; h++) tma_load_3d(sb + h * MN_CHUNK_BYTES, &map_b, tn * BN + h * 64, kb * BK, zb, full_bar(stage));
                     }
-                    if (++stage == STAGES) {
+                    if (++stage == ring) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -206,7 +226,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+            const int ring = p.b_keep ? p.num_kb : STAGES;
+            int tm, tn, tb;
+            for (int it = 0; ok && next_tile(it, p, tm, tn, tb); it++) {
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, err, tag, 2)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
@@ -221,7 +243,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; k++) umma_f16(d_tmem, da + a_kstep * k, db + b_kstep * k, idesc, (kb | k) != 0);
                     umma_commit(empty_bar(stage));  // the stage may be refilled once these MMAs have read it
-                    if (++stage == STAGES) {
+                    if (++stage == ring) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -243,58 +265,41 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t acc_phase = 0;
         float fused_bias = 0.0f;
         if (p.fuse) fused_bias = p.is_bf16 ? to_f32(*static_cast<const bf16*>(p.bias)) : to_f32(*static_cast<const f16*>(p.bias));
-        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
-            int tm, tn, tb;
-            tile_coords(tile, p, tm, tn, tb);
+        int tm, tn, tb;
+        for (int it = 0; next_tile(it, p, tm, tn, tb); it++) {
             // the TMEM loads below are warp-collective: leave the loop only as a whole warp
             const bool ready = mbar_wait(tfull_bar(acc), acc_phase, err, tag, 4);
             if (!__all_sync(0xFFFFFFFFu, ready)) break;
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
-#pragma unroll 1
-            for (int c = 0; c < BN / EPI_CHUNK_COLS; c++) {
-                uint32_t v0[32], v1[32];
-                tmem_ld_32x32b_x32(t_row + c * EPI_CHUNK_COLS, v0);
-                tmem_ld_32x32b_x32(t_row + c * EPI_CHUNK_COLS + 32, v1);
-                tmem_ld_wait();
-                if (c == BN / EPI_CHUNK_COLS - 1) {
-                    // every TMEM read of this accumulator is done: hand it back to the MMA warp
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty_bar(acc));
-                }
+            // One 64-column chunk: round, stage in shared memory (XOR-swizzled rows), hand to the copy engine.
+            auto store_chunk = [&](int c, uint32_t (&v0)[32], uint32_t (&v1)[32]) {
                 if (p.fuse) {
                     // Linear + bias (+ GELU) in one pass, with the roundings of the separate ops: the product is rounded to
                     // the operand type, the bias is added in f32 and rounded (u), the activation is evaluated on u in f32
                     // and rounded (act) - bit for bit what cuda_matmul, cuda_add and cuda_gelu give one after the other.
-                    uint32_t act0[32], act1[32];
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
-                        const float u0 = round16(round16(__uint_as_float(v0[j]), p.is_bf16) + fused_bias, p.is_bf16);
-                        const float u1 = round16(round16(__uint_as_float(v1[j]), p.is_bf16) + fused_bias, p.is_bf16);
-                        v0[j] = __float_as_uint(u0);
-                        v1[j] = __float_as_uint(u1);
-                        if (p.fuse == 2) {
-                            act0[j] = __float_as_uint(gelu_f32_fast(u0));
-                            act1[j] = __float_as_uint(gelu_f32_fast(u1));
-                        }
+                        v0[j] = __float_as_uint(round16(round16(__uint_as_float(v0[j]), p.is_bf16) + fused_bias, p.is_bf16));
+                        v1[j] = __float_as_uint(round16(round16(__uint_as_float(v1[j]), p.is_bf16) + fused_bias, p.is_bf16));
                     }
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
                         if (h == 1 && p.fuse != 2) break;
-                        const uint32_t* w0 = h ? act0 : v0;
-                        const uint32_t* w1 = h ? act1 : v1;
                         if (lane == 0) tma_store_wait_read<1>();
                         __syncwarp();
                         unsigned char* dst = stage_buf + buf * EPI_STAGE_BYTES + lane * 128;
 #pragma unroll
                         for (int j = 0; j < 8; j++) {
-                            const uint32_t* src = j < 4 ? &w0[j * 8] : &w1[(j - 4) * 8];
+                            const uint32_t* src = j < 4 ? &v0[j * 8] : &v1[(j - 4) * 8];
+                            float e[8];
+#pragma unroll
+                            for (int k = 0; k < 8; k++) e[k] = h ? gelu_f32_fast(__uint_as_float(src[k])) : __uint_as_float(src[k]);  // second pass: the activation of u
                             uint4 q;
-                            q.x = pack2(__uint_as_float(src[0]), __uint_as_float(src[1]), p.is_bf16);
-                            q.y = pack2(__uint_as_float(src[2]), __uint_as_float(src[3]), p.is_bf16);
-                            q.z = pack2(__uint_as_float(src[4]), __uint_as_float(src[5]), p.is_bf16);
-                            q.w = pack2(__uint_as_float(src[6]), __uint_as_float(src[7]), p.is_bf16);
+                            q.x = pack2(e[0], e[1], p.is_bf16);
+                            q.y = pack2(e[2], e[3], p.is_bf16);
+                            q.z = pack2(e[4], e[5], p.is_bf16);
+                            q.w = pack2(e[6], e[7], p.is_bf16);
                             *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = q;
                         }
                         fence_proxy_async_smem();
@@ -305,7 +310,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         }
                         buf ^= 1;
                     }
-                    continue;
+                    return;
                 }
                 if (p.out_f32) {
                     // two 32-column f32 chunks (128 bytes per row each), one per staging buffer
@@ -326,7 +331,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         }
                         buf ^= 1;
                     }
-                    continue;
+                    return;
                 }
                 // the staging buffer must have been read by its previous TMA store
                 if (lane == 0) tma_store_wait_read<1>();
@@ -349,6 +354,30 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tma_store_commit();
                 }
                 buf ^= 1;
+            };
+            // The TMEM loads of chunk c + 1 are in flight while chunk c is converted and stored.
+            uint32_t a0[32], a1[32], b0[32], b1[32];
+            tmem_ld_32x32b_x32(t_row, a0);
+            tmem_ld_32x32b_x32(t_row + 32, a1);
+#pragma unroll
+            for (int c = 0; c < BN / EPI_CHUNK_COLS; c += 2) {
+                tmem_ld_wait_for(a0);
+                reg_fence(a1);
+                tmem_ld_32x32b_x32(t_row + (c + 1) * EPI_CHUNK_COLS, b0);
+                tmem_ld_32x32b_x32(t_row + (c + 1) * EPI_CHUNK_COLS + 32, b1);
+                store_chunk(c, a0, a1);
+                tmem_ld_wait_for(b0);
+                reg_fence(b1);
+                if (c + 2 < BN / EPI_CHUNK_COLS) {
+                    tmem_ld_32x32b_x32(t_row + (c + 2) * EPI_CHUNK_COLS, a0);
+                    tmem_ld_32x32b_x32(t_row + (c + 2) * EPI_CHUNK_COLS + 32, a1);
+                } else {
+                    // every TMEM read of this accumulator is done: hand it back to the MMA warp
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(acc));
+                }
+                store_chunk(c + 1, b0, b1);
             }
             if (++acc == 2) {
                 acc = 0;
@@ -402,6 +431,18 @@ bool opt_in_shared_memory() {
 // D[M,N] = sum_k Aop[m,k] * Bop[n,k].  A K-major operand is a dense row-major [MN, K] matrix, an
 // MN-major operand a dense row-major [K, MN] matrix; D is dense row-major [M, N].
 // fuse: 0 plain product; 1 D = round(round(product) + bias); 2 also D2 = round(gelu(D)) (see the kernel's epilogue)
+std::atomic<int> g_keep_b{1};  // 0: the B-panel-resident schedule is never taken (tests, A/B timing)
+
+// CTAs per column tile of the schedule that keeps the B panel of a column tile in shared memory (0 = general schedule).
+// Taken when the whole reduction fits the ring (K <= STAGES * BK), there is one batch, and every CTA gets at least four
+// row tiles to spread the panel's load over.  With K = 256 a 128 x 256 tile otherwise loads 192 KB to do 2048 cycles
+// of tensor work; with the panel resident it loads the 64 KB of A.
+int keep_b_ctas(int tiles_m, int tiles_n, int num_kb, int batch, int ctas) {
+    if (!g_keep_b.load(std::memory_order_relaxed) || batch != 1 || num_kb > STAGES || tiles_n > ctas) return 0;
+    const int per_col = ctas / tiles_n;
+    return tiles_m >= 4 * per_col ? per_col : 0;
+}
+
 bool launch_gemm(bool is_bf16, const TcProduct& c, void* D, const char* where, int fuse = 0, const void* bias = nullptr, void* D2 = nullptr) {
     const void *A = c.A, *B = c.B;
     const bool a_mn = c.a_mn, b_mn = c.b_mn;
@@ -481,6 +522,8 @@ bool launch_gemm(bool is_bf16, const TcProduct& c, void* D, const char* where, i
     p.a_mn = a_mn ? 1 : 0;
     p.b_mn = b_mn ? 1 : 0;
     if (grid > p.num_tiles) grid = p.num_tiles;
+    p.b_keep = keep_b_ctas(p.tiles_m, p.tiles_n, p.num_kb, (int)batch, grid);
+    if (p.b_keep) grid = p.b_keep * p.tiles_n;
     tc_gemm_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx().stream>>>(ma, mb, md, md2, p, err, tag);
     check_launch(where);
     if (partial) splitk_reduce(is_bf16 ? 0 : 1, partial, slices, (size_t)(M * N), D, where);
@@ -801,6 +844,9 @@ static int debug_forward_path(size_t es, size_t num_els, const size_t* host_meta
 // 2: bf16 / f16 products run on the two-CTA kernel (pairs of SMs share the B tile); 1: on the one-CTA kernel.
 extern "C" void mx_set_gemm_cta_group(int ctas) { mx::g_two_cta.store(ctas == 2, std::memory_order_relaxed); }
 extern "C" void mx_debug_set_gemm_group_m(int rows) { mx::g_group_m.store(rows > 0 ? rows : 16, std::memory_order_relaxed); }
+// 1 (default): products with a reduction of at most 256 run with the B panel resident in shared memory; 0: general schedule
+extern "C" void mx_debug_set_gemm_keep_b(int on) { mx::g_keep_b.store(on ? 1 : 0, std::memory_order_relaxed); }
+extern "C" int mx_debug_gemm_keep_b_ctas(int tiles_m, int tiles_n, int num_kb, int batch, int ctas) { return mx::keep_b_ctas(tiles_m, tiles_n, num_kb, batch, ctas); }
 extern "C" int mx_debug_splitk_slices(size_t tiles, size_t k, int block_k, int sms) { return mx::tc::splitk_slices(tiles, k, block_k, sms); }
 extern "C" int mx_debug_matmul_forward_path(size_t num_els, const size_t* host_metadata, const void* a, const void* b, const void* out, int* a_mn_major,
                                             int* b_mn_major, size_t* m, size_t* n, size_t* k) {

@@ -318,3 +318,35 @@ def test_two_cta_kernel_on_the_small_batched_and_backward_cases(oracle, cuda, dt
         test_matmul_backward(oracle, cuda, dt)
     finally:
         lib.mx_set_gemm_cta_group(1)
+
+
+SHORT_K = [
+    ("keepb-nt", 25640, 600, 256, "k", "k"),      # 201 row tiles (40-row edge), 3 column tiles (88-column edge): 49 CTAs per column tile
+    ("keepb-nn", 25640, 600, 256, "k", "mn"),
+    ("keepb-tn", 25640, 600, 192, "mn", "mn"),    # three k-blocks: the ring is three slots long
+    ("keepb-ragged-k", 25640, 520, 136, "k", "k"),
+    ("keepb-one-kb", 151 * 128, 2304, 64, "k", "mn"),
+]
+
+
+@pytest.mark.parametrize("dt", [D.BF16, D.F16], ids=lambda d: d.name)
+@pytest.mark.parametrize("case", SHORT_K, ids=lambda c: c[0])
+def test_short_reductions_with_the_b_panel_resident(oracle, cuda, dt, case):
+    """K <= 256 with many row tiles: the CTAs of a column tile load its B panel once and stream only A.  Against the
+    oracle on sampled rows, and bit for bit against the general schedule of the same kernel."""
+    from maidenx_b200 import _lib
+    lib = _lib.load()
+    name, m, n, k, amaj, bmaj = case
+    assert lib.mx_debug_gemm_keep_b_ctas((m + 127) // 128, (n + 255) // 256, (k + 63) // 64, 1, 148) > 0
+    test_matmul_forward_many_tiles(oracle, cuda, dt, case)
+    rng = np.random.default_rng(zlib_seed(name))
+    a = H.random_store(rng, dt, m * k, dist="normal")
+    b = H.random_store(rng, dt, k * n, dist="normal")
+    meta = H.matmul_metadata([m, n], [m, k], [k, n], [k, 1] if amaj == "k" else [1, m], [1, k] if bmaj == "k" else [n, 1], 0, 0)
+    kept = H.run_matmul(cuda, dt, meta, m * n, a, b)
+    lib.mx_debug_set_gemm_keep_b(0)
+    try:
+        general = H.run_matmul(cuda, dt, meta, m * n, a, b)
+    finally:
+        lib.mx_debug_set_gemm_keep_b(1)
+    assert np.array_equal(kept, general)

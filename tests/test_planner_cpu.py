@@ -131,3 +131,15 @@ def test_split_k_plan():
     for tiles, k in ((1, 1 << 20), (3, 65536), (10, 16384)):
         s_ = sk(tiles, k, 64, 148)
         assert s_ >= 1 and (k // 64) % s_ == 0 and k // s_ >= 1024
+
+
+def test_b_panel_resident_schedule_is_for_short_reductions_with_many_row_tiles():
+    lib = _lib.load()
+    keep = lib.mx_debug_gemm_keep_b_ctas
+    assert keep(1568, 9, 4, 1, 148) == 16      # the conv input-gradient product (200704 x 2304 x 256): 16 CTAs per column tile
+    assert keep(1568, 9, 5, 1, 148) == 0       # K = 320 does not fit the four-slot ring
+    assert keep(1568, 9, 4, 2, 148) == 0       # batched products keep the general schedule
+    assert keep(40, 9, 4, 1, 148) == 0         # too few row tiles per CTA to spread the panel's load over
+    assert keep(1568, 200, 4, 1, 148) == 0     # more column tiles than CTAs
+    assert keep(400, 1, 2, 1, 148) == 0        # 148 CTAs on one column tile: fewer than four row tiles each
+    assert keep(1000, 1, 2, 1, 148) == 148
