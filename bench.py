@@ -164,11 +164,23 @@ class Launcher:
             self.args = (SZ(c.num_els), SZ(3), m, bufs["a"], bufs["out"])
         elif c.family in ("im2col", "col2im"):
             self.args = (SZ(c.num_els), m, bufs["a"], bufs["out"])
+        elif c.family == "softmax":
+            self.args = (SZ(c.num_els), SZ(2), SZ(c.extra["dim"]), m, bufs["a"], bufs["out"])
+        elif c.family in ("pad", "pad_backward"):
+            self.args = (SZ(c.num_els), SZ(c.extra["n_out"]), SZ(4), m, bufs["a"], bufs["out"]) + pad_value_arg(c)
         else:
             raise KeyError(c.family)
 
     def launch(self):
         self.fn(*self.args)
+
+
+def pad_value_arg(c):
+    """The by-value fill constant of pad_with_constant (0.5); the other padding entry points take none."""
+    if not c.extra.get("constant"):
+        return ()
+    from maidenx_b200 import dtypes as D
+    return (D.scalar_arg(0.5, D.BY_NAME[c.dtype]),)
 
 
 TORCH_DT = None
@@ -348,6 +360,43 @@ def verify_case(torch, c, a, b, out):
                 got = to_store(out[img * x_img:(img + 1) * x_img])
             ok = ok and close(got, ref, dt, 0.0, 0.0)
         return ok
+    if c.family == "softmax":
+        R, C = c.metadata[0], c.metadata[1]
+        x, y = a[:R * C].view(R, C), out[:R * C].view(R, C)
+        if c.extra["dim"] == 1:   # whole rows
+            idx = torch.as_tensor(sample_rows(R, 12, C), device="cuda")
+            sub, got, shape = to_store(x[idx]), to_store(y[idx]), (len(idx), C)
+        else:                     # whole columns
+            idx = torch.as_tensor(sample_rows(C, 64, R), device="cuda")
+            sub, got, shape = to_store(x[:, idx]), to_store(y[:, idx]), (R, len(idx))
+        m = np.asarray([shape[0], shape[1], shape[1], 1, 0], dtype=np.uint64)
+        ref = np.empty(shape[0] * shape[1], st)
+        binding.set_wide(True)   # exp and the sum in f32 for 16-bit inputs, as the kernel computes them
+        try:
+            oracle_call("softmax", dt, SZ(ref.size), SZ(2), SZ(c.extra["dim"]), m.ctypes.data, sub.ctypes.data, ref.ctypes.data)
+        finally:
+            binding.set_wide(False)
+        return close(got, ref, dt, 1e-5 if dt == "f32" else 2e-2, 1e-30 if dt == "f32" else 1e-4)
+    if c.family in ("pad", "pad_backward"):
+        # whole images: the first and the last of the batch
+        Bn, Cc, H, W = c.metadata[0:4]
+        Ho, Wo = c.metadata[11], c.metadata[12]
+        in_img, out_img = Cc * H * W, Cc * Ho * Wo
+        m = np.asarray([1] + list(c.metadata[1:9]) + [1] + list(c.metadata[10:]), dtype=np.uint64)
+        ok = True
+        for img in (0, Bn - 1):
+            if c.family == "pad":
+                src = to_store(a[img * in_img:(img + 1) * in_img])
+                ref = np.empty(out_img, st)
+                oracle_call(c.op, dt, SZ(in_img), SZ(out_img), SZ(4), m.ctypes.data, src.ctypes.data, ref.ctypes.data, *pad_value_arg(c))
+                got = to_store(out[img * out_img:(img + 1) * out_img])
+            else:
+                src = to_store(a[img * out_img:(img + 1) * out_img])
+                ref = np.empty(in_img, st)
+                oracle_call(c.op, dt, SZ(in_img), SZ(out_img), SZ(4), m.ctypes.data, src.ctypes.data, ref.ctypes.data)
+                got = to_store(out[img * in_img:(img + 1) * in_img])
+            ok = ok and close(got, ref, dt, 0.0, 0.0)
+        return ok
     raise KeyError(c.family)
 
 
@@ -407,6 +456,10 @@ def cpu_time_cases(cases, dist, passes=2):
             args = (SZ(c.num_els), SZ(2), SZ(c.extra["num_red"]), m.ctypes.data, a.ctypes.data, o.ctypes.data)
         elif c.family == "sum_to_shape":
             args = (SZ(c.num_els), SZ(3), m.ctypes.data, a.ctypes.data, o.ctypes.data)
+        elif c.family == "softmax":
+            args = (SZ(c.num_els), SZ(2), SZ(c.extra["dim"]), m.ctypes.data, a.ctypes.data, o.ctypes.data)
+        elif c.family in ("pad", "pad_backward"):
+            args = (SZ(c.num_els), SZ(c.extra["n_out"]), SZ(4), m.ctypes.data, a.ctypes.data, o.ctypes.data) + pad_value_arg(c)
         else:
             args = (SZ(c.num_els), m.ctypes.data, a.ctypes.data, o.ctypes.data)
         fn = binding.op(c.op, c.dtype)
@@ -1080,7 +1133,8 @@ def main():
         with_cpu = not args.no_cpu
         groups = (("elementwise", sweeps.elementwise_cases(), sweeps.elementwise_cases(1024, 16384), (1, 101), "uniform"),
                   ("reduction", sweeps.reduction_cases(), sweeps.reduction_cases(512, 16384, (4, 512, 4096)), (3, 103), "normal"),
-                  ("conv", sweeps.conv_cases(), sweeps.conv_cases(N=2), (10, 110), "normal"))
+                  ("conv", sweeps.conv_cases(), sweeps.conv_cases(N=2), (10, 110), "normal"),
+                  ("extras", sweeps.extras_cases(), sweeps.extras_cases(rows=512, N=2), (12, 112), "normal"))
         cores = None
         for name, cases, small_cases, seeds, kind in groups:
             rows, cores_g = run_sweep_group(torch, lib_mod, cases, small_cases, 10, 3, seeds, kind, peaks, verify, with_cpu)
@@ -1099,7 +1153,7 @@ def main():
         sweeps_out["config1"] = config1_row(torch, lib, with_cpu=with_cpu)
         hbm_rows = sweeps_out["elementwise"] + sweeps_out["reduction"] + sweeps_out["conv"] + sweeps_out["movement"]
         ew = sweeps_out["elementwise"]
-        summary = {g: summarize(sweeps_out[g]) for g in ("elementwise", "reduction", "conv", "movement")}
+        summary = {g: summarize(sweeps_out[g]) for g in ("elementwise", "reduction", "conv", "movement", "extras")}
         summary["all_hbm_cases"] = summarize(hbm_rows)
         summary["all_hbm_cases"]["min_frac_of_nominal_8000"] = round(min(r["gbs"] for r in hbm_rows) / NOMINAL_HBM_GBS, 4)
         summary["all_hbm_cases"]["median_frac_of_nominal_8000"] = round(sorted(r["gbs"] for r in hbm_rows)[len(hbm_rows) // 2] / NOMINAL_HBM_GBS, 4)
@@ -1140,9 +1194,9 @@ def run_only_case(torch, lib_mod, args):
     """Launch one sweep case a few times (for ncu captures of a single kernel)."""
     peaks = measured_peaks()
     if args.small:
-        groups = sweeps.elementwise_cases(8192, 8192) + sweeps.reduction_cases(4096, 16384, (16, 512, 4096)) + sweeps.conv_cases(N=16)
+        groups = sweeps.elementwise_cases(8192, 8192) + sweeps.reduction_cases(4096, 16384, (16, 512, 4096)) + sweeps.conv_cases(N=16) + sweeps.extras_cases(rows=4096, N=16)
     else:
-        groups = sweeps.elementwise_cases() + sweeps.reduction_cases() + sweeps.conv_cases()
+        groups = sweeps.elementwise_cases() + sweeps.reduction_cases() + sweeps.conv_cases() + sweeps.extras_cases()
     if args.only_case.startswith("gemm_"):
         # gemm_<bf16|f16|f32>[_<MxNxK>[_<nt|nn|tn|tt>]]: a product alone; default x . W^T of one MLP layer; --small: 8192 x 4096 x 8192
         parts = args.only_case.split("_")

@@ -176,6 +176,143 @@ __global__ void __launch_bounds__(kExThreads) pad_backward_scatter_kernel(const 
     }
 }
 
+// The same gather for the common sizes (outputs below 2^32 elements, at most four dims after size-1 dims are dropped and
+// neighbouring unpadded dims merged - an [N, C, H, W] batch padded along H and W is [N*C, H, W]): the rank is a
+// compile-time constant, so coordinates live in registers, all index arithmetic is 32-bit, and a thread produces one
+// 16-byte vector of consecutive output elements: the output index is split once per vector (multiply-shift division),
+// the outer dims' source offset is kept while the last coordinate advances and recomputed only when it wraps.
+constexpr int kPadFastDims = 4;
+struct PadFastParams {
+    int nd;
+    FastDiv div[kPadFastDims];                                              // forward: by out_dims; crop: by in_dims
+    u32 out_dims[kPadFastDims], in_dims[kPadFastDims], before[kPadFastDims];
+    u64 mul[kPadFastDims];                                                  // forward: element step per input dim; crop: per grad_out dim
+    u64 in_off;
+    u32 n_out, n_in;
+};
+
+template <int MODE>
+__device__ __forceinline__ bool pad_source32(int oc, int before, int size, int& ic) {
+    int pos = oc - before;
+    if (MODE == PAD_CONSTANT) {
+        if (pos < 0 || pos >= size) return false;
+    } else if (MODE == PAD_REFLECTION) {
+        for (int guard = 0; (pos < 0 || pos >= size) && guard < 64; guard++) pos = pos < 0 ? -pos : 2 * size - pos - 2;
+        if (pos < 0 || pos >= size) pos = 0;
+    } else {
+        pos = pos < 0 ? 0 : (pos > size - 1 ? size - 1 : pos);
+    }
+    ic = pos;
+    return true;
+}
+
+template <class T, int MODE, int ND>
+__global__ void __launch_bounds__(kExThreads) pad_forward_fast_kernel(const T* __restrict__ in, T* __restrict__ out, T pad_value, PadFastParams P) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    constexpr int last = ND - 1;
+    const u64 v0 = ((u64)blockIdx.x * kExThreads + threadIdx.x) * VEC;
+    if (v0 >= P.n_out) return;
+    u32 oc[ND];
+    u32 r = (u32)v0;
+#pragma unroll
+    for (int d = last; d >= 0; d--) P.div[d].divmod(r, r, oc[d]);
+    bool outer_in = true;
+    u64 outer_base = P.in_off;
+    auto outer = [&]() {
+        outer_in = true;
+        outer_base = P.in_off;
+#pragma unroll
+        for (int d = 0; d < last; d++) {
+            int ic = 0;
+            outer_in = outer_in && pad_source32<MODE>((int)oc[d], (int)P.before[d], (int)P.in_dims[d], ic);
+            outer_base += (u64)(u32)ic * P.mul[d];
+        }
+    };
+    outer();
+    Vec<T, VEC> res;
+    const u32 count = P.n_out - (u32)v0 < (u32)VEC ? P.n_out - (u32)v0 : (u32)VEC;
+#pragma unroll
+    for (int j = 0; j < VEC; j++) {
+        if ((u32)j < count) {
+            int ic = 0;
+            const bool inside = pad_source32<MODE>((int)oc[last], (int)P.before[last], (int)P.in_dims[last], ic) && outer_in;
+            res.v[j] = inside ? in[outer_base + (u64)(u32)ic * P.mul[last]] : pad_value;
+            if (++oc[last] == P.out_dims[last]) {
+                oc[last] = 0;
+                bool carry = true;
+#pragma unroll
+                for (int d = last - 1; d >= 0; d--) {
+                    if (carry) {
+                        if (++oc[d] < P.out_dims[d]) carry = false;
+                        else oc[d] = 0;
+                    }
+                }
+                outer();
+            }
+        }
+    }
+    if (count == (u32)VEC && reinterpret_cast<uintptr_t>(out + v0) % 16 == 0) {
+        *reinterpret_cast<Vec<T, VEC>*>(out + v0) = res;
+    } else {
+#pragma unroll
+        for (int j = 0; j < VEC; j++)
+            if ((u32)j < count) out[v0 + j] = res.v[j];
+    }
+}
+
+// Backward of constant padding over a contiguous input: every input element was read by exactly one output element,
+// so the gradient is a cropped copy - no accumulation, no workspace.
+template <class T, int ND>
+__global__ void __launch_bounds__(kExThreads) pad_constant_backward_crop_kernel(const T* __restrict__ grad_out, T* __restrict__ grad_in, PadFastParams P) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    constexpr int last = ND - 1;
+    const u64 v0 = ((u64)blockIdx.x * kExThreads + threadIdx.x) * VEC;
+    if (v0 >= P.n_in) return;
+    u32 ic[ND];
+    u32 r = (u32)v0;
+#pragma unroll
+    for (int d = last; d >= 0; d--) P.div[d].divmod(r, r, ic[d]);
+    auto outer = [&]() {
+        u64 base = 0;
+#pragma unroll
+        for (int d = 0; d < last; d++) base += (u64)(ic[d] + P.before[d]) * P.mul[d];
+        return base;
+    };
+    u64 outer_base = outer();
+    Vec<T, VEC> res;
+    const u32 count = P.n_in - (u32)v0 < (u32)VEC ? P.n_in - (u32)v0 : (u32)VEC;
+#pragma unroll
+    for (int j = 0; j < VEC; j++) {
+        if ((u32)j < count) {
+            res.v[j] = grad_out[outer_base + (u64)(ic[last] + P.before[last]) * P.mul[last]];
+            if (++ic[last] == P.in_dims[last]) {
+                ic[last] = 0;
+                bool carry = true;
+#pragma unroll
+                for (int d = last - 1; d >= 0; d--) {
+                    if (carry) {
+                        if (++ic[d] < P.in_dims[d]) carry = false;
+                        else ic[d] = 0;
+                    }
+                }
+                outer_base = outer();
+            }
+        }
+    }
+    T* dst = grad_in + P.in_off + v0;
+    if (count == (u32)VEC && reinterpret_cast<uintptr_t>(dst) % 16 == 0) {
+        *reinterpret_cast<Vec<T, VEC>*>(dst) = res;
+    } else {
+#pragma unroll
+        for (int j = 0; j < VEC; j++)
+            if ((u32)j < count) dst[j] = res.v[j];
+    }
+}
+
+// Fills F from P for the forward gather (crop = false: `mul` = input steps, `div` by out_dims) or the cropped copy
+// (crop = true: `mul` = dense grad_out steps, `div` by in_dims).  Returns false when the shape does not fit the fast form.
+static bool pad_fast_params(PadFastParams& F, const PadParams& P, bool crop);
+
 static bool pad_params(PadParams& P, size_t n_in, size_t n_out, size_t nd, const size_t* meta, const char* where) {
     const size_t* hm = resolve_metadata(meta, 5 * nd + 1);
     if (!hm || nd > (size_t)kExMaxDims) {
@@ -203,11 +340,72 @@ static bool pad_params(PadParams& P, size_t n_in, size_t n_out, size_t nd, const
     return true;
 }
 
+static bool pad_fast_params(PadFastParams& F, const PadParams& P, bool crop) {
+    if (P.nd < 1 || P.n_out >= (1ull << 32) || P.n_in >= (1ull << 32)) return false;
+    if (crop && !P.contiguous) return false;
+    u64 in_step[kExMaxDims], out_step[kExMaxDims], in_total = 1, out_total = 1;
+    for (int d = P.nd - 1; d >= 0; d--) {
+        if (P.out_dims[d] >= (1ull << 31) || P.in_dims[d] >= (1ull << 31) || P.before[d] >= (1ull << 31)) return false;
+        if (crop && P.before[d] + P.in_dims[d] > P.out_dims[d]) return false;  // a source outside grad_out
+        in_step[d] = P.contiguous ? in_total : P.in_strides[d];
+        out_step[d] = out_total;
+        in_total *= P.in_dims[d];
+        out_total *= P.out_dims[d];
+    }
+    if (out_total != P.n_out || (crop && in_total != P.n_in)) return false;
+    int k = 0;
+    bool prev_plain = false;
+    for (int d = 0; d < P.nd; d++) {
+        if (P.in_dims[d] == 1 && P.out_dims[d] == 1) continue;  // contributes nothing to either index
+        const bool plain = P.in_dims[d] == P.out_dims[d] && P.before[d] == 0;
+        // an unpadded dim joins the unpadded dim before it when the two are one run in the source
+        if (plain && prev_plain && F.mul[k - 1] == (crop ? out_step[d] * P.out_dims[d] : in_step[d] * P.in_dims[d]) && (u64)F.in_dims[k - 1] * P.in_dims[d] < (1ull << 31)) {
+            F.in_dims[k - 1] *= (u32)P.in_dims[d];
+            F.out_dims[k - 1] = F.in_dims[k - 1];
+            F.mul[k - 1] = crop ? out_step[d] : in_step[d];
+        } else {
+            if (k == kPadFastDims) return false;
+            F.in_dims[k] = (u32)P.in_dims[d];
+            F.out_dims[k] = (u32)P.out_dims[d];
+            F.before[k] = (u32)P.before[d];
+            F.mul[k] = crop ? out_step[d] : in_step[d];
+            k++;
+        }
+        prev_plain = plain;
+    }
+    if (k == 0) {  // every dim has extent 1
+        F.in_dims[0] = F.out_dims[0] = 1;
+        F.before[0] = 0;
+        F.mul[0] = 1;
+        k = 1;
+    }
+    F.nd = k;
+    for (int d = 0; d < k; d++) F.div[d].init(crop ? F.in_dims[d] : F.out_dims[d]);
+    F.in_off = P.in_off;
+    F.n_out = (u32)P.n_out;
+    F.n_in = (u32)P.n_in;
+    return true;
+}
+
 template <class T, int MODE>
 void pad_forward_entry(size_t n_in, size_t n_out, size_t nd, const size_t* meta, const T* in, T* out, T pad_value, const char* where) {
     if (n_out == 0) return;
     PadParams P;
     if (!pad_params(P, n_in, n_out, nd, meta, where)) return;
+    PadFastParams F;
+    if (pad_fast_params(F, P, false)) {
+        constexpr int VEC = 16 / (int)sizeof(T);
+        const unsigned blocks = (unsigned)(((n_out + VEC - 1) / VEC + kExThreads - 1) / kExThreads);
+        cudaStream_t st = ctx().stream;
+        switch (F.nd) {
+            case 1: pad_forward_fast_kernel<T, MODE, 1><<<blocks, kExThreads, 0, st>>>(in, out, pad_value, F); break;
+            case 2: pad_forward_fast_kernel<T, MODE, 2><<<blocks, kExThreads, 0, st>>>(in, out, pad_value, F); break;
+            case 3: pad_forward_fast_kernel<T, MODE, 3><<<blocks, kExThreads, 0, st>>>(in, out, pad_value, F); break;
+            default: pad_forward_fast_kernel<T, MODE, 4><<<blocks, kExThreads, 0, st>>>(in, out, pad_value, F); break;
+        }
+        check_launch(where);
+        return;
+    }
     pad_forward_kernel<T, MODE><<<ex_blocks(n_out), kExThreads, 0, ctx().stream>>>(in, out, pad_value, P);
     check_launch(where);
 }
@@ -218,6 +416,20 @@ void pad_backward_entry(size_t n_in, size_t n_out, size_t nd, const size_t* meta
     if (n_in == 0) return;
     PadParams P;
     if (!pad_params(P, n_in, n_out, nd, meta, where)) return;
+    PadFastParams F;
+    if (MODE == PAD_CONSTANT && pad_fast_params(F, P, true)) {
+        constexpr int VEC = 16 / (int)sizeof(T);
+        const unsigned blocks = (unsigned)(((n_in + VEC - 1) / VEC + kExThreads - 1) / kExThreads);
+        cudaStream_t st = ctx().stream;
+        switch (F.nd) {
+            case 1: pad_constant_backward_crop_kernel<T, 1><<<blocks, kExThreads, 0, st>>>(grad_out, grad_in, F); break;
+            case 2: pad_constant_backward_crop_kernel<T, 2><<<blocks, kExThreads, 0, st>>>(grad_out, grad_in, F); break;
+            case 3: pad_constant_backward_crop_kernel<T, 3><<<blocks, kExThreads, 0, st>>>(grad_out, grad_in, F); break;
+            default: pad_constant_backward_crop_kernel<T, 4><<<blocks, kExThreads, 0, st>>>(grad_out, grad_in, F); break;
+        }
+        check_launch(where);
+        return;
+    }
     Acc* ws = static_cast<Acc*>(scratch(sizeof(Acc) * n_in));
     if (!ws) return;
     cudaStream_t s = ctx().stream;
@@ -300,6 +512,162 @@ __global__ void __launch_bounds__(kExThreads) softmax_kernel(const T* in, T* out
     }
 }
 
+// Contiguous input, softmax along the last dim, rows short enough for the registers of their thread group (a warp for
+// rows up to 8 vectors per lane, else the block): every element is read once and written once, as 16-byte vectors.
+// Same formulas as above (comparison-based maximum, exp(x - max), quotient by the sum); the sum is a tree over the
+// group instead of the block-strided partial sums.
+__device__ __forceinline__ float exp2_approx(float v) {
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(v));
+    return e;
+}
+
+template <class A, int G, bool IS_MAX>
+__device__ __forceinline__ A softmax_group_all(A v, A* part) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const A w = __shfl_xor_sync(0xFFFFFFFFu, v, o);
+        v = IS_MAX ? (w > v ? w : v) : v + w;
+    }
+    if constexpr (G > 32) {
+        __syncthreads();  // the previous use of `part` has been read
+        if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+        __syncthreads();
+        v = part[0];
+#pragma unroll
+        for (int w = 1; w < G / 32; w++) v = IS_MAX ? (part[w] > v ? part[w] : v) : v + part[w];
+    }
+    return v;
+}
+
+template <class T, int G, int K>
+__global__ void __launch_bounds__(kExThreads) softmax_rows_kernel(const T* __restrict__ in, T* __restrict__ out, u64 rows, u32 n) {
+    typedef typename std::conditional<std::is_same<T, f64>::value, f64, f32>::type A;
+    constexpr int VEC = 16 / (int)sizeof(T);
+    __shared__ A part[kExThreads / 32];
+    const int t = threadIdx.x % G;
+    const u64 row = (u64)blockIdx.x * (kExThreads / G) + threadIdx.x / G;
+    if (G == 32 && row >= rows) return;  // whole warps; the warp form uses no block barrier
+    const T* src = in + row * n;
+    A x[K][VEC];
+    A mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < K; k++) {
+        const u32 i = (u32)(k * G + t) * VEC;
+        if (i < n) {
+            const Vec<T, VEC> v = *reinterpret_cast<const Vec<T, VEC>*>(src + i);
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                if constexpr (is_half_v<T>) x[k][j] = to_f32(v.v[j]);
+                else x[k][j] = (A)v.v[j];
+                mx = x[k][j] > mx ? x[k][j] : mx;  // a NaN never becomes the maximum
+            }
+        }
+    }
+    mx = softmax_group_all<A, G, true>(mx, part);
+    A sum = (A)0;
+#pragma unroll
+    for (int k = 0; k < K; k++) {
+        if ((u32)(k * G + t) * VEC < n) {
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                if constexpr (std::is_same<A, f64>::value) x[k][j] = exp(x[k][j] - mx);
+                else if constexpr (is_half_v<T>) x[k][j] = exp2_approx((x[k][j] - mx) * 1.4426950408889634f);  // error ~1e-5 of a 16-bit step
+                else x[k][j] = expf(x[k][j] - mx);
+                sum += x[k][j];
+            }
+        }
+    }
+    sum = softmax_group_all<A, G, false>(sum, part);
+    // f32 / 16-bit: one reciprocal per row and a multiply per element (within 1.5 ulp of the quotient); f64 divides
+    const A inv = (A)1 / sum;
+    T* dst = out + row * n;
+#pragma unroll
+    for (int k = 0; k < K; k++) {
+        const u32 i = (u32)(k * G + t) * VEC;
+        if (i < n) {
+            Vec<T, VEC> r;
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                A q;
+                if constexpr (std::is_same<A, f64>::value) q = x[k][j] / sum;
+                else q = x[k][j] * inv;
+                if constexpr (is_half_v<T>) r.v[j] = from_f32<T>(q);
+                else r.v[j] = (T)q;
+            }
+            *reinterpret_cast<Vec<T, VEC>*>(dst + i) = r;
+        }
+    }
+}
+
+// Contiguous input, softmax along a dim that is not the last: a block covers 32 neighbouring (pre, post) columns with 8
+// threads each (every pass reads full 128-byte lines of 32 columns; the 8 threads of a column take every 8th element
+// of the dim and combine through shared memory); three passes as in the general kernel.
+constexpr int kSmColLanes = 32, kSmColRows = kExThreads / kSmColLanes;
+
+template <class T>
+__global__ void __launch_bounds__(kExThreads) softmax_cols_kernel(const T* __restrict__ in, T* __restrict__ out, u64 pre, u64 n, u64 post) {
+    typedef typename std::conditional<std::is_same<T, f64>::value, f64, f32>::type A;
+    __shared__ A part[kSmColRows][kSmColLanes];
+    const int lane = threadIdx.x % kSmColLanes, ry = threadIdx.x / kSmColLanes;
+    const u64 col = (u64)blockIdx.x * kSmColLanes + lane;
+    const bool live = col < pre * post;
+    const u64 pre_idx = live ? col / post : 0, post_idx = live ? col - pre_idx * post : 0;
+    const T* src = in + pre_idx * n * post + post_idx;
+    T* dst = out + pre_idx * n * post + post_idx;
+    auto value = [&](u64 i) -> A {
+        if constexpr (is_half_v<T>) return to_f32(src[i * post]);
+        else return (A)src[i * post];
+    };
+    auto column_all = [&](A v, bool is_max) -> A {
+        __syncthreads();  // the previous use of `part` has been read
+        part[ry][lane] = v;
+        __syncthreads();
+        A r = part[0][lane];
+#pragma unroll
+        for (int k = 1; k < kSmColRows; k++) r = is_max ? (part[k][lane] > r ? part[k][lane] : r) : r + part[k][lane];
+        return r;
+    };
+    A mx = -INFINITY;
+    if (live)
+        for (u64 i = ry; i < n; i += kSmColRows) {
+            const A v = value(i);
+            mx = v > mx ? v : mx;
+        }
+    mx = column_all(mx, true);
+    A sum = (A)0;
+    if (live)
+        for (u64 i = ry; i < n; i += kSmColRows) {
+            if constexpr (std::is_same<A, f64>::value) sum += exp(value(i) - mx);
+            else sum += expf(value(i) - mx);
+        }
+    sum = column_all(sum, false);
+    if (live)
+        for (u64 i = ry; i < n; i += kSmColRows) {
+            A e;
+            if constexpr (std::is_same<A, f64>::value) e = exp(value(i) - mx);
+            else e = expf(value(i) - mx);
+            const A q = e / sum;
+            if constexpr (is_half_v<T>) dst[i * post] = from_f32<T>(q);
+            else dst[i * post] = (T)q;
+        }
+}
+
+template <class T, int G>
+bool softmax_rows_launch(const T* in, T* out, u64 rows, u32 n, cudaStream_t s) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    constexpr int KMAX = sizeof(T) == 2 ? 8 : 16;  // at most 64 values per thread
+    const u32 vecs = (n / VEC + G - 1) / G;          // vectors per thread
+    const unsigned blocks = (unsigned)((rows + kExThreads / G - 1) / (kExThreads / G));
+    if (vecs <= 1) softmax_rows_kernel<T, G, 1><<<blocks, kExThreads, 0, s>>>(in, out, rows, n);
+    else if (vecs <= 2) softmax_rows_kernel<T, G, 2><<<blocks, kExThreads, 0, s>>>(in, out, rows, n);
+    else if (vecs <= 4) softmax_rows_kernel<T, G, 4><<<blocks, kExThreads, 0, s>>>(in, out, rows, n);
+    else if (vecs <= 8) softmax_rows_kernel<T, G, 8><<<blocks, kExThreads, 0, s>>>(in, out, rows, n);
+    else if (KMAX >= 16 && vecs <= 16) softmax_rows_kernel<T, G, (KMAX >= 16 ? 16 : 8)><<<blocks, kExThreads, 0, s>>>(in, out, rows, n);
+    else return false;
+    return true;
+}
+
 template <class T>
 void softmax_entry(size_t num_els, size_t nd, size_t dim, const size_t* meta, const T* in, T* out, const char* where) {
     if (!meta || !in || !out || nd == 0 || num_els == 0) return;  // the reference returns silently
@@ -331,6 +699,25 @@ void softmax_entry(size_t num_els, size_t nd, size_t dim, const size_t* meta, co
     }
     const u64 slices = P.pre * P.post;
     if (slices == 0 || P.n == 0) return;
+    cudaStream_t st = ctx().stream;
+    if (P.contiguous && slices < (1ull << 31) * kSmColLanes) {
+        constexpr int VEC = 16 / (int)sizeof(T);
+        const T* src = in + P.off;
+        const bool vec_ok = P.n % VEC == 0 && P.n < (1ull << 31) && (reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
+        if (P.post == 1 && vec_ok && P.pre < (1ull << 31)) {
+            const bool done = P.n <= 32ull * VEC * 8 ? softmax_rows_launch<T, 32>(src, out, P.pre, (u32)P.n, st)
+                                                     : softmax_rows_launch<T, kExThreads>(src, out, P.pre, (u32)P.n, st);
+            if (done) {
+                check_launch(where);
+                return;
+            }
+        }
+        if (P.post >= 16) {
+            softmax_cols_kernel<T><<<(unsigned)((slices + kSmColLanes - 1) / kSmColLanes), kExThreads, 0, st>>>(src, out, P.pre, P.n, P.post);
+            check_launch(where);
+            return;
+        }
+    }
     u64 blocks = slices < (u64)sm_count() * 16 ? slices : (u64)sm_count() * 16;
     softmax_kernel<T><<<(unsigned)blocks, kExThreads, 0, ctx().stream>>>(in, out, P);
     check_launch(where);

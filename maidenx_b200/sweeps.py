@@ -95,3 +95,29 @@ def conv_cases(N: int = 64, Cin: int = 256, H: int = 56, W: int = 56, k: int = 3
         cases.append(Case(f"conv2d_im2col_{dt}", "conv2d_im2col", dt, "im2col", meta, col, [x], col, (x + col) * s))
         cases.append(Case(f"conv2d_col2im_{dt}", "conv2d_col2im", dt, "col2im", meta, col, [col], x, (x + col) * s))
     return cases
+
+
+def extras_cases(rows: int = 16384, cols: int = 8192, N: int = 64, C: int = 256, H: int = 56, W: int = 56, pad: int = 1):
+    """The crate's remaining families at sizes of the same order as the other sweeps: softmax along the last dim of
+    [rows, cols] and along the first dim of [cols / 8, rows] (a column softmax), the three paddings of an [N, C, H, W]
+    image batch by `pad` on each side of H and W, and the backward of the constant padding."""
+    cases = []
+    n = rows * cols
+    for dt in ("f32", "bf16"):
+        s = ELEM_SIZE[dt]
+        cases.append(Case(f"softmax_{dt}/last_dim", "softmax", dt, "softmax", [rows, cols, cols, 1, 0], n, [n], n, 2 * n * s, {"dim": 1}))
+    r2, c2 = cols // 8, rows
+    cases.append(Case("softmax_f32/first_dim", "softmax", "f32", "softmax", [r2, c2, c2, 1, 0], r2 * c2, [r2 * c2], r2 * c2, 2 * r2 * c2 * 4, {"dim": 0}))
+    in_dims = [N, C, H, W]
+    out_dims = [N, C, H + 2 * pad, W + 2 * pad]
+    n_in, n_out = N * C * H * W, N * C * (H + 2 * pad) * (W + 2 * pad)
+    meta = in_dims + [C * H * W, H * W, W, 1] + [0] + out_dims + [0, 0, 0, 0, pad, pad, pad, pad]
+    for dt in ("f32", "bf16"):
+        s = ELEM_SIZE[dt]
+        for mode in ("constant", "reflection", "replication"):
+            cases.append(Case(f"pad_with_{mode}_{dt}", f"pad_with_{mode}", dt, "pad", meta, n_in, [n_in], n_out, (n_in + n_out) * s,
+                              {"n_out": n_out, "constant": mode == "constant"}))
+        # the cropped copy reads only the n_in interior elements of grad_out
+        cases.append(Case(f"pad_with_constant_backward_{dt}", "pad_with_constant_backward", dt, "pad_backward", meta, n_in, [n_out], n_in,
+                          2 * n_in * s, {"n_out": n_out}))
+    return cases

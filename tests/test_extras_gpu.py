@@ -37,6 +37,10 @@ PAD_LAYOUTS = [
     ("3d", [5, 12, 21], [252, 21, 1], 0, [(0, 0), (3, 3), (2, 4)]),
     ("3d-no-pad", [4, 6, 8], [48, 8, 1], 2, [(0, 0), (0, 0), (0, 0)]),
     ("4d-image", [2, 3, 17, 23], [3 * 17 * 23, 17 * 23, 23, 1], 0, [(0, 0), (0, 0), (2, 2), (3, 3)]),
+    ("4d-image-pad1", [3, 5, 56, 56], [5 * 56 * 56, 56 * 56, 56, 1], 0, [(0, 0), (0, 0), (1, 1), (1, 1)]),
+    ("rows-of-vectors", [6, 64], [64, 1], 0, [(1, 2), (8, 8)]),
+    ("size-1-dims", [1, 9, 1, 16], [999, 16, 7, 1], 0, [(1, 1), (0, 2), (0, 0), (3, 5)]),
+    ("first-dim-only", [11, 40], [40, 1], 4, [(3, 2), (0, 0)]),
 ]
 
 
@@ -131,6 +135,15 @@ SOFTMAX_CASES = [
     ("last-by-default", [9, 33], [33, 1], 0, 5),
     ("transposed", [40, 24], [1, 40], 0, 1),
     ("long", [3, 20000], [20000, 1], 0, 1),
+    # rows held in registers: one warp per row (up to 8 vectors per lane), one block per row beyond that
+    ("warp-rows", [70, 256], [256, 1], 0, 1),
+    ("warp-rows-partial", [33, 1000], [1000, 1], 8, 1),
+    ("block-rows", [5, 4096], [4096, 1], 0, 1),
+    ("block-rows-ragged", [3, 8200], [8200, 1], 0, 1),
+    ("block-rows-max", [2, 16384], [16384, 1], 0, 1),
+    ("rows-unaligned-offset", [6, 512], [512, 1], 3, 1),      # not 16-byte aligned: general kernel
+    ("cols-wide", [3, 50, 64], [3200, 64, 1], 0, 1),          # one thread per column
+    ("cols-first-dim", [200, 160], [160, 1], 0, 0),
 ]
 
 
