@@ -197,8 +197,14 @@ __device__ __forceinline__ bool pad_source32(int oc, int before, int size, int& 
     if (MODE == PAD_CONSTANT) {
         if (pos < 0 || pos >= size) return false;
     } else if (MODE == PAD_REFLECTION) {
-        for (int guard = 0; (pos < 0 || pos >= size) && guard < 64; guard++) pos = pos < 0 ? -pos : 2 * size - pos - 2;
-        if (pos < 0 || pos >= size) pos = 0;
+        // one fold is enough for pads below the dim size (the only ones the layers above let through); the bounded
+        // walk of the general kernel covers the rest
+        if (pos < 0) pos = -pos;
+        else if (pos >= size) pos = 2 * size - pos - 2;
+        if (pos < 0 || pos >= size) {
+            for (int guard = 0; (pos < 0 || pos >= size) && guard < 64; guard++) pos = pos < 0 ? -pos : 2 * size - pos - 2;
+            if (pos < 0 || pos >= size) pos = 0;
+        }
     } else {
         pos = pos < 0 ? 0 : (pos > size - 1 ? size - 1 : pos);
     }
@@ -529,8 +535,7 @@ __device__ __forceinline__ A softmax_group_all(A v, A* part) {
         const A w = __shfl_xor_sync(0xFFFFFFFFu, v, o);
         v = IS_MAX ? (w > v ? w : v) : v + w;
     }
-    if constexpr (G > 32) {
-        __syncthreads();  // the previous use of `part` has been read
+    if constexpr (G > 32) {  // `part` is used once per kernel (the maximum and the sum have one each)
         if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
         __syncthreads();
         v = part[0];
@@ -544,7 +549,7 @@ template <class T, int G, int K>
 __global__ void __launch_bounds__(kExThreads) softmax_rows_kernel(const T* __restrict__ in, T* __restrict__ out, u64 rows, u32 n) {
     typedef typename std::conditional<std::is_same<T, f64>::value, f64, f32>::type A;
     constexpr int VEC = 16 / (int)sizeof(T);
-    __shared__ A part[kExThreads / 32];
+    __shared__ A part_max[kExThreads / 32], part_sum[kExThreads / 32];
     const int t = threadIdx.x % G;
     const u64 row = (u64)blockIdx.x * (kExThreads / G) + threadIdx.x / G;
     if (G == 32 && row >= rows) return;  // whole warps; the warp form uses no block barrier
@@ -564,7 +569,7 @@ __global__ void __launch_bounds__(kExThreads) softmax_rows_kernel(const T* __res
             }
         }
     }
-    mx = softmax_group_all<A, G, true>(mx, part);
+    mx = softmax_group_all<A, G, true>(mx, part_max);
     A sum = (A)0;
 #pragma unroll
     for (int k = 0; k < K; k++) {
@@ -578,7 +583,7 @@ __global__ void __launch_bounds__(kExThreads) softmax_rows_kernel(const T* __res
             }
         }
     }
-    sum = softmax_group_all<A, G, false>(sum, part);
+    sum = softmax_group_all<A, G, false>(sum, part_sum);
     // f32 / 16-bit: one reciprocal per row and a multiply per element (within 1.5 ulp of the quotient); f64 divides
     const A inv = (A)1 / sum;
     T* dst = out + row * n;
