@@ -1,10 +1,12 @@
 // The remaining families of the reference's CUDA crate: fold (the backward of unfold), the three
-// paddings with their backward passes, and softmax.  They are not on the benchmarked path; the
-// kernels are plain and correct rather than tuned - one thread per output element for fold and
-// the paddings, one block per slice for softmax - and they keep the contracts of
-// the rest of the library: outputs are overwritten (no pre-zero assumption), accumulation is
-// wide (f32 for 16-bit floats, wrapping for integers) with one final rounding, and loops that
-// the reference leaves unbounded are bounded here.
+// paddings with their backward passes, and softmax.  Each has a general kernel that follows the
+// reference's index formulas for any layout (one thread per output element for fold and the
+// paddings, one block per slice for softmax) and, for the common layouts, a faster form: softmax
+// rows held in registers and a column form, paddings with a compile-time rank and 16-byte output
+// vectors, the constant padding's backward as a cropped copy.  All keep the contracts of the rest
+// of the library: outputs are overwritten (no pre-zero assumption), accumulation is wide (f32 for
+// 16-bit floats, wrapping for integers) with one final rounding, and loops that the reference
+// leaves unbounded are bounded here.
 //   fold      crates/maidenx_cpu/src/ops/reduction.rs:274-381   kernels/ops/reduction.cu:169-241
 //   padding   crates/maidenx_cpu/src/ops/padding.rs             kernels/ops/padding.cu
 //   softmax   crates/maidenx_cpu/src/nn/activation/softmax.rs   kernels/nn/activation/softmax.cu
