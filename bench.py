@@ -1163,7 +1163,7 @@ def main():
         summary["conv2d_layer_ms"] = {r["case"]: r["ms"] for r in sweeps_out["conv2d_layer"] if "what" in r}
         c1 = sweeps_out["config1"]
         summary["config1_steps_per_s"] = {k: c1.get(k) for k in ("cached_allocator_steps_per_s", "cuda_malloc_free_steps_per_s", "cpu_steps_per_s")}
-        every = [r for g in ("elementwise", "reduction", "conv", "matmul", "conv2d_layer", "movement") for r in sweeps_out[g]] + [c1]
+        every = [r for g in ("elementwise", "reduction", "conv", "matmul", "conv2d_layer", "movement", "extras") for r in sweeps_out[g]] + [c1]
         verified["sweep_cases_checked"] = sum(1 for r in every if "verified" in r)
         verified["sweep_cases_failed"] = [r["case"] for r in every if r.get("verified") is False]
         roofline["sweeps"] = summary
