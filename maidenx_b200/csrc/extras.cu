@@ -607,57 +607,87 @@ __global__ void __launch_bounds__(kExThreads) softmax_rows_kernel(const T* __res
     }
 }
 
-// Contiguous input, softmax along a dim that is not the last: a block covers 32 neighbouring (pre, post) columns with 8
-// threads each (every pass reads full 128-byte lines of 32 columns; the 8 threads of a column take every 8th element
-// of the dim and combine through shared memory); three passes as in the general kernel.
-constexpr int kSmColLanes = 32, kSmColRows = kExThreads / kSmColLanes;
-
-template <class T>
+// Contiguous input, softmax along a dim that is not the last: a block covers LANES x VEC neighbouring (pre, post)
+// columns - 128 bytes of every row it touches: 8 lanes of 16-byte vectors when the extent of the trailing dims allows,
+// else 32 lanes of single elements - with 256 / LANES threads per column group, which take every (256 / LANES)-th
+// element of the dim, four loads in flight each, and combine through shared memory; three passes as in the general kernel.
+template <class T, int VEC, int LANES>
 __global__ void __launch_bounds__(kExThreads) softmax_cols_kernel(const T* __restrict__ in, T* __restrict__ out, u64 pre, u64 n, u64 post) {
     typedef typename std::conditional<std::is_same<T, f64>::value, f64, f32>::type A;
-    __shared__ A part[kSmColRows][kSmColLanes];
+    constexpr int kSmColLanes = LANES, kSmColRows = kExThreads / LANES;
+    __shared__ A part[kSmColRows][kSmColLanes][VEC];
     const int lane = threadIdx.x % kSmColLanes, ry = threadIdx.x / kSmColLanes;
-    const u64 col = (u64)blockIdx.x * kSmColLanes + lane;
+    const u64 col = ((u64)blockIdx.x * kSmColLanes + lane) * VEC;  // VEC divides post: a vector stays inside one pre index
     const bool live = col < pre * post;
     const u64 pre_idx = live ? col / post : 0, post_idx = live ? col - pre_idx * post : 0;
     const T* src = in + pre_idx * n * post + post_idx;
     T* dst = out + pre_idx * n * post + post_idx;
-    auto value = [&](u64 i) -> A {
-        if constexpr (is_half_v<T>) return to_f32(src[i * post]);
-        else return (A)src[i * post];
-    };
-    auto column_all = [&](A v, bool is_max) -> A {
-        __syncthreads();  // the previous use of `part` has been read
-        part[ry][lane] = v;
-        __syncthreads();
-        A r = part[0][lane];
+    auto load = [&](u64 i, A (&v)[VEC]) {
+        const Vec<T, VEC> raw = *reinterpret_cast<const Vec<T, VEC>*>(src + i * post);
 #pragma unroll
-        for (int k = 1; k < kSmColRows; k++) r = is_max ? (part[k][lane] > r ? part[k][lane] : r) : r + part[k][lane];
-        return r;
+        for (int j = 0; j < VEC; j++) {
+            if constexpr (is_half_v<T>) v[j] = to_f32(raw.v[j]);
+            else v[j] = (A)raw.v[j];
+        }
     };
-    A mx = -INFINITY;
-    if (live)
-        for (u64 i = ry; i < n; i += kSmColRows) {
-            const A v = value(i);
-            mx = v > mx ? v : mx;
+    auto exp_of = [](A v) -> A {
+        if constexpr (std::is_same<A, f64>::value) return exp(v);
+        else return expf(v);
+    };
+    auto column_all = [&](A (&v)[VEC], bool is_max) {
+        __syncthreads();  // the previous use of `part` has been read
+#pragma unroll
+        for (int j = 0; j < VEC; j++) part[ry][lane][j] = v[j];
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < VEC; j++) {
+            A r = part[0][lane][j];
+#pragma unroll
+            for (int k = 1; k < kSmColRows; k++) r = is_max ? (part[k][lane][j] > r ? part[k][lane][j] : r) : r + part[k][lane][j];
+            v[j] = r;
         }
-    mx = column_all(mx, true);
-    A sum = (A)0;
-    if (live)
+    };
+    A mx[VEC], sum[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; j++) {
+        mx[j] = -INFINITY;
+        sum[j] = (A)0;
+    }
+    if (live) {
+#pragma unroll 4
         for (u64 i = ry; i < n; i += kSmColRows) {
-            if constexpr (std::is_same<A, f64>::value) sum += exp(value(i) - mx);
-            else sum += expf(value(i) - mx);
+            A v[VEC];
+            load(i, v);
+#pragma unroll
+            for (int j = 0; j < VEC; j++) mx[j] = v[j] > mx[j] ? v[j] : mx[j];
         }
-    sum = column_all(sum, false);
-    if (live)
+    }
+    column_all(mx, true);
+    if (live) {
+#pragma unroll 4
         for (u64 i = ry; i < n; i += kSmColRows) {
-            A e;
-            if constexpr (std::is_same<A, f64>::value) e = exp(value(i) - mx);
-            else e = expf(value(i) - mx);
-            const A q = e / sum;
-            if constexpr (is_half_v<T>) dst[i * post] = from_f32<T>(q);
-            else dst[i * post] = (T)q;
+            A v[VEC];
+            load(i, v);
+#pragma unroll
+            for (int j = 0; j < VEC; j++) sum[j] += exp_of(v[j] - mx[j]);
         }
+    }
+    column_all(sum, false);
+    if (live) {
+#pragma unroll 4
+        for (u64 i = ry; i < n; i += kSmColRows) {
+            A v[VEC];
+            load(i, v);
+            Vec<T, VEC> r;
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                const A q = exp_of(v[j] - mx[j]) / sum[j];
+                if constexpr (is_half_v<T>) r.v[j] = from_f32<T>(q);
+                else r.v[j] = (T)q;
+            }
+            *reinterpret_cast<Vec<T, VEC>*>(dst + i * post) = r;
+        }
+    }
 }
 
 template <class T, int G>
@@ -707,7 +737,7 @@ void softmax_entry(size_t num_els, size_t nd, size_t dim, const size_t* meta, co
     const u64 slices = P.pre * P.post;
     if (slices == 0 || P.n == 0) return;
     cudaStream_t st = ctx().stream;
-    if (P.contiguous && slices < (1ull << 31) * kSmColLanes) {
+    if (P.contiguous && slices < (1ull << 31) * 8) {
         constexpr int VEC = 16 / (int)sizeof(T);
         const T* src = in + P.off;
         const bool vec_ok = P.n % VEC == 0 && P.n < (1ull << 31) && (reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
@@ -720,7 +750,9 @@ void softmax_entry(size_t num_els, size_t nd, size_t dim, const size_t* meta, co
             }
         }
         if (P.post >= 16) {
-            softmax_cols_kernel<T><<<(unsigned)((slices + kSmColLanes - 1) / kSmColLanes), kExThreads, 0, st>>>(src, out, P.pre, P.n, P.post);
+            const bool wide = P.post % VEC == 0 && (reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
+            if (wide) softmax_cols_kernel<T, VEC, 8><<<(unsigned)((slices / VEC + 7) / 8), kExThreads, 0, st>>>(src, out, P.pre, P.n, P.post);
+            else softmax_cols_kernel<T, 1, 32><<<(unsigned)((slices + 31) / 32), kExThreads, 0, st>>>(src, out, P.pre, P.n, P.post);
             check_launch(where);
             return;
         }

@@ -144,6 +144,7 @@ SOFTMAX_CASES = [
     ("rows-unaligned-offset", [6, 512], [512, 1], 3, 1),      # not 16-byte aligned: general kernel
     ("cols-wide", [3, 50, 64], [3200, 64, 1], 0, 1),          # one thread per column
     ("cols-first-dim", [200, 160], [160, 1], 0, 0),
+    ("cols-odd-extent", [9, 40, 18], [720, 18, 1], 0, 1),     # trailing extent not a multiple of the vector: one column per lane
 ]
 
 
