@@ -41,6 +41,10 @@ PAD_LAYOUTS = [
     ("rows-of-vectors", [6, 64], [64, 1], 0, [(1, 2), (8, 8)]),
     ("size-1-dims", [1, 9, 1, 16], [999, 16, 7, 1], 0, [(1, 1), (0, 2), (0, 0), (3, 5)]),
     ("first-dim-only", [11, 40], [40, 1], 4, [(3, 2), (0, 0)]),
+    # image batches of 64 planes or more are staged plane-wise through shared memory
+    ("image-batch-odd", [4, 40, 17, 23], [40 * 17 * 23, 17 * 23, 23, 1], 0, [(0, 0), (0, 0), (2, 2), (3, 3)]),
+    ("image-batch-offset", [2, 50, 24, 24], [50 * 576, 576, 24, 1], 3, [(0, 0), (0, 0), (1, 1), (1, 1)]),
+    ("image-batch-one-side", [70, 12, 20], [240, 20, 1], 0, [(0, 0), (0, 5), (4, 0)]),
 ]
 
 
