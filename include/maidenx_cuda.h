@@ -275,8 +275,11 @@ int mx_last_cuda_error(void);
 const char* mx_last_error_where(void);
 void mx_clear_error(void);
 int mx_device_synchronize(void);
-/* 0, or the wait that gave up (1 producer, 2/3 MMA issuer, 4 epilogue) in the last tensor-core matmul of
- * this thread's device; a non-zero value is also recorded as status 5.  Call after a synchronisation. */
+/* 0, or the wait that gave up in the last kernel of this thread's device that waits on copies it queued: tensor-core
+ * matmuls (1 producer, 2/3 MMA issuer, 4 epilogue, ...), and the kernels fed through shared memory by the copy engine
+ * (21 flat elementwise with staged operands, 22 transposed tiles of 2-byte types, 23 staged col2im).  A non-zero
+ * value is also recorded as status 5.  Call after a synchronisation; cuda_memcpy_d2h and cuda_stream_synchronize
+ * check it themselves and return non-zero. */
 int mx_tc_gemm_status(void);
 /* Number of metadata blocks currently remembered by cuda_memcpy_h2d (diagnostics). */
 int mx_metadata_table_size(void);

@@ -234,7 +234,7 @@ void col2im_entry(size_t num_els, const size_t* meta, const T* col, T* out, cons
             if (num_els >= planes * plane_elems && stage_bytes % 16 == 0 && stage_bytes <= 112 * 1024 && plane_elems < (1ull << 30)) {
                 auto go = [&](auto kernel) {
                     if (stage_bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stage_bytes);
-                    kernel<<<(unsigned)planes, kConvS1Threads, stage_bytes, s>>>(col, out, Q);
+                    kernel<<<(unsigned)planes, kConvS1Threads, stage_bytes, s>>>(col, out, Q, tc::next_wait_report());
                     check_launch(where);
                 };
                 if (kw == 1 && pw == 0) { go(col2im_s1_staged_kernel<T, VEC, 1, 0>); return; }

@@ -12,6 +12,7 @@
 #pragma once
 #include "common.cuh"
 #include "ops.cuh"
+#include "tc_ptx.cuh"
 
 namespace mx {
 
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(kConvS1Threads) col2im_s1_kernel(const T* __re
 // term walk as above (same order, same rounding).  Needs the whole column buffer readable (num_els covers every plane) and
 // KH * KW * OH * OW elements to fit the shared memory of at least two resident blocks.
 template <class T, int VEC, int KW, int PW>
-__global__ void __launch_bounds__(kConvS1Threads) col2im_s1_staged_kernel(const T* __restrict__ col, T* __restrict__ out, ConvS1Params P) {
+__global__ void __launch_bounds__(kConvS1Threads) col2im_s1_staged_kernel(const T* __restrict__ col, T* __restrict__ out, ConvS1Params P, tc::WaitReport rep) {
     extern __shared__ __align__(128) unsigned char conv_s1_stage[];
     __shared__ __align__(8) unsigned long long stage_bar;
     const T* planes = reinterpret_cast<const T*>(conv_s1_stage);
@@ -170,7 +171,10 @@ __global__ void __launch_bounds__(kConvS1Threads) col2im_s1_staged_kernel(const 
             : "memory");
         landed = ok != 0;
     }
-    if (!landed) return;
+    if (!landed) {
+        tc::wait_gave_up(rep, 23);  // surfaces as status 5 at the caller's next synchronisation point
+        return;
+    }
     ConvS1Params L = P;
     L.num_els = plane_elems;  // everything staged is readable
     const uint32_t wv = P.W / VEC;

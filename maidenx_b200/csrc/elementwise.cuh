@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(kEwThreads) ew_flat_shift_kernel(F f, const T*
 // kEwUnroll vectors, i.e. 16 KB (+ 16 bytes) of shared memory per shifted operand.  The wait on the barrier is bounded.
 constexpr int kEwStageBytes = kEwThreads * kEwUnroll * 16 + 16;
 
-__device__ __forceinline__ bool ew_stage_wait(uint32_t bar) {
+__device__ __forceinline__ bool ew_stage_wait(uint32_t bar, const tc::WaitReport& rep, int code) {
     for (int i = 0; i < (1 << 26); i++) {
         uint32_t ok;
         asm volatile(
@@ -244,12 +244,13 @@ __device__ __forceinline__ bool ew_stage_wait(uint32_t bar) {
             : "memory");
         if (ok) return true;
     }
+    tc::wait_gave_up(rep, code);  // surfaces as status 5 at the caller's next synchronisation point
     return false;
 }
 
 template <class F, class T, class O, int NIN, int VEC>
 __global__ void __launch_bounds__(kEwThreads) ew_flat_shift_staged_kernel(F f, const T* a, const T* b, O* out, uint64_t n, uint64_t head,
-                                                                          uint64_t body_vecs, int sa, int sb, uint32_t sha, uint32_t shb, int stage_aligned) {
+                                                                          uint64_t body_vecs, int sa, int sb, uint32_t sha, uint32_t shb, int stage_aligned, tc::WaitReport rep) {
     extern __shared__ __align__(128) unsigned char ew_stage[];
     __shared__ __align__(8) unsigned long long stage_bar;
     const uint64_t block_v0 = (uint64_t)blockIdx.x * kEwThreads * kEwUnroll;
@@ -300,7 +301,7 @@ __global__ void __launch_bounds__(kEwThreads) ew_flat_shift_staged_kernel(F f, c
     bool landed = true;
     if (stage_a || stage_b) {
         __syncthreads();  // the barrier is initialised before anyone polls it
-        landed = ew_stage_wait(bar);
+        landed = ew_stage_wait(bar, rep, 21);
     }
     if (landed) {
 #pragma unroll
@@ -667,7 +668,7 @@ struct EwTile16Params {
 
 template <class F, class T, class O, int NIN>
 __global__ void __launch_bounds__(kEwThreads) ew_tile16_kernel(F f, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                                                               const __grid_constant__ CUtensorMap map_o, EwTile16Params P) {
+                                                               const __grid_constant__ CUtensorMap map_o, EwTile16Params P, tc::WaitReport rep) {
     static_assert(sizeof(T) == 2 && sizeof(O) == 2, "2-byte elements on both sides");
     extern __shared__ unsigned char ew_smem_raw[];
     __shared__ __align__(8) unsigned long long tile_bar;
@@ -692,7 +693,7 @@ __global__ void __launch_bounds__(kEwThreads) ew_tile16_kernel(F f, const __grid
         }
     }
     __syncthreads();  // the barrier is initialised before anyone polls it
-    const bool landed = ew_stage_wait(bar);
+    const bool landed = ew_stage_wait(bar, rep, 22);
     if (landed) {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         unsigned char* obuf = tiles + NIN * kEwT16Bytes;
@@ -805,7 +806,7 @@ bool ew_launch_tile16(const EwPlan& pl, const EwTileParams& TP, uint32_t blocks,
         maps[2] = maps[1];
         P.transposed[2] = P.batched[2] = 0;
     }
-    ew_tile16_kernel<F, T, O, NIN><<<blocks, kEwThreads, (NIN + 1) * kEwT16Bytes + 1024, s>>>(f, maps[1], maps[2], maps[0], P);
+    ew_tile16_kernel<F, T, O, NIN><<<blocks, kEwThreads, (NIN + 1) * kEwT16Bytes + 1024, s>>>(f, maps[1], maps[2], maps[0], P, tc::next_wait_report());
     return true;
 }
 
@@ -833,7 +834,7 @@ void ew_launch(const EwPlan& pl, const F& f, const T* a, const T* b, O* out, con
                 const int staged = (sa ? 1 : 0) + (sb ? 1 : 0);
                 if (staged && pl.n / VEC >= 4096) {
                     ew_flat_shift_staged_kernel<F, T, O, NIN, VEC>
-                        <<<(uint32_t)blocks, kEwThreads, (size_t)staged * kEwStageBytes, s>>>(f, a, b, out, pl.n, 0, pl.n / VEC, sa, sb, 0, 0, 1);
+                        <<<(uint32_t)blocks, kEwThreads, (size_t)staged * kEwStageBytes, s>>>(f, a, b, out, pl.n, 0, pl.n / VEC, sa, sb, 0, 0, 1, tc::next_wait_report());
                     break;
                 }
             }
@@ -860,7 +861,7 @@ void ew_launch(const EwPlan& pl, const F& f, const T* a, const T* b, O* out, con
             if (staged && body_vecs >= 4096) {
                 // large operands: the shifted ones go through shared memory, one bulk copy per block and operand
                 ew_flat_shift_staged_kernel<F, T, O, NIN, VEC>
-                    <<<(uint32_t)blocks, kEwThreads, (size_t)staged * kEwStageBytes, s>>>(f, a, b, out, pl.n, head, body_vecs, sa, sb, sha, shb, 0);
+                    <<<(uint32_t)blocks, kEwThreads, (size_t)staged * kEwStageBytes, s>>>(f, a, b, out, pl.n, head, body_vecs, sa, sb, sha, shb, 0, tc::next_wait_report());
                 break;
             }
             ew_flat_shift_kernel<F, T, O, NIN, VEC><<<(uint32_t)blocks, kEwThreads, 0, s>>>(f, a, b, out, pl.n, head, body_vecs, sa, sb, sha, shb);

@@ -668,6 +668,13 @@ int* next_launch_error_word(int* tag) {
     return s->err;
 }
 
+WaitReport next_wait_report() {
+    WaitReport w;
+    w.tag = 0;
+    w.err = next_launch_error_word(&w.tag);
+    return w;
+}
+
 }  // namespace tc
 
 // Reads the error word of the calling thread's device.  The copy runs on the legacy stream, i.e. after the work the
@@ -681,7 +688,7 @@ static int collect_tc_status(bool only_if_unchecked) {
     if (cudaMemcpy(&v, s->err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     s->unchecked = false;
     if (v != 0) {
-        set_error(kErrDeviceWait, v & 0xFF, "tc_gemm_kernel");
+        set_error(kErrDeviceWait, v & 0xFF, (v & 0xFF) >= 21 ? "staged elementwise / conv kernel" : "tc_gemm_kernel");
         cudaMemset(s->err, 0, sizeof(int));
     }
     return v & 0xFF;

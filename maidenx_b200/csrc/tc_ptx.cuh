@@ -49,6 +49,16 @@ __device__ __forceinline__ void tc_err_report(int* err, int tag, int code) {
     const int old = atomicCAS(err, 0, mine);
     if (old != 0 && (old >> 8) != tag) atomicExch(err, mine);  // a stale report of an older launch gives way
 }
+// Where a kernel outside the GEMM family records that one of its bounded waits ran out: the same per-device error
+// word, tagged with the launch.  err == nullptr (no word could be had): the kernel gives up silently as before.
+struct WaitReport {
+    int* err;
+    int tag;
+};
+__device__ __forceinline__ void wait_gave_up(const WaitReport& w, int code) {
+    if (w.err) tc_err_report(w.err, w.tag, code);
+}
+
 // Bounded wait: returns false (and records `code` in *err) when the budget runs out or when
 // another thread of this launch has already reported an error.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int tag, int code) {
@@ -223,6 +233,8 @@ void splitk_reduce(int dtype, const float* partial, int slices, size_t n, void* 
 // The error word of the calling thread's current device (allocated on first use) and the tag of the launch about
 // to be made.  Returns nullptr when there is no usable device.
 int* next_launch_error_word(int* tag);
+// The same word and a fresh tag as a WaitReport, for the staged elementwise / conv kernels (codes 21..23).
+WaitReport next_wait_report();
 
 }  // namespace tc
 }  // namespace mx

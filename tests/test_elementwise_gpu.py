@@ -397,3 +397,37 @@ def test_two_byte_transposed_tiles(oracle, cuda, dt):
             H.assert_same(op, dt, H.run_binary(cuda, *args), H.run_binary(oracle, *args), what=name)
         uop = "square" if dt.kind == "uint" else "neg"
         H.assert_same(uop, dt, H.run_unary(cuda, uop, dt, dims, ls, lo, lhs), H.run_unary(oracle, uop, dt, dims, ls, lo, lhs), what=f"unary {name}")
+
+
+def test_wait_report_of_a_staged_kernel_is_surfaced_by_the_next_copy(oracle, cuda):
+    """The kernels that are fed through shared memory by the copy engine (staged flat operands, 2-byte transposed tiles,
+    staged col2im) record a bounded wait that ran out in the same per-device word as the tensor-core products, with
+    codes 21..23.  The ABI's own synchronisation points report it.  The word is written from the host - no wait has to
+    run out on the GPU - and the launch made over the stale report still computes its result."""
+    import ctypes
+    from maidenx_b200 import _lib, device
+    lib = _lib.load()
+    poke = lib.mx_debug_tc_gemm_poke_status
+    poke.argtypes, poke.restype = [ctypes.c_int], ctypes.c_int
+    dt = D.BF16
+    rng = np.random.default_rng(5)
+    P, Q = 128, 192
+    lhs, rhs = H.random_store(rng, dt, P * Q), H.random_store(rng, dt, P * Q)
+    ref = H.run_binary(oracle, "add", dt, [P, Q], [1, P], [Q, 1], 0, 0, lhs, rhs)
+    assert poke(22) == 0
+    bufs = [device.CudaBuffer.from_host(x) for x in (lhs, rhs, np.zeros(P * Q, dt.np_storage))]
+    try:
+        meta = [P, Q, 1, P, Q, 1, 0, 0]
+        device.dispatch("add", dt.name, meta, ctypes.c_size_t(P * Q), ctypes.c_size_t(2), "META", bufs[0].ptr, bufs[1].ptr, bufs[2].ptr)
+        out = np.empty(P * Q, dt.np_storage)
+        rc = lib.cuda_memcpy_d2h(out.ctypes.data, bufs[2].ptr, out.nbytes)
+        assert rc != 0, "the copy that follows the op must report the device-side wait"
+        assert lib.mx_last_error() == 5 and lib.mx_last_cuda_error() == 22
+        assert b"staged" in lib.mx_last_error_where()
+        lib.mx_clear_error()
+        H.assert_same("add", dt, out, ref, what="tile op launched over a stale report")
+        assert lib.cuda_memcpy_d2h(out.ctypes.data, bufs[2].ptr, out.nbytes) == 0  # reported once, then clear
+    finally:
+        lib.mx_clear_error()
+        for x in bufs:
+            x.free()
