@@ -28,6 +28,8 @@ int mx_debug_matmul_forward_path_f32(size_t num_els, const size_t* host_metadata
                                      int* b_mn_major, size_t* m, size_t* n, size_t* k);
 /* Tuning aid: row-tiles per column sweep in the one-CTA tensor-core kernel's tile order (default 16). */
 void mx_debug_set_gemm_group_m(int rows);
+/* Pairs of CTAs of the two-CTA tensor-core kernel that can be resident at once on the current device (-1: query failed). */
+int mx_debug_gemm_max_resident_pairs(void);
 /* Short reductions (K <= 256, one batch, many row tiles) keep the B panel of a column tile in shared memory and stream
  * only A.  set: 1 = on (default), 0 = always the general schedule.  The query returns the CTAs per column tile a launch
  * with these tile counts takes (0 = general schedule). */

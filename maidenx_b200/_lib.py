@@ -74,6 +74,7 @@ RUNTIME_SIGNATURES = {
                                           ctypes.POINTER(ctypes.c_size_t)], ctypes.c_int),
     "mx_debug_tc_gemm_poke_status": ([ctypes.c_int], ctypes.c_int),
     "mx_debug_set_gemm_group_m": ([ctypes.c_int], None),
+    "mx_debug_gemm_max_resident_pairs": ([], ctypes.c_int),
     "mx_debug_set_gemm_keep_b": ([ctypes.c_int], None),
     "mx_debug_gemm_keep_b_ctas": ([ctypes.c_int] * 5, ctypes.c_int),
     "mx_debug_splitk_slices": ([ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int, ctypes.c_int], ctypes.c_int),

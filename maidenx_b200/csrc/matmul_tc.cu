@@ -268,7 +268,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int tm, tn, tb;
         for (int it = 0; next_tile(it, p, tm, tn, tb); it++) {
             // the TMEM loads below are warp-collective: leave the loop only as a whole warp
-            const bool ready = mbar_wait(tfull_bar(acc), acc_phase, err, tag, 4);
+            // four warps wait here for most of a tile's reduction: they sleep between polls, so that their polling does not
+            // take shared-memory cycles from the TMA writes and the tensor core's operand reads
+            const bool ready = mbar_wait_relaxed(tfull_bar(acc), acc_phase, err, tag, 4, 400);
             if (!__all_sync(0xFFFFFFFFu, ready)) break;
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
@@ -850,6 +852,7 @@ static int debug_forward_path(size_t es, size_t num_els, const size_t* host_meta
 }
 // 2: bf16 / f16 products run on the two-CTA kernel (pairs of SMs share the B tile); 1: on the one-CTA kernel.
 extern "C" void mx_set_gemm_cta_group(int ctas) { mx::g_two_cta.store(ctas == 2, std::memory_order_relaxed); }
+extern "C" int mx_debug_gemm_max_resident_pairs(void) { return mx::tc2::max_resident_pairs(); }
 extern "C" void mx_debug_set_gemm_group_m(int rows) { mx::g_group_m.store(rows > 0 ? rows : 16, std::memory_order_relaxed); }
 // 1 (default): products with a reduction of at most 256 run with the B panel resident in shared memory; 0: general schedule
 extern "C" void mx_debug_set_gemm_keep_b(int on) { mx::g_keep_b.store(on ? 1 : 0, std::memory_order_relaxed); }

@@ -363,6 +363,29 @@ bool opt_in_shared_memory() {
 
 }  // namespace
 
+// How many pairs of CTAs of this kernel can be resident at once on the current device (pairs must sit on SMs the
+// hardware can join into a cluster, which can be fewer than half the SM count); -1 when the query fails.
+int max_resident_pairs() {
+    if (!opt_in_shared_memory()) return -1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * 148, 1, 1);
+    cfg.blockDim = dim3(THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, tc_gemm2_kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return n;
+}
+
 bool launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, const Params& p, int ctas, int* err, int tag, cudaStream_t stream) {
     if (!opt_in_shared_memory()) return false;
     int grid = ctas & ~1;  // whole pairs

@@ -29,5 +29,8 @@ struct Params {
 bool launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const Params& p, int ctas, int* err, int tag,
             cudaStream_t stream);
 
+// Pairs of CTAs of the kernel that can be resident at once on the current device; -1 when the query fails.
+int max_resident_pairs();
+
 }  // namespace tc2
 }  // namespace mx
