@@ -164,6 +164,8 @@ class Launcher:
             self.args = (SZ(c.num_els), SZ(3), m, bufs["a"], bufs["out"])
         elif c.family in ("im2col", "col2im"):
             self.args = (SZ(c.num_els), m, bufs["a"], bufs["out"])
+        elif c.family == "fold":
+            self.args = (SZ(c.num_els), SZ(3), m, bufs["a"], bufs["out"])
         elif c.family == "softmax":
             self.args = (SZ(c.num_els), SZ(2), SZ(c.extra["dim"]), m, bufs["a"], bufs["out"])
         elif c.family in ("pad", "pad_backward"):
@@ -360,6 +362,22 @@ def verify_case(torch, c, a, b, out):
                 got = to_store(out[img * x_img:(img + 1) * x_img])
             ok = ok and close(got, ref, dt, 0.0, 0.0)
         return ok
+    if c.family == "fold":
+        # whole rows of the [rows, windows, size] gradient
+        R, Wn, Sz = c.extra["rows"], c.extra["windows"], c.extra["size"]
+        F = Wn - 1 + Sz
+        idx = torch.as_tensor(sample_rows(R, 12, Wn), device="cuda")
+        sub = to_store(a[:R * Wn * Sz].view(R, Wn * Sz)[idx])
+        got = to_store(out[:R * F].view(R, F)[idx])
+        k = len(idx)
+        m = np.asarray([k, Wn, Sz, Wn * Sz, Sz, 1, 1, 2, F, 1, Sz, 0], dtype=np.uint64)
+        ref = np.empty(k * F, st)
+        binding.set_wide(True)
+        try:
+            oracle_call("fold", dt, SZ(k * Wn * Sz), SZ(3), m.ctypes.data, sub.ctypes.data, ref.ctypes.data)
+        finally:
+            binding.set_wide(False)
+        return close(got, ref, dt, 1e-5 if dt == "f32" else 1e-2, 2.0)
     if c.family == "softmax":
         R, C = c.metadata[0], c.metadata[1]
         x, y = a[:R * C].view(R, C), out[:R * C].view(R, C)
@@ -455,6 +473,8 @@ def cpu_time_cases(cases, dist, passes=2):
         elif c.family == "reduce":
             args = (SZ(c.num_els), SZ(2), SZ(c.extra["num_red"]), m.ctypes.data, a.ctypes.data, o.ctypes.data)
         elif c.family == "sum_to_shape":
+            args = (SZ(c.num_els), SZ(3), m.ctypes.data, a.ctypes.data, o.ctypes.data)
+        elif c.family == "fold":
             args = (SZ(c.num_els), SZ(3), m.ctypes.data, a.ctypes.data, o.ctypes.data)
         elif c.family == "softmax":
             args = (SZ(c.num_els), SZ(2), SZ(c.extra["dim"]), m.ctypes.data, a.ctypes.data, o.ctypes.data)

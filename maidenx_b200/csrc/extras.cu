@@ -69,6 +69,41 @@ __global__ void __launch_bounds__(kExThreads) fold_kernel(const T* in, T* out, F
     }
 }
 
+// The same gather with 32-bit arithmetic for inputs below 2^32 elements whose largest source index stays inside the
+// buffer (every dense layout and every view unfold() makes): multiply-shift divisions, no wrap of the source index.
+struct FoldFastParams {
+    int nd, fold_dim, window_dim;
+    FastDiv out_div[kExMaxDims];  // by the output extents (fold_dim: fold_size; window_dim unused)
+    u32 strides[kExMaxDims];
+    u32 nwin, wsize, step, out_size;
+    u64 off;
+};
+
+template <class T>
+__global__ void __launch_bounds__(kExThreads) fold_fast_kernel(const T* __restrict__ in, T* __restrict__ out, FoldFastParams P) {
+    typedef typename SumAcc<T>::type Acc;
+    const u32 j = blockIdx.x * kExThreads + threadIdx.x;
+    if (j >= P.out_size) return;
+    u32 r = j, pos = 0, base = 0;
+    for (int d = P.nd - 1; d >= 0; d--) {
+        if (d == P.window_dim) continue;
+        u32 c;
+        P.out_div[d].divmod(r, r, c);
+        if (d == P.fold_dim) pos = c;
+        else base += c * P.strides[d];
+    }
+    const T* src = in + P.off + base;
+    Acc acc = (Acc)0;
+    // windows w with 0 <= pos - w * step < window size, in ascending order
+    const u32 w_lo = pos >= P.wsize ? (pos - P.wsize + P.step) / P.step : 0;
+    for (u32 w = w_lo; w < P.nwin && w * P.step <= pos; w++) {
+        const u32 p = pos - w * P.step;
+        if (p >= P.wsize) continue;
+        acc = acc + RedTraits<T, RED_SUM>::load(src[w * P.strides[P.fold_dim] + p * P.strides[P.window_dim]]);
+    }
+    out[j] = RedTraits<T, RED_SUM>::finalize(acc, 1);
+}
+
 template <class T>
 void fold_entry(size_t num_els, size_t nd, const size_t* meta, const T* in, T* out, const char* where) {
     const size_t* hm = resolve_metadata(meta, 2 * nd + 6);
@@ -99,6 +134,33 @@ void fold_entry(size_t num_els, size_t nd, const size_t* meta, const T* in, T* o
         P.out_size *= d == P.fold_dim ? P.fold_size : P.dims[d];
     }
     if (P.out_size == 0) return;
+    {
+        // largest source index of the layout; the reference wraps indices at num_els, which a layout inside the buffer never needs
+        u64 max_src = 0;
+        bool fits = num_els < (1ull << 32) && P.out_size < (1ull << 32) && P.fold_size < (1ull << 31) && P.step < (1ull << 31);
+        for (int d = 0; d < P.nd && fits; d++) {
+            fits = P.dims[d] > 0 && P.dims[d] < (1ull << 31) && P.strides[d] < (1ull << 32);
+            if (fits) max_src += (P.dims[d] - 1) * P.strides[d];
+        }
+        if (fits && max_src < num_els) {
+            FoldFastParams F;
+            F.nd = P.nd;
+            F.fold_dim = P.fold_dim;
+            F.window_dim = P.window_dim;
+            for (int d = 0; d < P.nd; d++) {
+                F.out_div[d].init((u32)(d == P.fold_dim ? P.fold_size : P.dims[d]));
+                F.strides[d] = (u32)P.strides[d];
+            }
+            F.nwin = (u32)P.dims[P.fold_dim];
+            F.wsize = (u32)P.dims[P.window_dim];
+            F.step = (u32)P.step;
+            F.out_size = (u32)P.out_size;
+            F.off = P.off;
+            fold_fast_kernel<T><<<(unsigned)((P.out_size + kExThreads - 1) / kExThreads), kExThreads, 0, ctx().stream>>>(in, out, F);
+            check_launch(where);
+            return;
+        }
+    }
     fold_kernel<T><<<ex_blocks(P.out_size), kExThreads, 0, ctx().stream>>>(in, out, P);
     check_launch(where);
 }

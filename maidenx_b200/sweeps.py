@@ -120,4 +120,9 @@ def extras_cases(rows: int = 16384, cols: int = 8192, N: int = 64, C: int = 256,
         # the cropped copy reads only the n_in interior elements of grad_out
         cases.append(Case(f"pad_with_constant_backward_{dt}", "pad_with_constant_backward", dt, "pad_backward", meta, n_in, [n_out], n_in,
                           2 * n_in * s, {"n_out": n_out}))
+    # fold (the backward of unfold) of a dense [rows, windows, 4] gradient with step 1: every output sums up to 4 windows
+    fr, fw, fs = rows, cols // 8 - 3, 4
+    f_in, f_out = fr * fw * fs, fr * (fw - 1 + fs)
+    cases.append(Case("fold_f32/windows_of_4", "fold", "f32", "fold", [fr, fw, fs, fw * fs, fs, 1, 1, 2, fw - 1 + fs, 1, fs, 0], f_in, [f_in], f_out,
+                      (f_in + f_out) * 4, {"rows": fr, "windows": fw, "size": fs}))
     return cases
