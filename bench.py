@@ -1251,6 +1251,18 @@ def run_only_case(torch, lib_mod, args):
         groups = sweeps.elementwise_cases(8192, 8192) + sweeps.reduction_cases(4096, 16384, (16, 512, 4096)) + sweeps.conv_cases(N=16) + sweeps.extras_cases(rows=4096, N=16)
     else:
         groups = sweeps.elementwise_cases() + sweeps.reduction_cases() + sweeps.conv_cases() + sweeps.extras_cases()
+    if args.only_case.startswith("library_gemm_"):
+        # library_gemm_<bf16|f16>[_<MxNxK>]: torch.matmul (the library GEMM) on the operands gemm_<dt> uses - a comparison point
+        # for profiles, never the product path
+        parts = args.only_case.split("_")
+        dt = parts[2]
+        M, N, K = (8192, 4096, 8192) if args.small else (MLP_GLOBAL_BATCH, MLP_DIM, MLP_DIM)
+        if len(parts) > 3:
+            M, N, K = (int(v) for v in parts[3].split("x"))
+        a, b, c, _ = gemm_operands(torch, dt, M, N, K)
+        ms = time_launches(torch, lambda: torch.matmul(a, b.t(), out=c), max(1, args.steps), max(0, args.warmup))
+        print(json.dumps({"case": args.only_case, "shape": [M, N, K], "ms": round(ms, 4), "tflops": round(2.0 * M * N * K / ms / 1e9, 1)}))
+        return
     if args.only_case.startswith("gemm_"):
         # gemm_<bf16|f16|f32>[_<MxNxK>[_<nt|nn|tn|tt>]]: a product alone; default x . W^T of one MLP layer; --small: 8192 x 4096 x 8192
         parts = args.only_case.split("_")
