@@ -248,3 +248,48 @@ def test_casts_match_the_oracle_bit_for_bit(cuda):
                     assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (sdt.name, ddt.name, shift)
                 ob.free()
         xb.free()
+
+
+def test_softmax_special_values(oracle, cuda):
+    """-inf terms (alone in a slice, beside finite values, as a slice's first or last element), +inf and NaN: the row
+    kernel, the column kernel (which folds the maximum and the sum into one pass) and the general kernel must place NaN
+    and zeros where the reference's three-pass form does."""
+    rng = np.random.default_rng(99)
+    oracle.b.set_wide(True)
+    try:
+        for dt in (D.F32, D.BF16):
+            for dims, dim in (([12, 256], 1), ([300, 64], 0), ([5, 40, 18], 1), ([7, 33], 1)):
+                n = int(np.prod(dims))
+                x = rng.standard_normal(n) * 3.0
+                v = x.reshape(dims)
+                sl = [slice(None)] * len(dims)
+
+                def at(i, j):  # slice i along the softmax dim, position j inside it
+                    idx = [0] * len(dims)
+                    idx[dim] = j
+                    other = [d for d in range(len(dims)) if d != dim]
+                    rem = i
+                    for d in reversed(other):
+                        idx[d] = rem % dims[d]
+                        rem //= dims[d]
+                    return tuple(idx)
+
+                L = dims[dim]
+                v[at(0, 0)] = -np.inf                      # first element of a slice
+                v[at(1, L - 1)] = -np.inf                  # last element
+                for j in range(L):
+                    v[at(2, j)] = -np.inf                  # a slice of nothing but -inf
+                v[at(3, L // 2)] = np.inf                  # one +inf
+                v[at(4, 1)] = np.nan                       # one NaN
+                v[at(5, 0)] = -np.inf
+                v[at(5, 3)] = np.nan                       # -inf first, NaN later
+                xs = D.encode(v.reshape(-1), dt)
+                strides = H.contiguous_strides(dims)
+                ref = D.decode(H.run_softmax(oracle, dt, dims, strides, 0, dim, xs), dt).astype(np.float64)
+                got = D.decode(H.run_softmax(cuda, dt, dims, strides, 0, dim, xs), dt).astype(np.float64)
+                assert np.array_equal(np.isnan(got), np.isnan(ref)), (dt.name, dims, dim)
+                ok = ~np.isnan(ref)
+                tol = 1e-5 if dt.name == "f32" else 2e-2
+                assert np.all(np.abs(got[ok] - ref[ok]) <= tol * np.maximum(np.abs(ref[ok]), 1e-30 if dt.name == "f32" else 1e-4)), (dt.name, dims, dim)
+    finally:
+        oracle.b.set_wide(False)
