@@ -22,8 +22,15 @@
 // The caller owns every buffer, as everywhere in this ABI: `cols` (B*P*K elements) is written by forward and read
 // by backward; `workspace` holds the intermediates (sizes from mx_conv2d_workspace_elems).
 #include "abi_common.cuh"
+#include "matmul_tc.cuh"
 
 namespace mx {
+
+template <class T>
+constexpr int half_kind_of() {
+    return std::is_same<T, bf16>::value ? 1 : (std::is_same<T, f16>::value ? 2 : 0);
+}
+
 namespace {
 
 struct Geometry {
@@ -62,13 +69,14 @@ struct Ops {
     void (*add_inplace)(size_t, size_t, const size_t*, void*, const void*);
     void (*sum)(size_t, size_t, size_t, const size_t*, const void*, void*);
     void (*contiguous)(size_t, size_t, const size_t*, const void*, void*);
+    int half_kind;  // 1 bf16, 2 f16, 0 anything else
 };
 #define MX_CONV_OPS(T)                                                                                                                  \
     mx::Ops {                                                                                                                           \
         reinterpret_cast<decltype(mx::Ops::im2col)>(cuda_conv2d_im2col_##T), reinterpret_cast<decltype(mx::Ops::col2im)>(cuda_conv2d_col2im_##T), \
             reinterpret_cast<decltype(mx::Ops::matmul)>(cuda_matmul_##T), reinterpret_cast<decltype(mx::Ops::add)>(cuda_add_##T),                 \
             reinterpret_cast<decltype(mx::Ops::add_inplace)>(cuda_add_inplace_##T), reinterpret_cast<decltype(mx::Ops::sum)>(cuda_sum_##T),        \
-            reinterpret_cast<decltype(mx::Ops::contiguous)>(mx_contiguous_##T)                                                                   \
+            reinterpret_cast<decltype(mx::Ops::contiguous)>(mx_contiguous_##T), mx::half_kind_of<mx_##T>()                                       \
     }
 
 // sum over one dim of a dense tensor, metadata as crates/maidenx_tensor/src/ops/reduction.rs:722-733 builds it
@@ -146,6 +154,9 @@ void forward(const Ops& ops, size_t es, const MxConv2d* c, int mode, const void*
     ops.im2col(ncol, cm, x, cols);
     // out[B, Co, P] = W[Co, K] (shared by every batch) . cols[B, K, P]
     const size_t mm[20] = {3, 3, 3, g.B, g.Co, g.P, g.B, g.Co, g.K, g.B, g.K, g.P, 0, g.K, 1, g.K * g.P, g.P, 1, 0, 0};
+    // 16-bit types: the bias add rides in the product's epilogue (same roundings as the two ops below) when the
+    // tensor-core kernel takes the shape
+    if (bias && ops.half_kind && tc_batched_row_bias(ops.half_kind == 1, g.B, g.Co, g.K, g.P, w, cols, bias, out, "mx_conv2d_forward")) return;
     ops.matmul(g.B * g.Co * g.P, mm, w, cols, out);
     if (bias) {
         const size_t am[11] = {g.B, g.Co, g.P, g.Co * g.P, g.P, 1, 0, 1, 0, 0, 0};

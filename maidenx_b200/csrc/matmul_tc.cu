@@ -89,7 +89,8 @@ struct TcParams {
     int a_batched, b_batched;  // 0: the operand is one matrix shared by every batch (third TMA coordinate stays 0)
     int is_bf16;
     int out_f32;  // split-K partial results: the epilogue stores the f32 accumulators unrounded
-    int fuse;     // 0: store the product; 1: u = round(round(product) + bias) through map_d; 2: also act = round(gelu(u)) through map_d2
+    int fuse;     // 0: store the product; 1: u = round(round(product) + bias) through map_d; 2: also act = round(gelu(u)) through map_d2;
+                  // 3: as 1 with one bias element per output ROW (bias[row of the batch's matrix]): a convolution's per-channel bias
     const void* bias;  // fuse != 0: one element of the operand type in device memory
     int a_mn, b_mn;  // operand is MN-major in global memory ([K, MN] row-major) instead of K-major ([MN, K])
     int group_m;     // row-tiles per column sweep (L2 re-use of the A panels)
@@ -264,12 +265,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int acc = 0, buf = 0;
         uint32_t acc_phase = 0;
         float fused_bias = 0.0f;
-        if (p.fuse) fused_bias = p.is_bf16 ? to_f32(*static_cast<const bf16*>(p.bias)) : to_f32(*static_cast<const f16*>(p.bias));
+        if (p.fuse == 1 || p.fuse == 2) fused_bias = p.is_bf16 ? to_f32(*static_cast<const bf16*>(p.bias)) : to_f32(*static_cast<const f16*>(p.bias));
         int tm, tn, tb;
         for (int it = 0; next_tile(it, p, tm, tn, tb); it++) {
             // the TMEM loads below are warp-collective: leave the loop only as a whole warp
             // four warps wait here for most of a tile's reduction: they sleep between polls, so that their polling does not
             // take shared-memory cycles from the TMA writes and the tensor core's operand reads
+            if (p.fuse == 3) {  // this thread's output row inside the batch's matrix
+                const int row = tm * BM + quarter * 32 + lane;
+                fused_bias = row < p.M ? (p.is_bf16 ? to_f32(static_cast<const bf16*>(p.bias)[row]) : to_f32(static_cast<const f16*>(p.bias)[row])) : 0.0f;
+            }
             const bool ready = mbar_wait_relaxed(tfull_bar(acc), acc_phase, err, tag, 4, 400);
             if (!__all_sync(0xFFFFFFFFu, ready)) break;
             tc_fence_after();
@@ -823,6 +828,25 @@ bool tc_linear_bias_act(bool is_bf16, uint64_t rows, uint64_t in_features, uint6
     c.a_bs = c.b_bs = 0;
     if (!bias || !u || !eligible(2, c.m, c.n, c.k, 1, false, false, x, w, u) || (act && (uintptr_t)act % 16 != 0)) return false;
     return launch_gemm(is_bf16, c, u, where, act ? 2 : 1, bias, act);
+}
+
+// out[b] = w[rows, k] (shared by every batch) . cols[b][k, n] + bias[rows] broadcast along n, the bias add in the
+// product's epilogue with the roundings of the two separate ops; false = shape not taken, nothing launched.
+bool tc_batched_row_bias(bool is_bf16, uint64_t batch, uint64_t rows, uint64_t k, uint64_t n, const void* w, const void* cols, const void* bias, void* out,
+                         const char* where) {
+    TcProduct c;
+    c.A = static_cast<const char*>(w);
+    c.B = static_cast<const char*>(cols);
+    c.a_mn = false;
+    c.b_mn = true;  // [k, n] row-major per batch
+    c.m = rows;
+    c.n = n;
+    c.k = k;
+    c.batch = batch;
+    c.a_bs = 0;
+    c.b_bs = (int64_t)(k * n);
+    if (!bias || !out || batch == 0 || batch > 0x7FFFull || !eligible(2, c.m, c.n, c.k, batch, false, true, w, cols, out)) return false;
+    return launch_gemm(is_bf16, c, out, where, 3, bias, nullptr);
 }
 
 bool tc_gemm_bf16_f16(bool is_bf16, const MmDesc& d, int which, size_t num_els, size_t nea, size_t neb, const void* x, const void* y, void* out,

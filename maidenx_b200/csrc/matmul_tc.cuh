@@ -28,6 +28,10 @@ bool tc_gemm_bf16_f16(bool is_bf16, const MmDesc& d, int which, size_t num_els, 
 // memory.  Returns false when the shape does not qualify for the tensor-core kernel; nothing was launched then.
 bool tc_linear_bias_act(bool is_bf16, uint64_t rows, uint64_t in_features, uint64_t out_features, const void* x, const void* w, const void* bias,
                         void* u, void* act, const char* where);
+// Batched product with a per-row bias in the epilogue (bf16 / f16): out[b] = w[rows, k] . cols[b][k, n] + bias[rows], the
+// form of a convolution's forward pass over its column buffer.  false = not taken by the tensor-core kernel, nothing launched.
+bool tc_batched_row_bias(bool is_bf16, uint64_t batch, uint64_t rows, uint64_t k, uint64_t n, const void* w, const void* cols, const void* bias, void* out,
+                         const char* where);
 bool tc_gemm_f32(const MmDesc& d, int which, size_t num_els, size_t nea, size_t neb, const void* x, const void* y, void* out, const char* where);
 
 template <class T>

@@ -137,3 +137,18 @@ def test_literal_call_sequence_is_refused_when_the_swapped_slots_would_mean_a_ze
     fwd(ctypes.byref(conv), 0, 1, 1, None, 1, 1, 1)  # refused before any pointer is touched
     assert lib.mx_last_error() == 3
     lib.mx_clear_error()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", [D.BF16, D.F16], ids=lambda d: d.name)
+@pytest.mark.parametrize("shape", [(8, 32, 24, 24, 128, 3, 3, 1, 1, 1, 1), (5, 16, 20, 24, 200, 3, 3, 1, 1, 1, 1)], ids=lambda s: "x".join(map(str, s)))
+def test_bias_in_the_product_epilogue_equals_the_separate_add(cuda, dt, shape):
+    """Direct form, 16-bit types, shapes the tensor-core kernel takes: the per-channel bias rides in the batched
+    product's epilogue (one bias element per output row).  Bit for bit what cuda_matmul followed by cuda_add_inplace
+    gives (the op-by-op composition on the same backend), with ragged row tiles (200 channels) as well."""
+    x, w, b, g = _data(15, dt, shape)
+    got = CC.run_layer(dt, 1, shape, x, w, b, g)
+    ref = CC.compose(cuda, dt, 1, shape, x, w, b, g)
+    assert np.array_equal(got["out"], ref["out"])
+    for key in ("grad_x", "grad_w", "grad_bias"):
+        assert np.array_equal(got[key], ref[key]), key
